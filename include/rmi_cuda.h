@@ -1,0 +1,218 @@
+/*
+ * rmi_cuda.h -- C ABI of librmi_cuda.so: the quantized-matmul hot path of
+ * rust-model-inference on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point replaces (or is bound by) one interface of the reference; the
+ * comment above each declaration names it as path:line inside the reference project.
+ * All functions return an rmi_status (0 = ok).  After a non-zero return
+ * rmi_last_error() holds a message for the calling thread.  There is no CPU fallback:
+ * when no CUDA device is usable rmi_init fails and nothing else can be called.
+ *
+ * Pointer conventions: plain names are HOST pointers (the call copies in and out and
+ * returns after the result is in the host buffer).  Entry points ending in _dev take
+ * DEVICE pointers, enqueue on the context's stream and return without synchronising.
+ *
+ * Threading: a context may be used from several host threads; calls are serialised on
+ * one stream.  The reference invokes its kernels from every pool thread with
+ * (ith, nth) (src/ops/kernel/trait_.rs:15-31); here the caller passes the row range
+ * [row_begin, row_end) that (ith, nth) selects, and only that range of `output` is
+ * written, exactly as src/ops/kernel/q8_0/parallel.rs:124-139 does.
+ */
+#ifndef RMI_CUDA_H
+#define RMI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rmi_ctx rmi_ctx;
+typedef struct rmi_weight rmi_weight;
+typedef struct rmi_gguf rmi_gguf;
+typedef struct rmi_qwen3 rmi_qwen3;
+typedef struct rmi_session rmi_session;
+
+typedef enum {
+  RMI_OK = 0,
+  RMI_ERR_BAD_HANDLE = 1,  /* null / foreign handle */
+  RMI_ERR_BAD_SHAPE = 2,   /* n_in % 32 != 0 (Q8_0), % 256 != 0 (Q4_K), short buffer, bad row range */
+  RMI_ERR_OOM = 3,         /* device or host allocation failed */
+  RMI_ERR_CUDA = 4,        /* a CUDA call failed; message has the CUDA error string */
+  RMI_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up (kernel returned cleanly) */
+  RMI_ERR_UNSUPPORTED = 6, /* ggml type / semantics / size not handled by this path */
+  RMI_ERR_IO = 7,          /* file open / mmap failed */
+  RMI_ERR_FORMAT = 8,      /* malformed GGUF or model metadata */
+  RMI_ERR_NONFINITE = 9    /* "Cannot sample non-finite logits" (src/models/qwen3.rs:172-191) */
+} rmi_status;
+
+/* ggml type ids as in src/core/tensor.rs:15-35 */
+enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12 };
+
+/* The reference has three instruction-set variants of this path whose f32 results are not
+ * bit-identical to each other (docs/OPTIMIZATION.md:330-332).  The device reproduces the
+ * chosen one bit for bit:
+ *   AVX2   src/ops/quant/q8_0.rs:176-230 + src/ops/kernel/q8_0/avx2.rs:53-174
+ *   NEON   src/ops/quant/q8_0.rs:75-165  + src/ops/kernel/q8_0/neon.rs:49-73
+ *   SCALAR src/ops/quant/q8_0.rs:49-71   + src/ops/kernel/q8_0/scalar.rs:31-58
+ * The tensor-core GEMM (M > 32) yields whole-block int32 sums, so it implements NEON or
+ * SCALAR accumulation; under AVX2 it accumulates as NEON does (within 1e-5 relative of
+ * the AVX2 kernel, exact block sums). */
+typedef enum { RMI_SEM_AVX2 = 0, RMI_SEM_NEON = 1, RMI_SEM_SCALAR = 2 } rmi_semantics;
+
+/* ---- context ------------------------------------------------------------------------
+ * Replaces VulkanContext::new / Drop (src/vulkan.rs:31-59, :713-725) and the lazy global
+ * in src/ops/float.rs:44-58.  Init failure is an error, never a CPU fallback. */
+int32_t rmi_init(int32_t device, rmi_ctx** out);
+int32_t rmi_destroy(rmi_ctx* ctx);
+const char* rmi_last_error(void);
+int32_t rmi_set_semantics(rmi_ctx* ctx, int32_t sem);
+int32_t rmi_get_semantics(rmi_ctx* ctx, int32_t* sem);
+/* Use an existing cudaStream_t (e.g. the framework's current stream); NULL restores the
+ * context's own stream. */
+int32_t rmi_set_stream(rmi_ctx* ctx, void* cuda_stream);
+int32_t rmi_sync(rmi_ctx* ctx);
+/* sm count, L2 bytes, total device memory */
+int32_t rmi_device_info(rmi_ctx* ctx, int32_t* sm_count, size_t* l2_bytes, size_t* mem_bytes);
+/* Number of kernels this library has launched on this context (for launch accounting). */
+int32_t rmi_launch_count(rmi_ctx* ctx, uint64_t* count);
+
+/* Device buffers for callers that have no CUDA allocator of their own. */
+int32_t rmi_dev_alloc(rmi_ctx* ctx, size_t bytes, void** dev_ptr);
+int32_t rmi_dev_free(rmi_ctx* ctx, void* dev_ptr);
+int32_t rmi_h2d(rmi_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int32_t rmi_d2h(rmi_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+int32_t rmi_host_alloc_pinned(rmi_ctx* ctx, size_t bytes, void** host_ptr);
+int32_t rmi_host_free_pinned(rmi_ctx* ctx, void* host_ptr);
+
+/* ---- weights ------------------------------------------------------------------------
+ * Replaces QuantizedTensor::from_bytes + into_kernel (src/ops/kernel/quantized_tensor.rs:
+ * 120-189): called once per tensor at load with the raw GGUF bytes (row-major blocks,
+ * row length n_in, n_out rows).  Rows [row_begin, row_end) are uploaded -- the
+ * PlacementSlice::Rows of src/format/load_plan.rs:19-22 -- and re-laid out for the device
+ * (16-row interleaved blocks: 32 B of f16 scales then 16 x 32 B of quants).  The host bytes are not
+ * referenced after the call returns. */
+int32_t rmi_weight_upload(rmi_ctx* ctx, int32_t ggml_type, const void* bytes, size_t nbytes,
+                          size_t n_in, size_t n_out, size_t row_begin, size_t row_end,
+                          rmi_weight** out);
+int32_t rmi_weight_free(rmi_ctx* ctx, rmi_weight* w);
+int32_t rmi_weight_info(const rmi_weight* w, int32_t* ggml_type, size_t* n_in, size_t* n_rows,
+                        size_t* device_bytes);
+/* fuse_vstack_q8_0 / fuse_vstack_q4_k (src/ops/quant/fuse.rs:25-63) and
+ * QTensorOwned::fuse_vstack (src/ops/kernel/qtensor_owned.rs:138-164): rows of a, then rows
+ * of b.  RMI_ERR_BAD_SHAPE when the row lengths differ (the reference returns None). */
+int32_t rmi_weight_fuse_vstack(rmi_ctx* ctx, const rmi_weight* a, const rmi_weight* b,
+                               rmi_weight** out);
+
+/* ---- Q8_0 activation quantizer --------------------------------------------------------
+ * quantize_q8_0_into (src/ops/quant/q8_0.rs:3-24), row-wise for m rows of length n:
+ * q8[m*n] int8 as u8, scales[m*n/32] = f32(f16(amax/127)). */
+int32_t rmi_quantize_q8_0(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8,
+                          float* scales);
+int32_t rmi_quantize_q8_0_dev(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8,
+                              float* scales);
+
+/* ---- Q8_0 matmul ------------------------------------------------------------------------
+ * Kernel::forward_prequantized (src/ops/kernel/trait_.rs:19-29) ==
+ * matmul_q8_0_quantized_parallel_rows (src/ops/kernel/q8_0/parallel.rs:102-139) and the
+ * GPU hook ctx.matmul_q8_0 (src/vulkan.rs:347-355), for m activation rows:
+ *   output[t*n_rows + r] for r in [row_begin,row_end) ; other elements are not touched. */
+int32_t rmi_matmul_q8_0_prequantized(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8,
+                                     const float* scales, size_t m, float* output,
+                                     size_t row_begin, size_t row_end);
+int32_t rmi_matmul_q8_0_prequantized_dev(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8,
+                                         const float* scales, size_t m, float* output,
+                                         size_t row_begin, size_t row_end);
+/* Kernel::forward / forward_batched (src/ops/kernel/trait_.rs:57-109): per row quantize,
+ * then the matmul.  m <= 32 runs the memory-bound GEMV kernels, m > 32 the tcgen05 GEMM. */
+int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
+int32_t rmi_matmul_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                            float* output);
+/* Exact int32 dot of every 32-block, sums[(t*n_rows + r)*(n_in/32) + b]; debug/parity aid
+ * with no counterpart in the reference API (it is the integer part of
+ * src/ops/kernel/q8_0/scalar.rs:49-55).  use_tensor_cores != 0 routes through the
+ * tcgen05 int8 MMA path (m is padded to the tile internally). */
+int32_t rmi_q8_0_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8, size_t m,
+                            int32_t* sums, int32_t use_tensor_cores);
+
+/* ---- fused SwiGLU FFN -------------------------------------------------------------------
+ * src/models/qwen3.rs:981-1046 for m tokens: quantize x, gate and up projections (one
+ * pass over the v-stacked weight), up * silu(gate), re-quantize, down projection.
+ * w_gate_up must come from rmi_weight_fuse_vstack(gate, up).  x [m,n_embd] -> out [m,n_embd]. */
+int32_t rmi_ffn_swiglu_q8_0(rmi_ctx* ctx, const rmi_weight* w_gate_up, const rmi_weight* w_down,
+                            const float* x, size_t m, float* out);
+int32_t rmi_ffn_swiglu_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w_gate_up,
+                                const rmi_weight* w_down, const float* x, size_t m, float* out);
+/* silu_mul_inplace (src/ops/activation/mod.rs:137-151): up[i] *= gate[i]/(1+exp(-gate[i])) */
+int32_t rmi_silu_mul(rmi_ctx* ctx, const float* gate, float* up, size_t n);
+
+/* ---- Q4_K -------------------------------------------------------------------------------
+ * BlockQ8K (src/ops/quant/mod.rs:36-40) as three arrays: d[nb], qs[nb*256], bsums[nb*16].
+ * quantize_row_q8_k_into (src/ops/quant/mod.rs:52-61). */
+int32_t rmi_quantize_q8_k(rmi_ctx* ctx, const float* x, size_t m, size_t n, float* d, int8_t* qs,
+                          int16_t* bsums);
+/* Q4_KKernel::forward_prepared (src/ops/kernel/q4_k.rs:56-93): Q8_K activation, then
+ * vec_dot_q4k_q8k per row (src/ops/quant/mod.rs:202-289, :701-799). */
+int32_t rmi_matmul_q4_k_q8k(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                            float* output, size_t row_begin, size_t row_end);
+/* QuantizedLinear::forward_dequant / Layer::forward (src/core/model.rs:65-93): dequantized
+ * f32 weights times the f32 input.  No 64 MiB scratch: weights are decoded in registers. */
+int32_t rmi_matmul_q4_k_dequant(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                float* output);
+int32_t rmi_matmul_q4_k_dequant_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                    float* output);
+/* dequantize_q4_k_weight (src/ops/quant/mod.rs:492-508) */
+int32_t rmi_dequantize_q4_k(rmi_ctx* ctx, const rmi_weight* w, float* output);
+
+/* ---- GGUF -------------------------------------------------------------------------------
+ * GGUFLoader::from_file / tensor_info / tensor_slice / metadata (src/core/loader.rs:211-395):
+ * mmap + header, KV and tensor-table parse with the same range checks. */
+int32_t rmi_gguf_open(const char* path, rmi_gguf** out);
+int32_t rmi_gguf_close(rmi_gguf* g);
+int32_t rmi_gguf_n_tensors(const rmi_gguf* g, size_t* n);
+int32_t rmi_gguf_tensor(const rmi_gguf* g, const char* name, int32_t* ggml_type, uint64_t dims[4],
+                        int32_t* n_dims, const void** data, size_t* nbytes);
+int32_t rmi_gguf_meta_u64(const rmi_gguf* g, const char* key, uint64_t* value);
+int32_t rmi_gguf_meta_f64(const rmi_gguf* g, const char* key, double* value);
+int32_t rmi_gguf_meta_str(const rmi_gguf* g, const char* key, char* buf, size_t buf_len);
+/* tensor_slice -> device layout in one step ("GGUF mmap weight upload") */
+int32_t rmi_weight_upload_gguf(rmi_ctx* ctx, const rmi_gguf* g, const char* name,
+                               size_t row_begin, size_t row_end, rmi_weight** out);
+
+/* ---- Qwen3 decode -----------------------------------------------------------------------
+ * Qwen3Model::from_source (src/models/qwen3.rs:246-400): checks dims/types per tensor and
+ * uploads every weight once. */
+int32_t rmi_qwen3_load(rmi_ctx* ctx, const char* gguf_path, rmi_qwen3** out);
+int32_t rmi_qwen3_free(rmi_ctx* ctx, rmi_qwen3* model);
+int32_t rmi_qwen3_config(const rmi_qwen3* model, size_t* n_embd, size_t* n_layer, size_t* n_head,
+                         size_t* n_head_kv, size_t* head_dim, size_t* n_ff, size_t* vocab);
+/* Qwen3Session::new (src/models/qwen3.rs:440-550) for `batch` independent sequences:
+ * F16 KV cache [batch][n_layer][capacity][n_head_kv*head_dim] x2 in HBM plus all scratch. */
+int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size_t batch, size_t capacity,
+                           rmi_session** out);
+int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s);
+/* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): feeds the prompts one
+ * position at a time, then generates n_gen tokens per sequence; the whole step runs on the
+ * device.  prompts [batch, n_prompt] u32, out_tokens [batch, n_gen] u32.  EOS handling is
+ * the caller's (there is no tokenizer here).  gen_ms (optional) receives the device time of
+ * the n_gen generation steps, prefill_ms that of the prompt steps. */
+int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint32_t* prompts,
+                             size_t n_prompt, size_t n_gen, uint32_t* out_tokens, float* prefill_ms,
+                             float* gen_ms);
+/* Debug/parity reads after a generate call: hidden state of the last step [batch, n_embd]
+ * and logits of the last step [batch, vocab]. */
+int32_t rmi_session_read_hidden(rmi_ctx* ctx, rmi_session* s, float* hidden);
+int32_t rmi_session_read_logits(rmi_ctx* ctx, rmi_session* s, float* logits);
+
+/* ---- column-sharded matmul --------------------------------------------------------------
+ * New for multi-GPU (the reference only plans row splits: src/format/load_plan.rs:208-330).
+ * After each rank computed y_r [m, n/g] and an all-gather produced gathered [g, m, n/g],
+ * this restores row-major [m, n] on the device. */
+int32_t rmi_unshard_cols_dev(rmi_ctx* ctx, const float* gathered, size_t g, size_t m,
+                             size_t n_per_rank, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

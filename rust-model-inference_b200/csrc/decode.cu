@@ -1,0 +1,338 @@
+// Element-wise and attention kernels of the Qwen3 decode step, each reproducing the
+// reference's x86 arithmetic (paths inside the reference project):
+//   embedding row        src/ops/embedding.rs:12-22
+//   rms_norm             src/ops/norm.rs:3-19        (f32 squares summed in f64)
+//   rope_neox            src/ops/rope.rs:21-37       (cos/sin come from a host-built table)
+//   K/V -> f16 cache     src/models/qwen3.rs:851-870
+//   attention            src/models/qwen3.rs:876-933 (f16 q/k/v/p, f64 dot accumulation,
+//                        sequential f32 softmax sum: src/ops/attention.rs:28-38)
+//   greedy argmax        src/models/qwen3.rs:172-191 (first maximum, non-finite -> error)
+#include "common.cuh"
+#include "decode.cuh"
+#include "kernels.cuh"
+
+namespace {
+
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// x[b][:] = f16(d) * q of the token's embedding row (tile16 layout).
+__global__ void embed_kernel(const uint8_t* __restrict__ emb, size_t blocks, const uint32_t* __restrict__ prompts,
+                             size_t n_prompt, const uint32_t* __restrict__ gen, size_t n_gen,
+                             const int* __restrict__ d_step, float* __restrict__ x, uint32_t vocab) {
+  const size_t b = blockIdx.x;
+  const int step = *d_step;
+  uint32_t tok = (size_t)step < n_prompt ? prompts[b * n_prompt + step] : gen[b * n_gen + (step - n_prompt)];
+  if (tok >= vocab) tok = 0;  // out-of-range ids are rejected on the host before the first step
+  const uint8_t* base = emb + (size_t)(tok / 16) * blocks * Q8_REC_BYTES;
+  const int r = tok % 16;
+  for (size_t i = threadIdx.x; i < blocks * 32; i += blockDim.x) {
+    const uint8_t* rec = base + (i / 32) * Q8_REC_BYTES;
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(rec + 2 * r));
+    x[b * blocks * 32 + i] = __fmul_rn(d, (float)(int8_t)rec[32 + 32 * r + (i & 31)]);
+  }
+}
+
+// Optional residual add (x += add), rms_norm(x, weight) and Q8_0 quantization of the result.
+// One CTA of 256 threads per sequence; warp w owns 32-blocks w, w+8, ...
+template <int SEM>
+__global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restrict__ add,
+                                     const float* __restrict__ weight, size_t n, float eps,
+                                     uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  __shared__ double s_part[8];
+  __shared__ float s_scale;
+  const size_t b = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t blocks = n / 32;
+  float* xr = x + b * n;
+  double part = 0.0;
+  for (size_t blk = warp; blk < blocks; blk += 8) {
+    float v = xr[blk * 32 + lane];
+    if (add) {
+      v = __fadd_rn(v, add[b * n + blk * 32 + lane]);
+      xr[blk * 32 + lane] = v;
+    }
+    part += (double)__fmul_rn(v, v);
+  }
+  part = warp_sum_f64(part);
+  if (lane == 0) s_part[warp] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (int w = 0; w < 8; w++) s += s_part[w];
+    const float mean_sq = (float)(s / (double)n);
+    s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+  }
+  __syncthreads();
+  const float sc = s_scale;
+  for (size_t blk = warp; blk < blocks; blk += 8) {
+    const float v = __fmul_rn(__fmul_rn(xr[blk * 32 + lane], sc), weight[blk * 32 + lane]);
+    float a = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    float d, inv;
+    q8_scale_pair<SEM>(a, &d, &inv);
+    q8[b * n + blk * 32 + lane] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
+    if (lane == 0) scales[b * blocks + blk] = f16_round_trip(d);
+  }
+}
+
+// Per-head q/k rms_norm, NeoX rope, f16 conversion; K and V appended to the cache.
+// grid (batch, n_head + 2*n_head_kv), one warp per head.
+__global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_head, size_t n_head_kv, size_t hd,
+                                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                       const float* __restrict__ rope, const int* __restrict__ d_step,
+                                       uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
+                                       uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
+                                       size_t capacity) {
+  const size_t b = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x;
+  const int step = *d_step;
+  const size_t nq = n_head * hd, nk = n_head_kv * hd, half = hd / 2;
+  const float* src = qkv + b * (nq + 2 * nk) + head * hd;
+  const size_t cache_row = ((b * n_layer + layer) * capacity + (size_t)step) * nk;
+  if (head >= n_head + n_head_kv) {  // V: straight f16 conversion
+    const size_t kvh = head - n_head - n_head_kv;
+    for (size_t i = lane; i < hd; i += 32) v_cache[cache_row + kvh * hd + i] = f32_to_f16_bits(src[i]);
+    return;
+  }
+  const bool is_q = head < n_head;
+  const float* nw = is_q ? q_norm : k_norm;
+  double part = 0.0;
+  for (size_t i = lane; i < hd; i += 32) part += (double)__fmul_rn(src[i], src[i]);
+  part = warp_sum_f64(part);
+  float sc = 1.0f;
+  if (nw) {
+    const float mean_sq = (float)(part / (double)hd);
+    sc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+  }
+  const float* tab = rope + (size_t)step * hd;  // [pos][half][2]
+  uint16_t* dst = is_q ? q16 + b * nq + head * hd : k_cache + cache_row + (head - n_head) * hd;
+  for (size_t i = lane; i < half; i += 32) {
+    float x0 = src[i], x1 = src[i + half];
+    if (nw) {
+      x0 = __fmul_rn(__fmul_rn(x0, sc), nw[i]);
+      x1 = __fmul_rn(__fmul_rn(x1, sc), nw[i + half]);
+    }
+    const float c = tab[2 * i], s = tab[2 * i + 1];
+    const float r0 = __fmaf_rn(x0, c, __fmul_rn(x1, -s));
+    const float r1 = __fmaf_rn(x0, s, __fmul_rn(x1, c));
+    dst[i] = f32_to_f16_bits(r0);
+    dst[i + half] = f32_to_f16_bits(r1);
+  }
+}
+
+// One CTA per (sequence, kv head); the `group` query heads that share the kv head are
+// processed together.  Output is re-quantized to Q8_0 for the Wo projection.
+template <int SEM>
+__global__ void __launch_bounds__(256)
+    attention_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
+                     const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
+                     size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                     float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const size_t b = blockIdx.x, kvh = blockIdx.y;
+  const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
+  const int T = *d_step + 1;
+  float* sc = reinterpret_cast<float*>(smem);                        // [group][capacity]
+  float* outv = sc + group * capacity;                               // [group][hd]
+  float* red = outv + group * hd;                                    // [group] sums / maxima
+  uint16_t* p16 = reinterpret_cast<uint16_t*>(red + 2 * group + 2);  // [group][capacity]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+  const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+
+  // scores[g][t] = f32(sum_f64 q*k) * kq_scale
+  for (int t = warp; t < T; t += nwarp) {
+    const uint16_t* kr = kbase + (size_t)t * nk;
+    for (size_t g = 0; g < group; g++) {
+      const uint16_t* qr = q16 + b * nq + (kvh * group + g) * hd;
+      double s = 0.0;
+      for (size_t i = lane; i < hd; i += 32)
+        s += (double)__fmul_rn(f16_bits_to_f32(qr[i]), f16_bits_to_f32(kr[i]));
+      s = warp_sum_f64(s);
+      if (lane == 0) sc[g * capacity + t] = __fmul_rn((float)s, kq_scale);
+    }
+  }
+  __syncthreads();
+  // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
+  for (size_t g = warp; g < group; g += nwarp) {
+    float mx = -INFINITY;
+    for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * capacity + t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int t = lane; t < T; t += 32) sc[g * capacity + t] = exp_cr(__fsub_rn(sc[g * capacity + t], mx));
+    __syncwarp();
+    if (lane == 0) {
+      float sum = 0.0f;
+      for (int t = 0; t < T; t++) sum = __fadd_rn(sum, sc[g * capacity + t]);
+      red[g] = sum;
+    }
+    __syncwarp();
+    const float sum = red[g];
+    for (int t = lane; t < T; t += 32) {
+      float pv = sc[g * capacity + t];
+      if (sum > 0.0f) pv = __fdiv_rn(pv, sum);
+      p16[g * capacity + t] = f32_to_f16_bits(pv);
+    }
+  }
+  __syncthreads();
+  // out[g][d] = f32(sum_f64 v[t][d] * p[g][t])
+  for (size_t o = threadIdx.x; o < group * hd; o += blockDim.x) {
+    const size_t g = o / hd, d = o % hd;
+    double s = 0.0;
+    for (int t = 0; t < T; t++)
+      s += (double)__fmul_rn(f16_bits_to_f32(vbase[(size_t)t * nk + d]), f16_bits_to_f32(p16[g * capacity + t]));
+    outv[o] = (float)s;
+  }
+  __syncthreads();
+  // write f32 (debug) and Q8_0 blocks of this kv head's group*hd outputs
+  const size_t out0 = kvh * group * hd;  // heads kvh*group .. are contiguous in attn_out
+  for (size_t blk = warp; blk < group * hd / 32; blk += nwarp) {
+    const float v = outv[blk * 32 + lane];
+    if (attn_out) attn_out[b * nq + out0 + blk * 32 + lane] = v;
+    float a = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    float d, inv;
+    q8_scale_pair<SEM>(a, &d, &inv);
+    q8[b * nq + out0 + blk * 32 + lane] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
+    if (lane == 0) scales[b * (nq / 32) + (out0 / 32) + blk] = f16_round_trip(d);
+  }
+}
+
+// First maximal index per sequence; raises *flag when a logit is not finite.
+__global__ void argmax_kernel(const float* __restrict__ logits, size_t vocab, const int* __restrict__ d_step,
+                              size_t n_prompt, uint32_t* __restrict__ gen, size_t n_gen, int* __restrict__ flag) {
+  __shared__ float s_v[32];
+  __shared__ uint32_t s_i[32];
+  const size_t b = blockIdx.x;
+  const float* l = logits + b * vocab;
+  float best = -INFINITY;
+  uint32_t bi = 0xffffffffu;
+  bool bad = false;
+  for (size_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = l[i];
+    if (!isfinite(v)) bad = true;
+    if (v > best || (v == best && (uint32_t)i < bi)) {
+      best = v;
+      bi = (uint32_t)i;
+    }
+  }
+  if (bad) atomicExch(flag, 1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    s_v[warp] = best;
+    s_i[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+      if (s_v[w] > best || (s_v[w] == best && s_i[w] < bi)) {
+        best = s_v[w];
+        bi = s_i[w];
+      }
+    const int step = *d_step;
+    const size_t gi = (size_t)step + 1 - n_prompt;  // step >= n_prompt-1 when this kernel runs
+    if (gi < n_gen) gen[b * n_gen + gi] = bi == 0xffffffffu ? 0u : bi;
+  }
+}
+
+__global__ void step_inc_kernel(int* d_step) { *d_step += 1; }
+
+__global__ void unshard_cols_kernel(const float* __restrict__ gathered, size_t g, size_t m, size_t npr,
+                                    float* __restrict__ out) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= g * m * npr) return;
+  const size_t c = idx % npr, r = (idx / npr) % m, rank = idx / (npr * m);
+  out[r * (g * npr) + rank * npr + c] = gathered[idx];
+}
+
+}  // namespace
+
+int32_t launch_unshard_cols(rmi_ctx* ctx, const float* gathered, size_t g, size_t m, size_t npr, float* out) {
+  const size_t n = g * m * npr;
+  if (n == 0) return RMI_OK;
+  unshard_cols_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(gathered, g, m, npr, out);
+  return rmi_post_launch(ctx, "unshard_cols");
+}
+
+int32_t launch_embed(rmi_ctx* ctx, const rmi_weight* emb, const uint32_t* prompts, size_t n_prompt, const uint32_t* gen,
+                     size_t n_gen, const int* d_step, float* x, size_t batch) {
+  embed_kernel<<<(unsigned)batch, 256, 0, ctx->stream>>>(emb->d_tile16, emb->n_in / 32, prompts, n_prompt, gen, n_gen,
+                                                         d_step, x, (uint32_t)emb->n_rows);
+  return rmi_post_launch(ctx, "embed");
+}
+
+int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const float* weight, size_t n, float eps,
+                             uint8_t* q8, float* scales, size_t batch) {
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: rmsnorm_quant_kernel<RMI_SEM_AVX2><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
+    case RMI_SEM_NEON: rmsnorm_quant_kernel<RMI_SEM_NEON><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
+    default: rmsnorm_quant_kernel<RMI_SEM_SCALAR><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
+  }
+  return rmi_post_launch(ctx, "rmsnorm_quant");
+}
+
+int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
+                               const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
+                               uint16_t* k_cache, uint16_t* v_cache, size_t layer) {
+  dim3 grid((unsigned)d.batch, (unsigned)(d.n_head + 2 * d.n_head_kv));
+  qk_norm_rope_kv_kernel<<<grid, 32, 0, ctx->stream>>>(qkv, d.n_head, d.n_head_kv, d.hd, q_norm, k_norm, d.eps, rope,
+                                                       d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity);
+  return rmi_post_launch(ctx, "qk_norm_rope_kv");
+}
+
+size_t attention_smem_bytes(const decode_dims& d) {
+  const size_t group = d.n_head / d.n_head_kv;
+  return (group * d.capacity + group * d.hd + 2 * group + 2) * 4 + group * d.capacity * 2 + 16;
+}
+
+int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
+                         const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                         float* scales) {
+  const size_t smem = attention_smem_bytes(d);
+  dim3 grid((unsigned)d.batch, (unsigned)d.n_head_kv);
+#define RMI_ATT(SEMV)                                                                                             \
+  do {                                                                                                            \
+    auto kern = attention_kernel<SEMV>;                                                                           \
+    if (smem > 48 * 1024 &&                                                                                       \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {      \
+      rmi_set_error("attention needs %zu B of shared memory", smem);                                              \
+      return RMI_ERR_UNSUPPORTED;                                                                                 \
+    }                                                                                                             \
+    kern<<<grid, 256, smem, ctx->stream>>>(q16, k_cache, v_cache, d_step, d.n_head, d.n_head_kv, d.hd, layer,      \
+                                           d.n_layer, d.capacity, attn_out, q8, scales);                          \
+  } while (0)
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: RMI_ATT(RMI_SEM_AVX2); break;
+    case RMI_SEM_NEON: RMI_ATT(RMI_SEM_NEON); break;
+    default: RMI_ATT(RMI_SEM_SCALAR); break;
+  }
+#undef RMI_ATT
+  return rmi_post_launch(ctx, "attention");
+}
+
+int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
+                      size_t n_gen, int* flag, size_t batch) {
+  argmax_kernel<<<(unsigned)batch, 1024, 0, ctx->stream>>>(logits, vocab, d_step, n_prompt, gen, n_gen, flag);
+  return rmi_post_launch(ctx, "argmax");
+}
+
+int32_t launch_step_inc(rmi_ctx* ctx, int* d_step) {
+  step_inc_kernel<<<1, 1, 0, ctx->stream>>>(d_step);
+  return rmi_post_launch(ctx, "step_inc");
+}

@@ -1,0 +1,24 @@
+// Launchers of the decode-step kernels (decode.cu), used by the session code (qwen3.cu).
+#pragma once
+#include "common.cuh"
+
+struct decode_dims {
+  size_t batch, capacity;
+  size_t n_embd, n_layer, n_head, n_head_kv, hd, n_ff, vocab;
+  float eps;
+};
+
+int32_t launch_embed(rmi_ctx* ctx, const rmi_weight* emb, const uint32_t* prompts, size_t n_prompt, const uint32_t* gen,
+                     size_t n_gen, const int* d_step, float* x, size_t batch);
+int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const float* weight, size_t n, float eps,
+                             uint8_t* q8, float* scales, size_t batch);
+int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
+                               const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
+                               uint16_t* k_cache, uint16_t* v_cache, size_t layer);
+size_t attention_smem_bytes(const decode_dims& d);
+int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
+                         const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                         float* scales);
+int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
+                      size_t n_gen, int* flag, size_t batch);
+int32_t launch_step_inc(rmi_ctx* ctx, int* d_step);

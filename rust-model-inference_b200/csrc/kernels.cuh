@@ -1,0 +1,46 @@
+// Launchers shared between translation units of librmi_cuda.so.
+#pragma once
+#include "common.cuh"
+
+// q8_0.cu
+int32_t launch_q8_repack_tile16(rmi_ctx* ctx, const uint8_t* raw, uint8_t* dst, size_t n_rows, size_t blocks);
+int32_t launch_q8_copy_rows_tile16(rmi_ctx* ctx, const uint8_t* src, uint8_t* dst, size_t n_rows, size_t blocks, size_t row_off);
+int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, float* us, size_t n_rows, size_t blocks);
+int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8, float* scales, int out_mode);
+int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
+                       float* out, size_t out_stride, size_t row_begin, size_t row_end);
+int32_t launch_q8_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, size_t m, int32_t* sums);
+int32_t launch_silu_mul_quantize(rmi_ctx* ctx, const float* gate, const float* up, size_t in_stride, size_t m,
+                                 size_t n_ff, float* act, uint8_t* q8, float* scales);
+
+// gemm_tc.cu (tcgen05 int8 MMA)
+enum { GEMM_EPI_F32 = 0, GEMM_EPI_SWIGLU_Q8 = 1, GEMM_EPI_BLOCK_SUMS = 2 };
+struct gemm_tc_args {
+  const uint8_t* a_img;  // activations, tcgen05 A images [m_tiles][slabs][16 KiB]
+  const float* a_scales; // [m_tiles][blocks][128]
+  const rmi_weight* w;   // umma layout must be built
+  size_t m;              // valid rows
+  size_t col_begin, col_end;  // weight rows (= output columns) to compute
+  int epilogue;
+  float* out;            // F32: [m][out_stride]
+  size_t out_stride;
+  // SWIGLU_Q8: gate rows [0,n_ff), up rows [n_ff,2n_ff) of w; writes the re-quantized
+  // activation as A images for the down projection plus its scales, and optionally f32 act
+  size_t n_ff;
+  uint8_t* act_img;
+  float* act_scales;
+  float* act_f32;
+  int32_t* sums;         // BLOCK_SUMS: [m][n_rows][blocks]
+};
+int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
+int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w);
+
+// q4k.cu
+int32_t launch_q8k_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, float* d, int8_t* qs, int16_t* bsums);
+int32_t launch_q4k_q8k_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* d8, const int8_t* qs, const int16_t* bsums,
+                              size_t m, float* out, size_t row_begin, size_t row_end);
+int32_t launch_q4k_dequant_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* out);
+int32_t launch_q4k_dequantize(rmi_ctx* ctx, const rmi_weight* w, float* out);
+
+// decode.cu
+int32_t launch_unshard_cols(rmi_ctx* ctx, const float* gathered, size_t g, size_t m, size_t npr, float* out);

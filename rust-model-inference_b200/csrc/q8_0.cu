@@ -1,0 +1,420 @@
+// Q8_0 hot path on CUDA cores: weight re-layout, activation quantizer, the memory-bound
+// GEMV family (1 <= M <= 8 activation rows per pass), exact block sums, SiLU*mul.
+//
+// Reference semantics reproduced bit for bit (paths inside the reference project):
+//   quantizer  src/ops/quant/q8_0.rs:49-71 (scalar) :75-165 (NEON) :176-230 (AVX2)
+//   GEMV       src/ops/kernel/q8_0/scalar.rs:31-58, neon.rs:49-73, avx2.rs:53-174
+//   hsum       src/ops/dot.rs:447-456
+#include "common.cuh"
+#include "kernels.cuh"
+
+// ---------------------------------------------------------------- weight re-layout
+
+// raw GGUF rows ([f16 d][32 x i8] blocks, row stride blocks*34) -> tile16 records.
+// One thread per (row, block); rows >= n_rows inside the last tile were zeroed by memset.
+__global__ void q8_repack_tile16_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ dst,
+                                        size_t n_rows, size_t blocks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * blocks) return;
+  size_t row = idx / blocks, b = idx % blocks;
+  const uint8_t* src = raw + (row * blocks + b) * 34;
+  uint8_t* rec = dst + ((row / 16) * blocks + b) * Q8_REC_BYTES;
+  size_t r = row % 16;
+  rec[2 * r] = src[0];
+  rec[2 * r + 1] = src[1];
+  uint8_t* q = rec + 32 + 32 * r;
+#pragma unroll
+  for (int i = 0; i < 32; i++) q[i] = src[2 + i];
+}
+
+// tile16 rows of `src` appended after `row_off` rows of dst (v-stack); row_off % 16 may be != 0.
+__global__ void q8_copy_rows_tile16_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                           size_t n_rows, size_t blocks, size_t row_off) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * blocks) return;
+  size_t row = idx / blocks, b = idx % blocks;
+  const uint8_t* srec = src + ((row / 16) * blocks + b) * Q8_REC_BYTES;
+  size_t drow = row + row_off;
+  uint8_t* drec = dst + ((drow / 16) * blocks + b) * Q8_REC_BYTES;
+  size_t rs = row % 16, rd = drow % 16;
+  *reinterpret_cast<uint16_t*>(drec + 2 * rd) = *reinterpret_cast<const uint16_t*>(srec + 2 * rs);
+  const int4* s = reinterpret_cast<const int4*>(srec + 32 + 32 * rs);
+  int4* d = reinterpret_cast<int4*>(drec + 32 + 32 * rd);
+  d[0] = s[0];
+  d[1] = s[1];
+}
+
+// tile16 -> tcgen05 K-major core-matrix images + f32 scales [tile128][block][128].
+__global__ void q8_build_umma_kernel(const uint8_t* __restrict__ t16, uint8_t* __restrict__ uq,
+                                     float* __restrict__ us, size_t n_rows, size_t blocks,
+                                     size_t n_slabs) {
+  // one thread per (row, 16-byte chunk)
+  size_t chunks = blocks * 2;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t rows_pad = (n_rows + 127) / 128 * 128;
+  if (idx >= rows_pad * n_slabs * 8) return;
+  size_t row = idx / (n_slabs * 8), c_all = idx % (n_slabs * 8);
+  size_t slab = c_all / 8, c = c_all % 8;
+  int4 v = make_int4(0, 0, 0, 0);
+  size_t b = c_all / 2;
+  float s = 0.0f;
+  if (row < n_rows && c_all < chunks) {
+    const uint8_t* rec = t16 + ((row / 16) * blocks + b) * Q8_REC_BYTES;
+    v = *reinterpret_cast<const int4*>(rec + 32 + 32 * (row % 16) + 16 * (c_all & 1));
+    s = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(rec + 2 * (row % 16)));
+  }
+  size_t tile = row / 128, r = row % 128;
+  uint8_t* img = uq + (tile * n_slabs + slab) * 16384;
+  *reinterpret_cast<int4*>(img + (r / 8) * 1024 + c * 128 + (r % 8) * 16) = v;
+  if ((c_all & 1) == 0 && b < blocks) us[(tile * blocks + b) * 128 + r] = s;
+}
+
+// ---------------------------------------------------------------- activation quantizer
+
+// One warp per 32-block.  out_mode 0: q8 row-major [m][n], scales [m][n/32].
+// out_mode 1: q8 in tcgen05 A-operand images ([tile128][slab][16 KiB]) and scales
+// [tile128][block][128]; rows m..pad are written as zeros by the caller's memset.
+template <int SEM>
+__global__ void q8_quantize_kernel(const float* __restrict__ x, size_t m, size_t n,
+                                   uint8_t* __restrict__ q8, float* __restrict__ scales,
+                                   int out_mode) {
+  size_t blocks = n / 32;
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  int lane = threadIdx.x & 31;
+  if (warp >= m * blocks) return;
+  size_t row = warp / blocks, b = warp % blocks;
+  float v = x[row * n + b * 32 + lane];
+  float a = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  float d, inv;
+  q8_scale_pair<SEM>(a, &d, &inv);
+  int q = q8_quant_value<SEM>(v, inv);
+  float sc = f16_round_trip(d);
+  if (out_mode == 0) {
+    q8[row * n + b * 32 + lane] = (uint8_t)(int8_t)q;
+    if (lane == 0) scales[row * blocks + b] = sc;
+  } else {
+    size_t n_slabs = (n + 127) / 128;
+    size_t tile = row / 128, r = row % 128, k = b * 32 + lane;
+    size_t slab = k / 128, c = (k % 128) / 16, byte = k % 16;
+    q8[(tile * n_slabs + slab) * 16384 + (r / 8) * 1024 + c * 128 + (r % 8) * 16 + byte] =
+        (uint8_t)(int8_t)q;
+    if (lane == 0) scales[(tile * blocks + b) * 128 + r] = sc;
+  }
+}
+
+// ---------------------------------------------------------------- GEMV
+
+// LB bytes of each row's 32-byte block per lane; a warp covers LB rows of one 16-row tile.
+// MP activation rows are processed per pass with the weights read once.
+template <int SEM, int LB, int MP>
+__global__ void __launch_bounds__(256)
+    q8_gemv_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
+                   const float* __restrict__ xs, float* __restrict__ out, size_t out_stride,
+                   size_t row_begin, size_t row_end, size_t first_tile) {
+  constexpr int LPR = 32 / LB;      // lanes per row
+  constexpr int NL = LB / 4;        // AVX2 lanes (dp4a groups) per thread
+  constexpr int WPT = 16 / LB;      // warps per 16-row tile
+  constexpr int U = LB == 16 ? 4 : 8;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const size_t K = blocks * 32;
+  int8_t* xq_s = reinterpret_cast<int8_t*>(smem);
+  float* xs_s = reinterpret_cast<float*>(smem + MP * K);
+
+  // stage the quantized activations (shared by every row)
+  {
+    const int4* src = reinterpret_cast<const int4*>(xq);
+    int4* dst = reinterpret_cast<int4*>(xq_s);
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = src[i];
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = xs[i];
+  }
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const size_t gw = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const size_t tile = first_tile + gw / WPT;
+  const int sub = (int)(gw % WPT);
+  const int rit = sub * LB + lane / LPR;  // row in tile
+  const int part = lane % LPR;
+  const size_t row = tile * 16 + rit;
+  if (tile * 16 >= row_end) return;  // whole warp out of range (uniform)
+
+  const uint8_t* rec0 = w + tile * blocks * Q8_REC_BYTES;
+  const uint8_t* qp = rec0 + 32 + rit * 32 + part * LB;
+  const uint8_t* sp = rec0 + 2 * rit;
+
+  float acc[MP][SEM == RMI_SEM_AVX2 ? NL : 1];
+#pragma unroll
+  for (int m = 0; m < MP; m++)
+#pragma unroll
+    for (int j = 0; j < (SEM == RMI_SEM_AVX2 ? NL : 1); j++) acc[m][j] = 0.0f;
+
+  for (size_t b0 = 0; b0 < blocks; b0 += U) {
+    int wq[U][NL];
+    uint16_t wd_bits[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      if (b0 + u < blocks) {
+        const uint8_t* p = qp + (b0 + u) * Q8_REC_BYTES;
+        if (LB == 16) {
+          int4 v = __ldg(reinterpret_cast<const int4*>(p));
+          wq[u][0] = v.x; wq[u][NL > 1 ? 1 : 0] = v.y; wq[u][NL > 2 ? 2 : 0] = v.z; wq[u][NL > 3 ? 3 : 0] = v.w;
+        } else if (LB == 8) {
+          int2 v = __ldg(reinterpret_cast<const int2*>(p));
+          wq[u][0] = v.x; wq[u][NL > 1 ? 1 : 0] = v.y;
+        } else {
+          wq[u][0] = __ldg(reinterpret_cast<const int*>(p));
+        }
+        wd_bits[u] = __ldg(reinterpret_cast<const uint16_t*>(sp + (b0 + u) * Q8_REC_BYTES));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      if (b0 + u < blocks) {
+        const size_t b = b0 + u;
+        const float wd = f16_bits_to_f32(wd_bits[u]);
+#pragma unroll
+        for (int m = 0; m < MP; m++) {
+          const int* xp = reinterpret_cast<const int*>(xq_s + m * K + b * 32 + part * LB);
+          const float da = __fmul_rn(wd, xs_s[m * blocks + b]);
+          if (SEM == RMI_SEM_AVX2) {
+            // avx2.rs:96-148: eight partial sums of four products, one FMA each
+#pragma unroll
+            for (int j = 0; j < NL; j++) {
+              int p = dp4a_s8(wq[u][j], xp[j], 0x4B400000);
+              float f = __fsub_rn(__int_as_float(p), 12582912.0f);
+              acc[m][j] = __fmaf_rn(da, f, acc[m][j]);
+            }
+          } else {
+            int dot = 0;
+#pragma unroll
+            for (int j = 0; j < NL; j++) dot = dp4a_s8(wq[u][j], xp[j], dot);
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            float f = small_int_to_f32(dot);
+            if (SEM == RMI_SEM_NEON) {
+              acc[m][0] = __fmaf_rn(f, da, acc[m][0]);  // neon.rs:69
+            } else {
+              acc[m][0] = __fadd_rn(acc[m][0], __fmul_rn(da, f));  // scalar.rs:55
+            }
+          }
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int m = 0; m < MP; m++) {
+    float r;
+    if (SEM == RMI_SEM_AVX2) {
+      // dot.rs:447-456: s_i = a[i+4] + a[i]; (s0 + s1) + (s2 + s3)
+      if (LB == 16) {
+        float s[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          s[j] = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc[m][j % NL], 1), acc[m][j % NL]);
+        r = __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3]));
+      } else if (LB == 8) {
+        float s0 = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc[m][0], 2), acc[m][0]);
+        float s1 = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc[m][NL > 1 ? 1 : 0], 2), acc[m][NL > 1 ? 1 : 0]);
+        float t = __fadd_rn(s0, s1);  // part 0: s0+s1, part 1: s2+s3
+        float o = __shfl_xor_sync(0xffffffffu, t, 1);
+        r = __fadd_rn(t, o);          // part 0: (s0+s1)+(s2+s3)
+      } else {
+        float s = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc[m][0], 4), acc[m][0]);  // parts 0..3: s_part
+        float t = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));                  // part 0: s0+s1, part 2: s2+s3
+        r = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));                        // part 0: final
+      }
+    } else {
+      r = acc[m][0];
+    }
+    if (part == 0 && row >= row_begin && row < row_end) out[m * out_stride + row] = r;
+  }
+}
+
+// ---------------------------------------------------------------- exact block sums
+
+__global__ void q8_block_sums_kernel(const uint8_t* __restrict__ w, size_t blocks, size_t n_rows,
+                                     const uint8_t* __restrict__ xq, size_t m,
+                                     int32_t* __restrict__ sums) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= m * n_rows * blocks) return;
+  size_t b = idx % blocks, row = (idx / blocks) % n_rows, t = idx / (blocks * n_rows);
+  const int* wp = reinterpret_cast<const int*>(w + ((row / 16) * blocks + b) * Q8_REC_BYTES + 32 + 32 * (row % 16));
+  const int* xp = reinterpret_cast<const int*>(xq + t * blocks * 32 + b * 32);
+  int dot = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) dot = dp4a_s8(wp[j], xp[j], dot);
+  sums[idx] = dot;
+}
+
+// ---------------------------------------------------------------- SiLU * mul (+ quantize)
+
+// gate_up [m][2*n_ff] (gate columns first, then up).  act = up * (g / (1 + exp(-g)))
+// (src/ops/activation/mod.rs:137-151), optionally written as f32 and/or re-quantized.
+// One warp per 32-block of n_ff.
+template <int SEM>
+__global__ void silu_mul_quantize_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                         size_t in_stride, size_t m, size_t n_ff,
+                                         float* __restrict__ act, uint8_t* __restrict__ q8,
+                                         float* __restrict__ scales) {
+  size_t blocks = n_ff / 32;
+  size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
+  int lane = threadIdx.x & 31;
+  if (warp >= m * blocks) return;
+  size_t row = warp / blocks, b = warp % blocks;
+  float g = gate[row * in_stride + b * 32 + lane];
+  float u = up[row * in_stride + b * 32 + lane];
+  float s = __fdiv_rn(g, __fadd_rn(1.0f, exp_cr(-g)));
+  float v = __fmul_rn(u, s);
+  if (act) act[row * n_ff + b * 32 + lane] = v;
+  if (q8) {
+    float a = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    float d, inv;
+    q8_scale_pair<SEM>(a, &d, &inv);
+    q8[row * n_ff + b * 32 + lane] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
+    if (lane == 0) scales[row * blocks + b] = f16_round_trip(d);
+  }
+}
+
+// ---------------------------------------------------------------- host launchers
+
+int32_t launch_q8_repack_tile16(rmi_ctx* ctx, const uint8_t* raw, uint8_t* dst, size_t n_rows,
+                                size_t blocks) {
+  size_t n = n_rows * blocks;
+  if (n == 0) return RMI_OK;
+  q8_repack_tile16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(raw, dst, n_rows, blocks);
+  return rmi_post_launch(ctx, "q8_repack_tile16");
+}
+
+int32_t launch_q8_copy_rows_tile16(rmi_ctx* ctx, const uint8_t* src, uint8_t* dst, size_t n_rows,
+                                   size_t blocks, size_t row_off) {
+  size_t n = n_rows * blocks;
+  if (n == 0) return RMI_OK;
+  q8_copy_rows_tile16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(src, dst, n_rows, blocks, row_off);
+  return rmi_post_launch(ctx, "q8_copy_rows_tile16");
+}
+
+int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, float* us, size_t n_rows,
+                             size_t blocks) {
+  size_t n_slabs = (blocks * 32 + 127) / 128;
+  size_t rows_pad = (n_rows + 127) / 128 * 128;
+  size_t n = rows_pad * n_slabs * 8;
+  if (n == 0) return RMI_OK;
+  q8_build_umma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(t16, uq, us, n_rows, blocks, n_slabs);
+  return rmi_post_launch(ctx, "q8_build_umma");
+}
+
+int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8, float* scales,
+                           int out_mode) {
+  size_t warps = m * (n / 32);
+  if (warps == 0) return RMI_OK;
+  unsigned grid = (unsigned)((warps + 7) / 8);
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: q8_quantize_kernel<RMI_SEM_AVX2><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
+    case RMI_SEM_NEON: q8_quantize_kernel<RMI_SEM_NEON><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
+    default: q8_quantize_kernel<RMI_SEM_SCALAR><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
+  }
+  return rmi_post_launch(ctx, "q8_quantize");
+}
+
+template <int SEM, int LB, int MP>
+static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
+                               float* out, size_t out_stride, size_t row_begin, size_t row_end) {
+  const size_t blocks = w->n_in / 32;
+  const size_t first_tile = row_begin / 16;
+  const size_t last_tile = (row_end + 15) / 16;
+  const size_t warps = (last_tile - first_tile) * (16 / LB);
+  const size_t smem = (size_t)MP * w->n_in + (size_t)MP * blocks * 4;
+  auto kern = q8_gemv_kernel<SEM, LB, MP>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed: %s", smem, cudaGetErrorString(e));
+      return RMI_ERR_CUDA;
+    }
+  }
+  // fewer warps per CTA when the problem is small so that more SMs take part
+  int wpc = warps >= (size_t)ctx->sm_count * 16 ? 8 : (warps >= (size_t)ctx->sm_count * 4 ? 4 : 2);
+  unsigned grid = (unsigned)((warps + wpc - 1) / wpc);
+  kern<<<grid, wpc * 32, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin,
+                                              row_end, first_tile);
+  return rmi_post_launch(ctx, "q8_gemv");
+}
+
+template <int SEM, int LB>
+static int32_t gemv_dispatch_mp(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
+                                size_t m, float* out, size_t out_stride, size_t row_begin,
+                                size_t row_end) {
+  const size_t blocks = w->n_in / 32;
+  size_t t = 0;
+  // largest pass whose staged activations fit in shared memory
+  size_t max_mp = 8;
+  while (max_mp > 1 && max_mp * (w->n_in + blocks * 4) > ctx->smem_optin - 1024) max_mp >>= 1;
+  RMI_REQUIRE(w->n_in + blocks * 4 <= ctx->smem_optin - 1024, RMI_ERR_UNSUPPORTED,
+              "n_in=%zu does not fit the GEMV activation staging buffer", w->n_in);
+  while (t < m) {
+    size_t left = m - t;
+    size_t mp = left >= 8 ? 8 : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
+    if (mp > max_mp) mp = max_mp;
+    const uint8_t* q = xq + t * w->n_in;
+    const float* s = xs + t * blocks;
+    float* o = out + t * out_stride;
+    int32_t st;
+    switch (mp) {
+      case 8: st = gemv_launch_one<SEM, LB, 8>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
+      case 4: st = gemv_launch_one<SEM, LB, 4>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
+      case 2: st = gemv_launch_one<SEM, LB, 2>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
+      default: st = gemv_launch_one<SEM, LB, 1>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
+    }
+    if (st != RMI_OK) return st;
+    t += mp;
+  }
+  return RMI_OK;
+}
+
+template <int SEM>
+static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
+                                size_t m, float* out, size_t out_stride, size_t row_begin,
+                                size_t row_end) {
+  const size_t tiles = (row_end + 15) / 16 - row_begin / 16;
+  const size_t want = (size_t)ctx->sm_count * 16;  // warps that keep every SM streaming
+  if (tiles >= want) return gemv_dispatch_mp<SEM, 16>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+  if (tiles * 2 >= want) return gemv_dispatch_mp<SEM, 8>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+  return gemv_dispatch_mp<SEM, 4>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+}
+
+int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
+                       float* out, size_t out_stride, size_t row_begin, size_t row_end) {
+  if (row_begin >= row_end || m == 0) return RMI_OK;
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: return gemv_dispatch_lb<RMI_SEM_AVX2>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+    case RMI_SEM_NEON: return gemv_dispatch_lb<RMI_SEM_NEON>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+    default: return gemv_dispatch_lb<RMI_SEM_SCALAR>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+  }
+}
+
+int32_t launch_q8_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, size_t m,
+                             int32_t* sums) {
+  size_t n = m * w->n_rows * (w->n_in / 32);
+  if (n == 0) return RMI_OK;
+  q8_block_sums_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(w->d_tile16, w->n_in / 32,
+                                                                            w->n_rows, xq, m, sums);
+  return rmi_post_launch(ctx, "q8_block_sums");
+}
+
+int32_t launch_silu_mul_quantize(rmi_ctx* ctx, const float* gate, const float* up, size_t in_stride,
+                                 size_t m, size_t n_ff, float* act, uint8_t* q8, float* scales) {
+  size_t warps = m * (n_ff / 32);
+  if (warps == 0) return RMI_OK;
+  unsigned grid = (unsigned)((warps + 7) / 8);
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: silu_mul_quantize_kernel<RMI_SEM_AVX2><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
+    case RMI_SEM_NEON: silu_mul_quantize_kernel<RMI_SEM_NEON><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
+    default: silu_mul_quantize_kernel<RMI_SEM_SCALAR><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
+  }
+  return rmi_post_launch(ctx, "silu_mul_quantize");
+}

@@ -1,0 +1,522 @@
+// Qwen3-architecture model and decode session on the device.
+//
+// Restates Qwen3Model::from_source (src/models/qwen3.rs:246-400) and
+// Qwen3Session::{new, generate_inner} (src/models/qwen3.rs:440-550, :581-1158) of the
+// reference for `batch` independent sequences.  One decode step is a fixed sequence of
+// kernels captured once into a CUDA graph; the position lives in device memory and is
+// advanced by the last node, so the same graph is replayed for every step.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "decode.cuh"
+#include "kernels.cuh"
+
+static constexpr uint32_t RMI_MODEL_MAGIC = 0x524d494d;
+static constexpr uint32_t RMI_SESSION_MAGIC = 0x524d4953;
+
+struct layer_weights {
+  float *attn_norm, *ffn_norm, *q_norm, *k_norm;
+  rmi_weight *wqkv, *wo, *wgu, *wdown;
+};
+
+struct rmi_qwen3 {
+  uint32_t magic;
+  decode_dims d;  // batch / capacity unused here
+  float freq_base;
+  size_t n_ctx;
+  std::vector<layer_weights> layers;
+  float* output_norm;
+  rmi_weight* token_embd;
+  rmi_weight* output;  // == token_embd when tied
+  size_t weight_bytes;
+};
+
+struct rmi_session {
+  uint32_t magic;
+  const rmi_qwen3* model;
+  decode_dims d;
+  uint16_t *k_cache, *v_cache;
+  float *x, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;
+  uint16_t* q16;
+  uint8_t* q8;
+  float* xs;
+  uint32_t *prompts, *gen;
+  size_t prompts_cap, gen_cap;
+  int *d_step, *d_flag;
+  cudaGraph_t graph_body, graph_full;
+  cudaGraphExec_t exec_body, exec_full;
+  size_t graph_n_prompt, graph_n_gen;
+  int graph_sem;
+  cudaStream_t graph_stream;
+};
+
+static int32_t check_model(const rmi_qwen3* m) {
+  RMI_REQUIRE(m != nullptr && m->magic == RMI_MODEL_MAGIC, RMI_ERR_BAD_HANDLE, "invalid rmi_qwen3 handle");
+  return RMI_OK;
+}
+static int32_t check_session(const rmi_session* s) {
+  RMI_REQUIRE(s != nullptr && s->magic == RMI_SESSION_MAGIC, RMI_ERR_BAD_HANDLE, "invalid rmi_session handle");
+  return RMI_OK;
+}
+
+// load_f32_tensor (src/models/qwen3.rs:1338-1348) + checked_tensor (:1350-1380)
+static int32_t load_f32(rmi_ctx* ctx, const rmi_gguf* g, const std::string& name, size_t n, float** out) {
+  int32_t type, nd;
+  uint64_t dims[4];
+  const void* data;
+  size_t nbytes;
+  RMI_TRY(rmi_gguf_tensor(g, name.c_str(), &type, dims, &nd, &data, &nbytes));
+  RMI_REQUIRE(type == RMI_GGML_F32 && nd == 1 && dims[0] == n, RMI_ERR_FORMAT,
+              "Invalid tensor %s: expected F32 [%zu]", name.c_str(), n);
+  RMI_CUDA_CHECK(cudaMalloc(out, n * 4));
+  RMI_CUDA_CHECK(cudaMemcpy(*out, data, n * 4, cudaMemcpyHostToDevice));
+  return RMI_OK;
+}
+
+static int32_t load_q8(rmi_ctx* ctx, const rmi_gguf* g, const std::string& name, size_t n_in, size_t n_out,
+                       rmi_weight** out) {
+  int32_t type, nd;
+  uint64_t dims[4];
+  RMI_TRY(rmi_gguf_tensor(g, name.c_str(), &type, dims, &nd, nullptr, nullptr));
+  RMI_REQUIRE(type == RMI_GGML_Q8_0 && nd == 2 && dims[0] == n_in && dims[1] == n_out, RMI_ERR_FORMAT,
+              "Invalid tensor %s: shape [%llu,%llu] type %d; expected [%zu,%zu] Q8_0", name.c_str(),
+              (unsigned long long)dims[0], (unsigned long long)(nd > 1 ? dims[1] : 0), type, n_in, n_out);
+  return rmi_weight_upload_gguf(ctx, g, name.c_str(), 0, (size_t)-1, out);
+}
+
+static void free_model(rmi_ctx* ctx, rmi_qwen3* m) {
+  if (!m) return;
+  for (auto& l : m->layers) {
+    cudaFree(l.attn_norm); cudaFree(l.ffn_norm); cudaFree(l.q_norm); cudaFree(l.k_norm);
+    if (l.wqkv) rmi_weight_free(ctx, l.wqkv);
+    if (l.wo) rmi_weight_free(ctx, l.wo);
+    if (l.wgu) rmi_weight_free(ctx, l.wgu);
+    if (l.wdown) rmi_weight_free(ctx, l.wdown);
+  }
+  cudaFree(m->output_norm);
+  if (m->output && m->output != m->token_embd) rmi_weight_free(ctx, m->output);
+  if (m->token_embd) rmi_weight_free(ctx, m->token_embd);
+  m->magic = 0;
+  delete m;
+}
+
+static size_t wbytes(const rmi_weight* w) {
+  size_t b = 0;
+  rmi_weight_info(w, nullptr, nullptr, nullptr, &b);
+  return b;
+}
+
+static int32_t load_model(rmi_ctx* ctx, const rmi_gguf* g, rmi_qwen3* m) {
+  char arch[64];
+  RMI_TRY(rmi_gguf_meta_str(g, "general.architecture", arch, sizeof(arch)));
+  RMI_REQUIRE(strcmp(arch, "qwen3") == 0, RMI_ERR_UNSUPPORTED, "Unsupported architecture: %s (this path handles qwen3)", arch);
+  auto u = [&](const char* key, size_t* v) -> int32_t {
+    uint64_t t;
+    RMI_TRY(rmi_gguf_meta_u64(g, (std::string("qwen3.") + key).c_str(), &t));
+    *v = (size_t)t;
+    return RMI_OK;
+  };
+  decode_dims& d = m->d;
+  RMI_TRY(u("embedding_length", &d.n_embd));
+  RMI_TRY(u("block_count", &d.n_layer));
+  RMI_TRY(u("attention.head_count", &d.n_head));
+  RMI_TRY(u("attention.head_count_kv", &d.n_head_kv));
+  RMI_TRY(u("feed_forward_length", &d.n_ff));
+  RMI_TRY(u("context_length", &m->n_ctx));
+  RMI_REQUIRE(d.n_head > 0 && d.n_embd % d.n_head == 0, RMI_ERR_FORMAT, "Invalid qwen3 head shape");
+  uint64_t t;
+  d.hd = d.n_embd / d.n_head;
+  if (rmi_gguf_meta_u64(g, "qwen3.attention.key_length", &t) == RMI_OK) d.hd = (size_t)t;
+  if (rmi_gguf_meta_u64(g, "qwen3.attention.value_length", &t) == RMI_OK)
+    RMI_REQUIRE((size_t)t == d.hd, RMI_ERR_UNSUPPORTED, "key_length != value_length is not handled");
+  RMI_REQUIRE(d.n_head_kv > 0 && d.n_head % d.n_head_kv == 0 && d.hd % 2 == 0 && d.hd > 0, RMI_ERR_FORMAT,
+              "Invalid qwen3 attention shape");
+  double f;
+  m->freq_base = 1000000.0f;
+  if (rmi_gguf_meta_f64(g, "qwen3.rope.freq_base", &f) == RMI_OK) m->freq_base = (float)f;
+  RMI_TRY(rmi_gguf_meta_f64(g, "qwen3.attention.layer_norm_rms_epsilon", &f));
+  d.eps = (float)f;
+  {
+    int32_t type, nd;
+    uint64_t dims[4];
+    RMI_TRY(rmi_gguf_tensor(g, "token_embd.weight", &type, dims, &nd, nullptr, nullptr));
+    RMI_REQUIRE(nd == 2 && dims[0] == d.n_embd, RMI_ERR_FORMAT, "Invalid tensor token_embd.weight");
+    d.vocab = (size_t)dims[1];
+    if (rmi_gguf_meta_u64(g, "qwen3.vocab_size", &t) == RMI_OK)
+      RMI_REQUIRE((size_t)t == d.vocab, RMI_ERR_FORMAT, "qwen3.vocab_size does not match token_embd.weight");
+  }
+  const size_t nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
+  RMI_REQUIRE(d.n_embd % 32 == 0 && nq % 32 == 0 && nk % 32 == 0 && d.n_ff % 32 == 0, RMI_ERR_BAD_SHAPE,
+              "Q8_0 needs every matmul width to be a multiple of 32");
+  RMI_TRY(load_f32(ctx, g, "output_norm.weight", d.n_embd, &m->output_norm));
+  RMI_TRY(load_q8(ctx, g, "token_embd.weight", d.n_embd, d.vocab, &m->token_embd));
+  m->weight_bytes += wbytes(m->token_embd);
+  m->output = m->token_embd;
+  if (rmi_gguf_tensor(g, "output.weight", nullptr, nullptr, nullptr, nullptr, nullptr) == RMI_OK) {
+    RMI_TRY(load_q8(ctx, g, "output.weight", d.n_embd, d.vocab, &m->output));
+    m->weight_bytes += wbytes(m->output);
+  }
+  m->layers.resize(d.n_layer);
+  for (auto& l : m->layers) memset(&l, 0, sizeof(l));
+  for (size_t i = 0; i < d.n_layer; i++) {
+    layer_weights& l = m->layers[i];
+    const std::string p = "blk." + std::to_string(i) + ".";
+    RMI_TRY(load_f32(ctx, g, p + "attn_norm.weight", d.n_embd, &l.attn_norm));
+    RMI_TRY(load_f32(ctx, g, p + "ffn_norm.weight", d.n_embd, &l.ffn_norm));
+    // has_qk_norm for "qwen3" (src/core/loader.rs:556)
+    RMI_TRY(load_f32(ctx, g, p + "attn_q_norm.weight", d.hd, &l.q_norm));
+    RMI_TRY(load_f32(ctx, g, p + "attn_k_norm.weight", d.hd, &l.k_norm));
+    rmi_weight *wq = nullptr, *wk = nullptr, *wv = nullptr, *wqk = nullptr, *wg = nullptr, *wu = nullptr;
+    int32_t st = load_q8(ctx, g, p + "attn_q.weight", d.n_embd, nq, &wq);
+    if (st == RMI_OK) st = load_q8(ctx, g, p + "attn_k.weight", d.n_embd, nk, &wk);
+    if (st == RMI_OK) st = load_q8(ctx, g, p + "attn_v.weight", d.n_embd, nk, &wv);
+    // q, k and v share the activation: one v-stacked weight, one GEMV (fuse.rs:1-8)
+    if (st == RMI_OK) st = rmi_weight_fuse_vstack(ctx, wq, wk, &wqk);
+    if (st == RMI_OK) st = rmi_weight_fuse_vstack(ctx, wqk, wv, &l.wqkv);
+    if (wq) rmi_weight_free(ctx, wq);
+    if (wk) rmi_weight_free(ctx, wk);
+    if (wv) rmi_weight_free(ctx, wv);
+    if (wqk) rmi_weight_free(ctx, wqk);
+    RMI_TRY(st);
+    RMI_TRY(load_q8(ctx, g, p + "attn_output.weight", nq, d.n_embd, &l.wo));
+    st = load_q8(ctx, g, p + "ffn_gate.weight", d.n_embd, d.n_ff, &wg);
+    if (st == RMI_OK) st = load_q8(ctx, g, p + "ffn_up.weight", d.n_embd, d.n_ff, &wu);
+    if (st == RMI_OK) st = rmi_weight_fuse_vstack(ctx, wg, wu, &l.wgu);
+    if (wg) rmi_weight_free(ctx, wg);
+    if (wu) rmi_weight_free(ctx, wu);
+    RMI_TRY(st);
+    RMI_TRY(load_q8(ctx, g, p + "ffn_down.weight", d.n_ff, d.n_embd, &l.wdown));
+    m->weight_bytes += wbytes(l.wqkv) + wbytes(l.wo) + wbytes(l.wgu) + wbytes(l.wdown);
+  }
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_qwen3_load(rmi_ctx* ctx, const char* gguf_path, rmi_qwen3** out) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_REQUIRE(out && gguf_path, RMI_ERR_BAD_HANDLE, "rmi_qwen3_load: null argument");
+  *out = nullptr;
+  rmi_gguf* g = nullptr;
+  RMI_TRY(rmi_gguf_open(gguf_path, &g));
+  rmi_qwen3* m = new (std::nothrow) rmi_qwen3();
+  if (!m) {
+    rmi_gguf_close(g);
+    rmi_set_error("host allocation failed");
+    return RMI_ERR_OOM;
+  }
+  m->magic = RMI_MODEL_MAGIC;
+  m->output_norm = nullptr;
+  m->token_embd = m->output = nullptr;
+  m->weight_bytes = 0;
+  memset(&m->d, 0, sizeof(m->d));
+  int32_t st = load_model(ctx, g, m);
+  std::string err = rmi_last_error();
+  rmi_gguf_close(g);
+  if (st != RMI_OK) {
+    free_model(ctx, m);
+    rmi_set_error("%s", err.c_str());
+    return st;
+  }
+  *out = m;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_qwen3_free(rmi_ctx* ctx, rmi_qwen3* model) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_model(model));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  free_model(ctx, model);
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_qwen3_config(const rmi_qwen3* m, size_t* n_embd, size_t* n_layer, size_t* n_head,
+                                    size_t* n_head_kv, size_t* head_dim, size_t* n_ff, size_t* vocab) {
+  RMI_TRY(check_model(m));
+  if (n_embd) *n_embd = m->d.n_embd;
+  if (n_layer) *n_layer = m->d.n_layer;
+  if (n_head) *n_head = m->d.n_head;
+  if (n_head_kv) *n_head_kv = m->d.n_head_kv;
+  if (head_dim) *head_dim = m->d.hd;
+  if (n_ff) *n_ff = m->d.n_ff;
+  if (vocab) *vocab = m->d.vocab;
+  return RMI_OK;
+}
+
+// ---------------------------------------------------------------- session
+
+static void drop_graphs(rmi_session* s) {
+  if (s->exec_body) cudaGraphExecDestroy(s->exec_body);
+  if (s->exec_full) cudaGraphExecDestroy(s->exec_full);
+  if (s->graph_body) cudaGraphDestroy(s->graph_body);
+  if (s->graph_full) cudaGraphDestroy(s->graph_full);
+  s->exec_body = s->exec_full = nullptr;
+  s->graph_body = s->graph_full = nullptr;
+}
+
+static void free_session(rmi_session* s) {
+  if (!s) return;
+  drop_graphs(s);
+  cudaFree(s->k_cache); cudaFree(s->v_cache); cudaFree(s->x); cudaFree(s->qkv); cudaFree(s->proj);
+  cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8);
+  cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
+  cudaFree(s->attn_dbg);
+  s->magic = 0;
+  delete s;
+}
+
+extern "C" int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  free_session(s);
+  return RMI_OK;
+}
+
+#define SESSION_ALLOC(ptr, bytes)                                                             \
+  do {                                                                                        \
+    cudaError_t _e = cudaMalloc((void**)&(ptr), (bytes) ? (bytes) : 16);                      \
+    if (_e != cudaSuccess) {                                                                  \
+      (void)cudaGetLastError();                                                               \
+      rmi_set_error("session allocation of %zu bytes failed: %s", (size_t)(bytes), cudaGetErrorString(_e)); \
+      free_session(s);                                                                        \
+      return RMI_ERR_OOM;                                                                     \
+    }                                                                                         \
+  } while (0)
+
+extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size_t batch, size_t capacity,
+                                      rmi_session** out) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_model(model));
+  RMI_REQUIRE(out != nullptr, RMI_ERR_BAD_HANDLE, "rmi_session_create: out is null");
+  *out = nullptr;
+  // src/models/qwen3.rs:442-447
+  RMI_REQUIRE(capacity > 0 && capacity <= model->n_ctx, RMI_ERR_BAD_SHAPE,
+              "Session capacity %zu must be within 1..=%zu", capacity, model->n_ctx);
+  RMI_REQUIRE(batch > 0 && batch <= 65535, RMI_ERR_BAD_SHAPE, "batch %zu out of range", batch);
+  rmi_session* s = new (std::nothrow) rmi_session();
+  RMI_REQUIRE(s != nullptr, RMI_ERR_OOM, "host allocation failed");
+  memset(s, 0, sizeof(*s));
+  s->magic = RMI_SESSION_MAGIC;
+  s->model = model;
+  s->d = model->d;
+  s->d.batch = batch;
+  s->d.capacity = capacity;
+  const decode_dims& d = s->d;
+  if (attention_smem_bytes(d) > ctx->smem_optin) {
+    rmi_set_error("capacity %zu needs %zu B of shared memory per attention CTA (limit %zu)", capacity,
+                  attention_smem_bytes(d), ctx->smem_optin);
+    free_session(s);
+    return RMI_ERR_UNSUPPORTED;
+  }
+  const size_t nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
+  const size_t max_n_in = nq > d.n_ff ? (nq > d.n_embd ? nq : d.n_embd) : (d.n_ff > d.n_embd ? d.n_ff : d.n_embd);
+  const size_t kv = batch * d.n_layer * capacity * nk * 2;
+  SESSION_ALLOC(s->k_cache, kv);
+  SESSION_ALLOC(s->v_cache, kv);
+  SESSION_ALLOC(s->x, batch * d.n_embd * 4);
+  SESSION_ALLOC(s->qkv, batch * (nq + 2 * nk) * 4);
+  SESSION_ALLOC(s->proj, batch * d.n_embd * 4);
+  SESSION_ALLOC(s->gu, batch * 2 * d.n_ff * 4);
+  SESSION_ALLOC(s->logits, batch * d.vocab * 4);
+  SESSION_ALLOC(s->rope, capacity * d.hd * 4);
+  SESSION_ALLOC(s->q16, batch * nq * 2);
+  SESSION_ALLOC(s->q8, batch * max_n_in);
+  SESSION_ALLOC(s->xs, batch * (max_n_in / 32) * 4);
+  SESSION_ALLOC(s->d_step, 4);
+  SESSION_ALLOC(s->d_flag, 4);
+  SESSION_ALLOC(s->attn_dbg, batch * nq * 4);
+  cudaMemset(s->k_cache, 0, kv);
+  cudaMemset(s->v_cache, 0, kv);
+  // rope_neox (src/ops/rope.rs:21-37): theta_0 = pos, theta_{i+1} = theta_i * base^(-2/d) in f32,
+  // cos/sin from this host's libm so that the table equals what the CPU path evaluates.
+  {
+    std::vector<float> tab(capacity * d.hd);
+    const float theta_scale = powf(model->freq_base, -2.0f / (float)d.hd);
+    for (size_t pos = 0; pos < capacity; pos++) {
+      float theta = (float)pos;
+      for (size_t i = 0; i < d.hd / 2; i++) {
+        tab[pos * d.hd + 2 * i] = cosf(theta);
+        tab[pos * d.hd + 2 * i + 1] = sinf(theta);
+        theta = theta * theta_scale;
+      }
+    }
+    if (cudaMemcpy(s->rope, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+      rmi_set_error("rope table upload failed");
+      free_session(s);
+      return RMI_ERR_CUDA;
+    }
+  }
+  *out = s;
+  return RMI_OK;
+}
+
+// One decode step for every sequence of the batch.  with_logits = false skips the output
+// projection (prompt positions whose logits nobody reads).
+static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_t n_gen, bool with_logits) {
+  const rmi_qwen3* m = s->model;
+  const decode_dims& d = s->d;
+  const size_t B = d.batch, nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
+  RMI_TRY(launch_embed(ctx, m->token_embd, s->prompts, n_prompt, s->gen, n_gen, s->d_step, s->x, B));
+  const float* pending = nullptr;  // residual branch still to be added to x
+  for (size_t l = 0; l < d.n_layer; l++) {
+    const layer_weights& w = m->layers[l];
+    RMI_TRY(launch_rmsnorm_quant(ctx, s->x, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+    RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
+    RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
+                                   s->v_cache, l));
+    RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+    RMI_TRY(launch_q8_gemv(ctx, w.wo, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
+    RMI_TRY(launch_rmsnorm_quant(ctx, s->x, s->proj, w.ffn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+    RMI_TRY(launch_q8_gemv(ctx, w.wgu, s->q8, s->xs, B, s->gu, 2 * d.n_ff, 0, 2 * d.n_ff));
+    RMI_TRY(launch_silu_mul_quantize(ctx, s->gu, s->gu + d.n_ff, 2 * d.n_ff, B, d.n_ff, nullptr, s->q8, s->xs));
+    RMI_TRY(launch_q8_gemv(ctx, w.wdown, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
+    pending = s->proj;
+  }
+  // x += last down projection; output norm; logits; greedy token
+  RMI_TRY(launch_rmsnorm_quant(ctx, s->x, pending, m->output_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+  if (with_logits) {
+    RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
+    RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B));
+  }
+  return launch_step_inc(ctx, s->d_step);
+}
+
+static int32_t build_graphs(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_t n_gen) {
+  if (s->exec_full && s->graph_n_prompt == n_prompt && s->graph_n_gen == n_gen && s->graph_sem == ctx->sem &&
+      s->graph_stream == ctx->stream)
+    return RMI_OK;
+  drop_graphs(s);
+  for (int which = 0; which < 2; which++) {
+    RMI_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    int32_t st = enqueue_step(ctx, s, n_prompt, n_gen, which == 1);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (st != RMI_OK) {
+      if (g) cudaGraphDestroy(g);
+      return st;
+    }
+    if (e != cudaSuccess) {
+      rmi_set_error("graph capture of the decode step failed: %s", cudaGetErrorString(e));
+      return RMI_ERR_CUDA;
+    }
+    cudaGraphExec_t ex = nullptr;
+    e = cudaGraphInstantiate(&ex, g, 0);
+    if (e != cudaSuccess) {
+      cudaGraphDestroy(g);
+      rmi_set_error("graph instantiation failed: %s", cudaGetErrorString(e));
+      return RMI_ERR_CUDA;
+    }
+    if (which == 0) {
+      s->graph_body = g;
+      s->exec_body = ex;
+    } else {
+      s->graph_full = g;
+      s->exec_full = ex;
+    }
+  }
+  s->graph_n_prompt = n_prompt;
+  s->graph_n_gen = n_gen;
+  s->graph_sem = ctx->sem;
+  s->graph_stream = ctx->stream;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint32_t* prompts, size_t n_prompt,
+                                        size_t n_gen, uint32_t* out_tokens, float* prefill_ms, float* gen_ms) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  const decode_dims& d = s->d;
+  RMI_REQUIRE(prompts != nullptr && n_prompt > 0, RMI_ERR_BAD_SHAPE, "Cannot generate from an empty prompt");
+  // src/models/qwen3.rs:569-578
+  RMI_REQUIRE(n_prompt + n_gen <= d.capacity, RMI_ERR_BAD_SHAPE, "Generation requires capacity %zu; session has %zu",
+              n_prompt + n_gen, d.capacity);
+  RMI_REQUIRE(n_gen == 0 || out_tokens != nullptr, RMI_ERR_BAD_HANDLE, "out_tokens is null");
+  for (size_t i = 0; i < d.batch * n_prompt; i++)
+    RMI_REQUIRE(prompts[i] < d.vocab, RMI_ERR_BAD_SHAPE, "token id %u outside the vocabulary (%zu)", prompts[i], d.vocab);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (s->prompts_cap < d.batch * n_prompt) {
+    cudaFree(s->prompts);
+    s->prompts = nullptr;
+    RMI_CUDA_CHECK(cudaMalloc(&s->prompts, d.batch * n_prompt * 4));
+    s->prompts_cap = d.batch * n_prompt;
+    drop_graphs(s);
+  }
+  if (s->gen_cap < d.batch * (n_gen ? n_gen : 1)) {
+    cudaFree(s->gen);
+    s->gen = nullptr;
+    RMI_CUDA_CHECK(cudaMalloc(&s->gen, d.batch * (n_gen ? n_gen : 1) * 4));
+    s->gen_cap = d.batch * (n_gen ? n_gen : 1);
+    drop_graphs(s);
+  }
+  RMI_CUDA_CHECK(cudaMemcpyAsync(s->prompts, prompts, d.batch * n_prompt * 4, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->gen, 0, s->gen_cap * 4, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->d_step, 0, 4, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->d_flag, 0, 4, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  RMI_TRY(build_graphs(ctx, s, n_prompt, n_gen));
+  cudaEvent_t e0, e1, e2;
+  RMI_CUDA_CHECK(cudaEventCreate(&e0));
+  RMI_CUDA_CHECK(cudaEventCreate(&e1));
+  RMI_CUDA_CHECK(cudaEventCreate(&e2));
+  // steps 0 .. n_prompt+n_gen-2 (src/models/qwen3.rs:118-126); logits from step n_prompt-1 on
+  const size_t steps = n_prompt + n_gen - 1;
+  // kernels per graph: the GEMV launcher issues one kernel per pass of 8/4/2/1 activation rows
+  uint64_t passes = d.batch / 8;
+  for (size_t rem = d.batch % 8, p2 = 4; p2 >= 1; p2 >>= 1)
+    if (rem >= p2) {
+      passes++;
+      rem -= p2;
+    }
+  const uint64_t launches_per_body = 3 + d.n_layer * (5 + 4 * passes), launches_full = launches_per_body + passes + 1;
+  RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
+  cudaError_t ce = cudaSuccess;
+  for (size_t st = 0; st < steps && ce == cudaSuccess; st++) {
+    if (st == n_prompt - 1) ce = cudaEventRecord(e1, ctx->stream);
+    const bool full = st + 1 >= n_prompt && n_gen > 0;
+    if (ce == cudaSuccess) ce = cudaGraphLaunch(full ? s->exec_full : s->exec_body, ctx->stream);
+    ctx->launches.fetch_add(full ? launches_full : launches_per_body, std::memory_order_relaxed);
+  }
+  if (ce == cudaSuccess && steps < n_prompt) ce = cudaEventRecord(e1, ctx->stream);
+  if (ce == cudaSuccess) ce = cudaEventRecord(e2, ctx->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx->stream);
+  float t_pre = 0.0f, t_gen = 0.0f;
+  if (ce == cudaSuccess) {
+    cudaEventElapsedTime(&t_pre, e0, e1);
+    cudaEventElapsedTime(&t_gen, e1, e2);
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaEventDestroy(e2);
+  if (ce != cudaSuccess) {
+    rmi_set_error("decode step failed: %s", cudaGetErrorString(ce));
+    return RMI_ERR_CUDA;
+  }
+  if (prefill_ms) *prefill_ms = t_pre;
+  if (gen_ms) *gen_ms = t_gen;
+  int flag = 0;
+  RMI_CUDA_CHECK(cudaMemcpy(&flag, s->d_flag, 4, cudaMemcpyDeviceToHost));
+  if (n_gen) RMI_CUDA_CHECK(cudaMemcpy(out_tokens, s->gen, d.batch * n_gen * 4, cudaMemcpyDeviceToHost));
+  RMI_REQUIRE(flag == 0, RMI_ERR_NONFINITE, "Cannot sample non-finite logits");
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_read_hidden(rmi_ctx* ctx, rmi_session* s, float* hidden) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  RMI_CUDA_CHECK(cudaMemcpy(hidden, s->x, s->d.batch * s->d.n_embd * 4, cudaMemcpyDeviceToHost));
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_read_logits(rmi_ctx* ctx, rmi_session* s, float* logits) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  RMI_CUDA_CHECK(cudaMemcpy(logits, s->logits, s->d.batch * s->d.vocab * 4, cudaMemcpyDeviceToHost));
+  return RMI_OK;
+}
