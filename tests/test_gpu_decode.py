@@ -1,0 +1,99 @@
+"""Qwen3-architecture decode on the device vs the oracle: identical greedy tokens and
+bit-identical hidden state / logits of the final step."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import orc
+from tests.helpers import bits
+from tests.synth_model import tiny_cfg
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx(rmi):
+    c = rmi.context(0)
+    yield c
+    c.set_semantics(rmi.SEM_AVX2)
+
+
+def _model(rmi, tmp_path_factory, cfg, seed):
+    tensors = rmi.synth.qwen3_tensors(cfg, seed)
+    path = str(tmp_path_factory.mktemp("m") / "model.gguf")
+    rmi.synth.write_qwen3_gguf(path, cfg, tensors)
+    return path, tensors
+
+
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
+def test_tiny_model_tokens_hidden_and_logits(rmi, ctx, tmp_path_factory, sem):
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=0)
+    model = rmi.Qwen3Model.from_file(path)
+    assert model.config["n_embd"] == cfg["n_embd"] and model.config["vocab"] == cfg["vocab"]
+    oracle = orc.Qwen3(cfg, tensors)
+    prompt = rmi.synth.prompt_tokens(cfg["vocab"], 24, seed=7)
+    s = rmi.Qwen3Session(model, 24 + 40)
+    got = s.generate(prompt, 40)[0]
+    ref, trace, logits = oracle.generate(prompt, 40, sem=sem, want_trace=True, want_logits=True)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    assert np.array_equal(bits(s.logits()[0]), bits(logits))
+    # a second run on the same session reproduces the tokens (KV cache is overwritten in place)
+    assert np.array_equal(s.generate(prompt, 40)[0], ref)
+    s.free()
+    model.free()
+
+
+def test_batch_of_independent_sequences(rmi, ctx, tmp_path_factory):
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_layer=3)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=4)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    B, P, G = 11, 16, 12
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], P, seed=100 + b) for b in range(B)])
+    got = model.generate(prompts, G)
+    for b in range(B):
+        assert np.array_equal(got[b], oracle.generate(prompts[b], G, sem=orc.SEM_AVX2)), b
+    model.free()
+
+
+def test_qwen3_head_shape_and_long_context(rmi, ctx, tmp_path_factory):
+    # head_dim 128, 16 q / 8 kv heads, QK-norm, theta 1e6 as in Qwen3-0.6B; 2 layers, small vocab;
+    # 300 positions crosses the 256-padding boundary of the reference's score rows
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_embd=1024, n_layer=2, n_head=16, n_head_kv=8, head_dim=128, n_ff=3072, vocab=2048)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=0)
+    model = rmi.Qwen3Model.from_file(path)
+    prompt = rmi.synth.prompt_tokens(cfg["vocab"], 270, seed=1)
+    s = rmi.Qwen3Session(model, 300)
+    got = s.generate(prompt, 30)[0]
+    ref, trace = orc.Qwen3(cfg, tensors).generate(prompt, 30, sem=orc.SEM_AVX2, threads=8, want_trace=True)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    s.free()
+    model.free()
+
+
+def test_session_errors(rmi, ctx, tmp_path_factory):
+    cfg = tiny_cfg()
+    path, _ = _model(rmi, tmp_path_factory, cfg, seed=0)
+    model = rmi.Qwen3Model.from_file(path)
+    with pytest.raises(rmi.RmiError) as e:          # src/models/qwen3.rs:442-447
+        rmi.Qwen3Session(model, 0)
+    assert e.value.status == 2
+    s = rmi.Qwen3Session(model, 8)
+    with pytest.raises(rmi.RmiError) as e:          # :569-578 capacity
+        s.generate(np.arange(6, dtype=np.uint32), 4)
+    assert e.value.status == 2
+    with pytest.raises(rmi.RmiError) as e:          # token id outside the vocabulary
+        s.generate(np.array([cfg["vocab"]], np.uint32), 1)
+    assert e.value.status == 2
+    s.free()
+    model.free()
+    with pytest.raises(rmi.RmiError) as e:
+        rmi.Qwen3Model.from_file(os.path.join(os.path.dirname(path), "missing.gguf"))
+    assert e.value.status == 7
