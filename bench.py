@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+Headline (one JSON line): int8 tensor-op throughput of the fused Q8_0 SwiGLU FFN at the
+prefill shape M=512, K=1024, n_ff=3072 (x -> quantize -> gate|up GEMM + SiLU*mul + re-quantize
+-> down GEMM).  One step = one FFN pass over one batch of 512 synthetic token rows.
+  value     whole-job TOPS with inputs resident in HBM (all ranks; weak scaling: every rank
+            runs its own 512-row batch, no collective)
+  e2e       the same metric through the host-pointer C ABI call (pinned host x in, host out)
+  roofline  the dominant kernel (gate|up tcgen05 GEMM with fused epilogue), timed with CUDA
+            events on the launching stream
+  cpu_baseline / --impl reference: the CPU oracle port of the reference's AVX2 path, timed on
+            this box's host cores
+Secondary figures (GEMV GB/s, decode tok/s, Q4_K) are carried in "also" at N=1.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M, E, FF = 512, 1024, 3072
+OPS_GATE_UP = 2 * M * E * (2 * FF)
+OPS_DOWN = 2 * M * FF * E
+OPS_STEP = OPS_GATE_UP + OPS_DOWN          # 9.664 G int8-op
+METRIC = "Q8_0 fused FFN prefill int8 GEMM throughput (M=512,K=1024,n_ff=3072)"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+                 nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                 nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        return {"sm_mhz": int(statistics.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def ffn_weights_bytes(pkg):
+    return (pkg.synth.q8_0_weight(FF, E, seed=0), pkg.synth.q8_0_weight(FF, E, seed=1),
+            pkg.synth.q8_0_weight(E, FF, seed=2))
+
+
+def cpu_ffn_tops(pkg, threads: int, reps: int):
+    """The oracle's AVX2 path (quantize, gate, up, SiLU*mul, re-quantize, down per token) on host cores."""
+    from oracle import orc
+    g, u, d = ffn_weights_bytes(pkg)
+    x = pkg.synth.normal((M, E), seed=3)
+    orc.ffn_swiglu_q8_0(g, u, d, x[:32], E, FF, orc.SEM_AVX2, threads)  # warm the pool and caches
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.ffn_swiglu_q8_0(g, u, d, x, E, FF, orc.SEM_AVX2, threads)
+        times.append(time.perf_counter() - t0)
+    return OPS_STEP / statistics.median(times) / 1e12, times
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU implementation of the path (C port of its AVX2
+    kernels; the Rust crate cannot be built offline) on all host threads, same config/metric."""
+    if rank != 0:
+        return
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    threads = args.threads or os.cpu_count() or 1
+    from oracle import orc
+    g, u, d = ffn_weights_bytes(pkg)
+    x = pkg.synth.normal((M, E), seed=3)
+    for _ in range(max(args.warmup, 1)):
+        orc.ffn_swiglu_q8_0(g, u, d, x[:64], E, FF, orc.SEM_AVX2, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.ffn_swiglu_q8_0(g, u, d, x, E, FF, orc.SEM_AVX2, threads)
+    dt = time.perf_counter() - t0
+    tops = OPS_STEP * args.steps / dt / 1e12
+    line = {"impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "configs[1]: Q8_0 prefill GEMM + fused FFN, M=512 K=1024 n_ff=3072",
+                       "semantics": "avx2"},
+            "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port",
+                             "sample": f"{args.steps} full M=512 batches, {threads} threads, row-partitioned GEMVs"},
+            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem):
+    """GB/s of the decode GEMV with `copies` distinct weight buffers so every launch streams from HBM."""
+    ctx.set_semantics(sem)
+    wb = pkg.synth.q8_0_weight(n, k, seed=0)
+    ws = [pkg.QuantizedTensor.from_bytes(wb, pkg.GGML_Q8_0, k, n) for _ in range(copies)]
+    x = torch.from_numpy(pkg.synth.normal((1, k), seed=1)).cuda()
+    q8 = torch.empty(k, dtype=torch.uint8, device="cuda")
+    sc = torch.empty(k // 32, dtype=torch.float32, device="cuda")
+    out = torch.empty(n, dtype=torch.float32, device="cuda")
+    pkg.quantize_q8_0_dev(ctx, x.data_ptr(), 1, k, q8.data_ptr(), sc.data_ptr())
+
+    def burst():
+        for w in ws:
+            pkg.matmul_q8_0_prequantized_dev(w, q8.data_ptr(), sc.data_ptr(), 1, out.data_ptr())
+
+    for _ in range(3):
+        burst()
+    stream.synchronize()
+    mode = "stream"
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            burst()
+        graph.replay()
+        stream.synchronize()
+        mode = "cuda-graph"
+    except Exception:
+        graph = None
+        ctx.set_stream(stream.cuda_stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(iters):
+            graph.replay() if graph is not None else burst()
+        e1.record(stream)
+    stream.synchronize()
+    per = e0.elapsed_time(e1) / 1e3 / (iters * copies)
+    algo = n * (k // 32) * 34 + k + (k // 32) * 4 + n * 4   # weights + pre-quantized x + y
+    for w in ws:
+        w.free()
+    return {"shape": [n, k], "us_per_gemv": per * 1e6, "gbs": algo / per / 1e9, "algorithmic_bytes": algo,
+            "distinct_weight_copies": copies, "launch": mode}
+
+
+def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem):
+    ctx.set_semantics(sem)
+    model = pkg.Qwen3Model.from_file(path)
+    s = pkg.Qwen3Session(model, n_prompt + n_gen, batch=batch)
+    prompts = np.stack([pkg.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=1000 + b) for b in range(batch)])
+    toks = s.generate(prompts, n_gen)
+    res = {"batch": batch, "prompt": n_prompt, "gen": n_gen, "tok_s": batch * n_gen / (s.gen_ms / 1e3),
+           "gen_ms": s.gen_ms, "prefill_ms": s.prefill_ms, "first_tokens": [int(t) for t in toks[0, :4]]}
+    s.free()
+    model.free()
+    return res, toks
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--threads", type=int, default=0, help="CPU threads of the reference arm / cpu baseline (0 = all)")
+    ap.add_argument("--semantics", default="neon", choices=["neon", "scalar", "avx2"])
+    ap.add_argument("--no-also", action="store_true", help="skip the secondary figures (GEMV, decode)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = pkg.context(local_rank)
+    sem = {"neon": pkg.SEM_NEON, "scalar": pkg.SEM_SCALAR, "avx2": pkg.SEM_AVX2}[args.semantics]
+    ctx.set_semantics(sem)
+    stream = torch.cuda.Stream()
+    ctx.set_stream(stream.cuda_stream)
+    hbm_peak, bf16_peak, bf16_sus, peak_kind = measured_peaks()
+    sm_count, l2_bytes, _ = ctx.device_info()
+
+    # R distinct weight/input/output sets, > L2 in total, rotated every step
+    g, u, d = ffn_weights_bytes(pkg)
+    set_bytes = (2 * FF * E + E * FF) * (1 + 4 / 32) + 2 * M * E * 4
+    R = int(max(4, -(-2 * l2_bytes // set_bytes)))
+    sets = []
+    for r in range(R):
+        wgu = pkg.QuantizedTensor.from_bytes(g, pkg.GGML_Q8_0, E, FF).fuse_vstack(
+            pkg.QuantizedTensor.from_bytes(u, pkg.GGML_Q8_0, E, FF))
+        wd = pkg.QuantizedTensor.from_bytes(d, pkg.GGML_Q8_0, FF, E)
+        x = torch.from_numpy(pkg.synth.normal((M, E), seed=3 + 17 * r + 1000 * rank)).cuda()
+        out = torch.empty((M, E), dtype=torch.float32, device="cuda")
+        sets.append((wgu, wd, x, out))
+
+    def step(i):
+        wgu, wd, x, out = sets[i % R]
+        pkg.ffn_swiglu_q8_0_dev(wgu, wd, x.data_ptr(), M, out.data_ptr())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, R)):   # also builds the tcgen05 weight layout of every set
+        step(i)
+    barrier()
+    launches0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        barrier()
+    launches = ctx.launch_count() - launches0
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    value = world * OPS_STEP * args.steps / (ms_total / 1e3) / 1e12
+
+    # per-kernel timing of the same steps (second pass, events around the tagged launches)
+    ksteps = min(args.steps, 2000)
+    ctx.prof_enable(True)
+    for i in range(ksteps):
+        step(i)
+    n_k, ms_k = ctx.prof_read("gemm_tc_swiglu")
+    n_d, ms_d = ctx.prof_read("gemm_tc")
+    ctx.prof_enable(False)
+    roofline = None
+    int8_peak = 2.0 * bf16_peak   # no int8 figure is measured on this pool: dense int8 = 2 x the measured bf16 peak
+    if n_k:
+        achieved = OPS_GATE_UP / (ms_k / n_k / 1e3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<128,SWIGLU_Q8> (gate|up GEMM, fused SiLU*mul + re-quantize)",
+                    "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
+                    "peak_source": f"2 x bf16 {peak_kind} ({bf16_peak} TFLOP/s burst); of {peak_kind}",
+                    "frac_of_bf16_peak": achieved / bf16_peak, "avg_kernel_us": ms_k / n_k * 1e3, "launches": n_k,
+                    "down_gemm_avg_us": (ms_d / n_d * 1e3) if n_d else None,
+                    "down_gemm_tops": (OPS_DOWN / (ms_d / n_d / 1e3) / 1e12) if n_d else None,
+                    "traffic": None}
+    else:   # AVX2 semantics keep every M on the CUDA-core kernels
+        n_g, ms_g = ctx.prof_read("q8_gemv")
+        roofline = {"bound": "tensor", "kernel": "q8_gemv_kernel (CUDA cores; AVX2 semantics)", "achieved": value,
+                    "peak": int8_peak, "unit": "TFLOP/s", "frac": value / int8_peak, "traffic": None}
+
+    # end to end through the host-pointer C ABI call: pinned x in, pinned out back, every step
+    e2e_steps = min(args.steps, 300)
+    hx = torch.from_numpy(pkg.synth.normal((M, E), seed=99 + rank)).pin_memory()
+    hout = torch.empty((M, E), dtype=torch.float32).pin_memory()
+    hx_np, hout_np = hx.numpy(), hout.numpy()
+    lib, C = pkg.lib(), __import__("ctypes")
+    wgu0, wd0 = sets[0][0], sets[0][1]
+
+    def e2e_step(i):
+        wgu, wd = sets[i % R][0], sets[i % R][1]
+        st = lib.rmi_ffn_swiglu_q8_0(ctx.handle, wgu._h, wd._h, C.c_void_p(hx_np.ctypes.data), C.c_size_t(M),
+                                     C.c_void_p(hout_np.ctypes.data))
+        if st != 0:
+            raise RuntimeError(lib.rmi_last_error().decode())
+
+    for i in range(5):
+        e2e_step(i)
+    barrier()
+    e0.record(stream)
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record(stream)
+    barrier()
+    e2e_ms = torch.tensor([max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e = {"value": world * OPS_STEP * e2e_steps / (float(e2e_ms.item()) / 1e3) / 1e12, "unit": "TOPS",
+           "h2d_bytes_per_step": M * E * 4, "d2h_bytes_per_step": M * E * 4, "steps": e2e_steps,
+           "api": "rmi_ffn_swiglu_q8_0 (host pointers, pinned)"}
+
+    line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "configs[1]: Q8_0 prefill GEMM + fused FFN, M=512 K=1024 n_ff=3072",
+                       "semantics": args.semantics, "l2_hygiene": f"{R} distinct weight/input/output sets "
+                       f"({R * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB) rotated every step",
+                       "int8_ops_per_step": OPS_STEP, "parallelism": f"replicas x{world}, no collective"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary()}
+
+    if rank == 0 and world == 1:
+        threads = args.threads or os.cpu_count() or 1
+        tops, times = cpu_ffn_tops(pkg, threads, reps=3)
+        line["cpu_baseline"] = {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port",
+                                "sample": f"3 full M=512 batches (median {statistics.median(times) * 1e3:.1f} ms), "
+                                          f"AVX2 path of the C oracle, {threads} threads"}
+        if not args.no_also:
+            also = {}
+            try:
+                ctx.set_stream(stream.cuda_stream)
+                also["gemv_c1_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 3072, 1024, 160, 10, pkg.SEM_AVX2)
+                also["gemv_logits_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 151936, 1024, 4, 10, pkg.SEM_AVX2)
+                also["gemv_c5_m1_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 32768, 8192, 3, 10, pkg.SEM_AVX2)
+                for k_ in list(also):
+                    also[k_]["frac_of_hbm_peak"] = also[k_]["gbs"] / hbm_peak
+                also["hbm_peak_gbs"] = hbm_peak
+            except Exception as ex:   # secondary figures never break the headline line
+                also["gemv_error"] = repr(ex)
+            try:
+                ctx.set_stream(None)
+                cfg = dict(pkg.synth.QWEN3_0_6B)
+                path = os.path.join(tempfile.gettempdir(), "rmi_qwen3_0_6b_seed0.gguf")
+                if not os.path.exists(path):
+                    pkg.synth.write_qwen3_gguf(path, cfg, pkg.synth.qwen3_tensors(cfg, 0))
+                for b in (1, 32):
+                    res, _ = decode_bench(pkg, ctx, cfg, path, b, 512, 128, pkg.SEM_AVX2)
+                    kv = 28 * (512 + 64) * 1024 * 2 * 2
+                    res["roofline_tok_s"] = hbm_peak * 1e9 / (633233408 + b * kv) * b
+                    res["frac_of_roofline"] = res["tok_s"] / res["roofline_tok_s"]
+                    also[f"decode_qwen3_0_6b_b{b}_avx2"] = res
+            except Exception as ex:
+                also["decode_error"] = repr(ex)
+            line["also"] = also
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

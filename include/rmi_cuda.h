@@ -56,9 +56,12 @@ enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12
  *   AVX2   src/ops/quant/q8_0.rs:176-230 + src/ops/kernel/q8_0/avx2.rs:53-174
  *   NEON   src/ops/quant/q8_0.rs:75-165  + src/ops/kernel/q8_0/neon.rs:49-73
  *   SCALAR src/ops/quant/q8_0.rs:49-71   + src/ops/kernel/q8_0/scalar.rs:31-58
- * The tensor-core GEMM (M > 32) yields whole-block int32 sums, so it implements NEON or
- * SCALAR accumulation; under AVX2 it accumulates as NEON does (within 1e-5 relative of
- * the AVX2 kernel, exact block sums). */
+ * The tensor-core GEMM (M > 32) yields whole-block int32 sums, which is how the NEON and
+ * SCALAR variants accumulate, so those two run on tcgen05.  The AVX2 variant accumulates
+ * eight partial sums per block; under AVX2 every M stays on the CUDA-core kernels so that
+ * the result remains bit-exact (slower for M > 32).  Element-wise steps (rms_norm, rope,
+ * softmax, SiLU) follow the reference's portable x86 code under all three settings; exp()
+ * is the correctly rounded f32 exponential. */
 typedef enum { RMI_SEM_AVX2 = 0, RMI_SEM_NEON = 1, RMI_SEM_SCALAR = 2 } rmi_semantics;
 
 /* ---- context ------------------------------------------------------------------------
@@ -77,6 +80,13 @@ int32_t rmi_sync(rmi_ctx* ctx);
 int32_t rmi_device_info(rmi_ctx* ctx, int32_t* sm_count, size_t* l2_bytes, size_t* mem_bytes);
 /* Number of kernels this library has launched on this context (for launch accounting). */
 int32_t rmi_launch_count(rmi_ctx* ctx, uint64_t* count);
+
+/* Per-kernel device timing for benchmarks (no counterpart in the reference; its --profile
+ * flag accumulates wall-clock per phase, src/app/text.rs:238-245).  While enabled, CUDA event
+ * pairs are recorded around the launches tagged "q8_gemv", "gemm_tc" and "gemm_tc_swiglu";
+ * rmi_prof_read sums them.  Enabling resets the records.  Not for use inside graph capture. */
+int32_t rmi_prof_enable(rmi_ctx* ctx, int32_t on);
+int32_t rmi_prof_read(rmi_ctx* ctx, const char* tag, uint64_t* launches, float* total_ms);
 
 /* Device buffers for callers that have no CUDA allocator of their own. */
 int32_t rmi_dev_alloc(rmi_ctx* ctx, size_t bytes, void** dev_ptr);

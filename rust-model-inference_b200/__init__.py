@@ -110,6 +110,15 @@ class Context:
         _check(lib().rmi_launch_count(self._h, C.byref(v)))
         return v.value
 
+    def prof_enable(self, on: bool):
+        _check(lib().rmi_prof_enable(self._h, C.c_int32(1 if on else 0)))
+
+    def prof_read(self, tag: str):
+        """-> (launches, total_ms) of the kernels tagged `tag` since prof_enable(True)."""
+        n, ms = C.c_uint64(), C.c_float()
+        _check(lib().rmi_prof_read(self._h, tag.encode(), C.byref(n), C.byref(ms)))
+        return n.value, ms.value
+
     # raw device memory (for callers without an allocator of their own)
     def dev_alloc(self, nbytes: int) -> int:
         p = C.c_void_p()
@@ -398,6 +407,41 @@ def ffn_swiglu_q8_0(w_gate_up: QuantizedTensor, w_down: QuantizedTensor, x) -> n
     out = np.zeros((x.shape[0], w_down.n_out), np.float32)
     _check(lib().rmi_ffn_swiglu_q8_0(w_gate_up._ctx.handle, w_gate_up._h, w_down._h, _p(x), _sz(x.shape[0]), _p(out)))
     return out
+
+
+# Device-pointer variants (stream-ordered, no synchronisation): pointers are integers, e.g.
+# torch.Tensor.data_ptr() or Context.dev_alloc().
+
+def ffn_swiglu_q8_0_dev(w_gate_up: QuantizedTensor, w_down: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    _check(lib().rmi_ffn_swiglu_q8_0_dev(w_gate_up._ctx.handle, w_gate_up._h, w_down._h, C.c_void_p(x_ptr), _sz(m),
+                                         C.c_void_p(out_ptr)))
+
+
+def matmul_q8_0_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    _check(lib().rmi_matmul_q8_0_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m), C.c_void_p(out_ptr)))
+
+
+def matmul_q8_0_prequantized_dev(weight: QuantizedTensor, q8_ptr: int, scales_ptr: int, m: int, out_ptr: int,
+                                 row_begin: int = 0, row_end: int | None = None):
+    row_end = weight.n_out if row_end is None else row_end
+    _check(lib().rmi_matmul_q8_0_prequantized_dev(weight._ctx.handle, weight._h, C.c_void_p(q8_ptr),
+                                                  C.c_void_p(scales_ptr), _sz(m), C.c_void_p(out_ptr), _sz(row_begin),
+                                                  _sz(row_end)))
+
+
+def quantize_q8_0_dev(ctx: Context, x_ptr: int, m: int, n: int, q8_ptr: int, scales_ptr: int):
+    _check(lib().rmi_quantize_q8_0_dev(ctx.handle, C.c_void_p(x_ptr), _sz(m), _sz(n), C.c_void_p(q8_ptr),
+                                       C.c_void_p(scales_ptr)))
+
+
+def matmul_q4_k_dequant_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    _check(lib().rmi_matmul_q4_k_dequant_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m),
+                                             C.c_void_p(out_ptr)))
+
+
+def unshard_cols_dev(ctx: Context, gathered_ptr: int, g: int, m: int, n_per_rank: int, out_ptr: int):
+    _check(lib().rmi_unshard_cols_dev(ctx.handle, C.c_void_p(gathered_ptr), _sz(g), _sz(m), _sz(n_per_rank),
+                                      C.c_void_p(out_ptr)))
 
 
 def quantize_row_q8_k(x, ctx: Context | None = None):

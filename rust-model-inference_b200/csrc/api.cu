@@ -85,6 +85,60 @@ int32_t rmi_scratch(rmi_ctx* ctx, int slot, size_t bytes, void** out) {
   return RMI_OK;
 }
 
+// ---------------------------------------------------------------- per-kernel timing
+
+int rmi_prof_begin(rmi_ctx* ctx, const char* tag) {
+  if (!ctx->prof_on || ctx->prof.size() >= 16384) return -1;
+  rmi_prof_rec r;
+  r.tag = tag;
+  if (cudaEventCreate(&r.a) != cudaSuccess) return -1;
+  if (cudaEventCreate(&r.b) != cudaSuccess) {
+    cudaEventDestroy(r.a);
+    return -1;
+  }
+  cudaEventRecord(r.a, ctx->stream);
+  ctx->prof.push_back(r);
+  return (int)ctx->prof.size() - 1;
+}
+
+void rmi_prof_end(rmi_ctx* ctx, int idx) {
+  if (idx >= 0) cudaEventRecord(ctx->prof[idx].b, ctx->stream);
+}
+
+static void prof_clear(rmi_ctx* ctx) {
+  for (auto& r : ctx->prof) {
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  ctx->prof.clear();
+}
+
+extern "C" int32_t rmi_prof_enable(rmi_ctx* ctx, int32_t on) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  prof_clear(ctx);
+  ctx->prof_on = on != 0;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_prof_read(rmi_ctx* ctx, const char* tag, uint64_t* launches, float* total_ms) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  uint64_t n = 0;
+  double ms = 0.0;
+  for (auto& r : ctx->prof) {
+    if (strcmp(r.tag, tag) != 0) continue;
+    float t = 0.0f;
+    if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) {
+      ms += t;
+      n++;
+    }
+  }
+  if (launches) *launches = n;
+  if (total_ms) *total_ms = (float)ms;
+  return RMI_OK;
+}
+
 // ---------------------------------------------------------------- context
 
 extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
@@ -113,6 +167,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->smem_optin = prop.sharedMemPerBlockOptin;
   c->sem = RMI_SEM_AVX2;
   c->launches = 0;
+  c->prof_on = false;
   for (int i = 0; i < 8; i++) {
     c->scratch[i] = nullptr;
     c->scratch_bytes[i] = 0;
@@ -133,6 +188,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
 extern "C" int32_t rmi_destroy(rmi_ctx* ctx) {
   RMI_TRY(rmi_check_ctx(ctx));
   cudaStreamSynchronize(ctx->stream);
+  prof_clear(ctx);
   for (int i = 0; i < 8; i++)
     if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
   cudaFree(ctx->d_status);

@@ -12,6 +12,7 @@
 #include <atomic>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/rmi_cuda.h"
 
@@ -56,6 +57,11 @@ struct rmi_dev_status {
   int32_t pad;
 };
 
+struct rmi_prof_rec {
+  const char* tag;
+  cudaEvent_t a, b;
+};
+
 struct rmi_ctx {
   uint32_t magic;
   int device;
@@ -73,6 +79,9 @@ struct rmi_ctx {
   // growable scratch owned by the context (activations in quantized form etc.)
   void* scratch[8];
   size_t scratch_bytes[8];
+  // optional per-kernel timing (rmi_prof_*): event pairs recorded around tagged launches
+  bool prof_on;
+  std::vector<rmi_prof_rec> prof;
 };
 
 // Q8_0 / Q4_K weight resident in HBM.
@@ -113,6 +122,9 @@ int32_t rmi_check_weight(const rmi_weight* w, int ggml_type);
 int32_t rmi_scratch(rmi_ctx* ctx, int slot, size_t bytes, void** out);
 int32_t rmi_post_launch(rmi_ctx* ctx, const char* what);
 int32_t rmi_check_dev_status(rmi_ctx* ctx, const char* what);
+// Returns a record index (or -1 when timing is off); pass it to rmi_prof_end after the launch.
+int rmi_prof_begin(rmi_ctx* ctx, const char* tag);
+void rmi_prof_end(rmi_ctx* ctx, int idx);
 
 // ---------------------------------------------------------------- device helpers
 

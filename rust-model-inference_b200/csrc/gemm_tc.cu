@@ -396,7 +396,9 @@ int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
     return RMI_ERR_CUDA;
   }
   size_t grid = m_tiles * p.n_tiles_n;
+  const int pr = rmi_prof_begin(ctx, EPI == GEMM_EPI_SWIGLU_Q8 ? "gemm_tc_swiglu" : "gemm_tc");
   kern<<<(unsigned)grid, 320, smem, ctx->stream>>>(p);
+  rmi_prof_end(ctx, pr);
   return rmi_post_launch(ctx, "gemm_tc");
 }
 

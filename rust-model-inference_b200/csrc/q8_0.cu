@@ -340,8 +340,10 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
   // fewer warps per CTA when the problem is small so that more SMs take part
   int wpc = warps >= (size_t)ctx->sm_count * 16 ? 8 : (warps >= (size_t)ctx->sm_count * 4 ? 4 : 2);
   unsigned grid = (unsigned)((warps + wpc - 1) / wpc);
+  const int pr = rmi_prof_begin(ctx, "q8_gemv");
   kern<<<grid, wpc * 32, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin,
                                               row_end, first_tile);
+  rmi_prof_end(ctx, pr);
   return rmi_post_launch(ctx, "q8_gemv");
 }
 

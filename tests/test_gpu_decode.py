@@ -97,3 +97,44 @@ def test_session_errors(rmi, ctx, tmp_path_factory):
     with pytest.raises(rmi.RmiError) as e:
         rmi.Qwen3Model.from_file(os.path.join(os.path.dirname(path), "missing.gguf"))
     assert e.value.status == 7
+
+
+def _full_model(rmi):
+    """Qwen3-0.6B-architecture checkpoint with random-init weights (seed 0), cached in the temp dir."""
+    import tempfile
+    cfg = dict(rmi.synth.QWEN3_0_6B)
+    path = os.path.join(tempfile.gettempdir(), "rmi_qwen3_0_6b_seed0.gguf")
+    if not os.path.exists(path):
+        tmp = path + f".{os.getpid()}.tmp"
+        rmi.synth.write_qwen3_gguf(tmp, cfg, rmi.synth.qwen3_tensors(cfg, 0))
+        os.replace(tmp, path)
+    f = rmi.gguf.GGUFFile(path)
+    tensors = {}
+    for name, (dims, gtype, data) in f.tensors.items():
+        tensors[name] = data if gtype == rmi.gguf.GGML_Q8_0 else data.view(np.float32)
+    return cfg, path, tensors
+
+
+def test_config4_full_size_greedy_tokens_identical_over_128_steps(rmi, ctx):
+    # BASELINE config 4: 28 layers, hidden 1024, 16 Q / 8 KV heads x 128, FFN 3072, vocab 151936 tied,
+    # F16 KV cache, 512 random prompt ids, 128 greedy tokens (x86 production semantics)
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg, path, tensors = _full_model(rmi)
+    model = rmi.Qwen3Model.from_file(path)
+    B, P, G = 2, 512, 128
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], P, seed=1000 + b) for b in range(B)])
+    s = rmi.Qwen3Session(model, P + G, batch=B)
+    got = s.generate(prompts, G)
+    oracle = orc.Qwen3(cfg, tensors)
+    threads = min(os.cpu_count() or 1, 16)
+    ref0, trace, logits = oracle.generate(prompts[0], G, sem=orc.SEM_AVX2, threads=threads, want_trace=True,
+                                          want_logits=True)
+    assert np.array_equal(got[0], ref0)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    assert np.array_equal(bits(s.logits()[0]), bits(logits))
+    top2 = np.sort(logits)[-2:]
+    print(f"final-step top-1/top-2 logit margin: {top2[1] - top2[0]:.6f}")
+    ref1 = oracle.generate(prompts[1], G, sem=orc.SEM_AVX2, threads=threads)
+    assert np.array_equal(got[1], ref1)
+    s.free()
+    model.free()
