@@ -317,6 +317,8 @@ static void free_weight(rmi_weight* w) {
   if (w->d_tile16) cudaFree(w->d_tile16);
   if (w->d_umma_q) cudaFree(w->d_umma_q);
   if (w->d_umma_s) cudaFree(w->d_umma_s);
+  if (w->d_umma_gu_q) cudaFree(w->d_umma_gu_q);
+  if (w->d_umma_gu_s) cudaFree(w->d_umma_gu_s);
   if (w->d_raw) cudaFree(w->d_raw);
   w->magic = 0;
   delete w;
@@ -449,9 +451,11 @@ extern "C" int32_t rmi_weight_fuse_vstack(rmi_ctx* ctx, const rmi_weight* a, con
   return RMI_OK;
 }
 
-int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* cw) {
+int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* cw, bool gate_up_interleaved) {
   rmi_weight* w = const_cast<rmi_weight*>(cw);
-  if (w->d_umma_q) return RMI_OK;
+  if (gate_up_interleaved ? w->d_umma_gu_q != nullptr : w->d_umma_q != nullptr) return RMI_OK;
+  RMI_REQUIRE(!gate_up_interleaved || (w->n_rows_a * 2 == w->n_rows && w->n_rows_a % 32 == 0), RMI_ERR_BAD_SHAPE,
+              "gate/up interleaving needs a v-stack of two equal halves with n_ff a multiple of 32");
   const size_t blocks = w->n_in / 32;
   const size_t n_slabs = (w->n_in + 127) / 128;
   const size_t tiles = (w->n_rows + 127) / 128;
@@ -461,15 +465,21 @@ int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* cw) {
   RMI_TRY(dev_malloc((void**)&q, qb));
   int32_t st = dev_malloc((void**)&s, sb);
   if (st == RMI_OK && cudaMemsetAsync(s, 0, sb, ctx->stream) != cudaSuccess) st = RMI_ERR_CUDA;
-  if (st == RMI_OK) st = launch_q8_build_umma(ctx, w->d_tile16, q, s, w->n_rows, blocks);
+  if (st == RMI_OK)
+    st = launch_q8_build_umma(ctx, w->d_tile16, q, s, w->n_rows, blocks, gate_up_interleaved ? w->n_rows_a : 0);
   if (st != RMI_OK) {
     cudaFree(q);
     if (s) cudaFree(s);
     return st;
   }
-  w->d_umma_q = q;
-  w->d_umma_s = s;
-  w->umma_bytes = qb + sb;
+  if (gate_up_interleaved) {
+    w->d_umma_gu_q = q;
+    w->d_umma_gu_s = s;
+  } else {
+    w->d_umma_q = q;
+    w->d_umma_s = s;
+  }
+  w->umma_bytes += qb + sb;
   return RMI_OK;
 }
 
@@ -674,7 +684,7 @@ static int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight*
   RMI_REQUIRE(n_ff % 32 == 0, RMI_ERR_BAD_SHAPE, "n_ff=%zu is not a multiple of 32", n_ff);
   const size_t b1 = n_embd / 32, b2 = n_ff / 32;
   if (use_tensor_cores(ctx, m)) {
-    RMI_TRY(ensure_umma_layout(ctx, wgu));
+    RMI_TRY(ensure_umma_layout(ctx, wgu, true));
     RMI_TRY(ensure_umma_layout(ctx, wd));
     const size_t m_tiles = (m + 127) / 128;
     const size_t s1 = (n_embd + 127) / 128, s2 = (n_ff + 127) / 128;
@@ -696,7 +706,7 @@ static int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight*
     g.w = wgu;
     g.m = m;
     g.col_begin = 0;
-    g.col_end = n_ff;  // each tile computes gate columns and the matching up columns
+    g.col_end = n_ff;  // FFN columns; each tile computes 32 gate columns and the matching up columns
     g.epilogue = GEMM_EPI_SWIGLU_Q8;
     g.n_ff = n_ff;
     g.act_img = a2;

@@ -108,6 +108,8 @@ struct rmi_weight {
   size_t tile16_bytes;
   uint8_t* d_umma_q;   // Q8_0, lazily built
   float* d_umma_s;
+  uint8_t* d_umma_gu_q;  // v-stacked gate|up weight in gate/up-interleaved row order (lazily built)
+  float* d_umma_gu_s;
   size_t umma_bytes;
   uint8_t* d_raw;      // Q4_K
   size_t raw_bytes;

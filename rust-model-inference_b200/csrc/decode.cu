@@ -7,11 +7,23 @@
 //   attention            src/models/qwen3.rs:876-933 (f16 q/k/v/p, f64 dot accumulation,
 //                        sequential f32 softmax sum: src/ops/attention.rs:28-38)
 //   greedy argmax        src/models/qwen3.rs:172-191 (first maximum, non-finite -> error)
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "decode.cuh"
 #include "kernels.cuh"
 
 namespace {
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 __device__ __forceinline__ double warp_sum_f64(double v) {
 #pragma unroll
@@ -125,68 +137,127 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
   }
 }
 
-// One CTA per (sequence, kv head); the `group` query heads that share the kv head are
-// processed together.  Output is re-quantized to Q8_0 for the Wo projection.
+// Attention for one (sequence, kv head) by a thread-block cluster of CL CTAs; the `group`
+// query heads that share the kv head are processed together.  CTA r owns the time steps
+// [r*chunk, (r+1)*chunk): it stages its K and V rows in shared memory (cp.async, V overlapped
+// with the score pass), computes its scores with the reference's sequential f64 dot, and
+// publishes them into every CTA's score array through distributed shared memory.  After a
+// cluster barrier each CTA evaluates the soft-max over all T scores (max, exp, the
+// reference's sequential f32 sum, divide, f16), forms the f64 partial of P.V over its own
+// steps and sends it to CTA 0, which adds the partials in rank order, re-quantizes the
+// group*hd outputs to Q8_0 for the Wo projection and writes them.
 template <int SEM>
 __global__ void __launch_bounds__(256)
     attention_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
                      const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
-                     size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                     size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity, size_t chunk,
                      float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned CL = cluster.num_blocks(), rank = cluster.block_rank();
   extern __shared__ __align__(16) uint8_t smem[];
-  const size_t b = blockIdx.x, kvh = blockIdx.y;
+  const size_t b = blockIdx.y, kvh = blockIdx.x / CL;
   const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
   const int T = *d_step + 1;
-  float* sc = reinterpret_cast<float*>(smem);                        // [group][capacity]
-  float* outv = sc + group * capacity;                               // [group][hd]
-  float* red = outv + group * hd;                                    // [group] sums / maxima
-  uint16_t* p16 = reinterpret_cast<uint16_t*>(red + 2 * group + 2);  // [group][capacity]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-  const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
-  const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const size_t cs = (capacity + 3) & ~(size_t)3;  // score row stride (keeps 16-byte alignment)
+  const size_t kstride = hd * 2 + 16;  // bytes; the pad spreads rows over the banks
+  // layout (all offsets multiples of 16 bytes)
+  double* part = reinterpret_cast<double*>(smem);                            // [CL][group*hd] (used on rank 0)
+  float* sc = reinterpret_cast<float*>(part + (size_t)CL * group * hd);      // [group][capacity]
+  float* outv = sc + group * cs;                                       // [group*hd]
+  float* red = outv + group * hd;                                            // [group] sums
+  uint16_t* qs = reinterpret_cast<uint16_t*>(red + ((group + 3) & ~(size_t)3));  // [group][hd]
+  uint16_t* p16 = qs + group * hd;                                           // [group][chunk]
+  uint8_t* kbuf = reinterpret_cast<uint8_t*>(p16 + ((group * chunk + 7) & ~(size_t)7));  // [chunk][kstride]
+  uint8_t* vbuf = kbuf + chunk * kstride;                                    // [chunk][hd*2]
 
-  // scores[g][t] = f32(sum_f64 q*k) * kq_scale
-  for (int t = warp; t < T; t += nwarp) {
-    const uint16_t* kr = kbase + (size_t)t * nk;
-    for (size_t g = 0; g < group; g++) {
-      const uint16_t* qr = q16 + b * nq + (kvh * group + g) * hd;
-      double s = 0.0;
-      for (size_t i = lane; i < hd; i += 32)
-        s += (double)__fmul_rn(f16_bits_to_f32(qr[i]), f16_bits_to_f32(kr[i]));
-      s = warp_sum_f64(s);
-      if (lane == 0) sc[g * capacity + t] = __fmul_rn((float)s, kq_scale);
-    }
-  }
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const int t0 = (int)(rank * chunk);
+  const int n_t = T > t0 ? (T - t0 < (int)chunk ? T - t0 : (int)chunk) : 0;
+  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+  const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity + t0) * nk + kvh * hd;
+  const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity + t0) * nk + kvh * hd;
+
+  // stage q, K (group 0) and V (group 1) with 16-byte async copies
+  const size_t row16 = hd / 8;  // 16-byte pieces per row
+  for (size_t i = tid; i < group * row16; i += blockDim.x)
+    cp_async16(qs + i * 8, q16 + b * nq + kvh * group * hd + i * 8);
+  for (size_t i = tid; i < (size_t)n_t * row16; i += blockDim.x)
+    cp_async16(kbuf + (i / row16) * kstride + (i % row16) * 16, kbase + (i / row16) * nk + (i % row16) * 8);
+  cp_async_commit();
+  for (size_t i = tid; i < (size_t)n_t * row16; i += blockDim.x)
+    cp_async16(vbuf + i * 16, vbase + (i / row16) * nk + (i % row16) * 8);
+  cp_async_commit();
+  cp_async_wait<1>();
   __syncthreads();
-  // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
-  for (size_t g = warp; g < group; g += nwarp) {
-    float mx = -INFINITY;
-    for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * capacity + t]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    for (int t = lane; t < T; t += 32) sc[g * capacity + t] = exp_cr(__fsub_rn(sc[g * capacity + t], mx));
-    __syncwarp();
-    if (lane == 0) {
-      float sum = 0.0f;
-      for (int t = 0; t < T; t++) sum = __fadd_rn(sum, sc[g * capacity + t]);
-      red[g] = sum;
-    }
-    __syncwarp();
-    const float sum = red[g];
-    for (int t = lane; t < T; t += 32) {
-      float pv = sc[g * capacity + t];
-      if (sum > 0.0f) pv = __fdiv_rn(pv, sum);
-      p16[g * capacity + t] = f32_to_f16_bits(pv);
-    }
-  }
-  __syncthreads();
-  // out[g][d] = f32(sum_f64 v[t][d] * p[g][t])
-  for (size_t o = threadIdx.x; o < group * hd; o += blockDim.x) {
-    const size_t g = o / hd, d = o % hd;
+
+  // scores[g][t] = f32(sum_f64 q*k) * kq_scale, sequential over the head dimension (dot.rs:115-118)
+  for (size_t item = tid; item < (size_t)n_t * group; item += blockDim.x) {
+    const size_t tl = item / group, g = item % group;
+    const uint32_t* kr = reinterpret_cast<const uint32_t*>(kbuf + tl * kstride);
+    const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + g * hd);
     double s = 0.0;
-    for (int t = 0; t < T; t++)
-      s += (double)__fmul_rn(f16_bits_to_f32(vbase[(size_t)t * nk + d]), f16_bits_to_f32(p16[g * capacity + t]));
+    for (size_t i = 0; i < hd / 2; i++) {
+      const uint32_t kk = kr[i], qq = qr[i];
+      s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq & 0xffff)), f16_bits_to_f32((uint16_t)(kk & 0xffff)));
+      s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq >> 16)), f16_bits_to_f32((uint16_t)(kk >> 16)));
+    }
+    const float v = __fmul_rn((float)s, kq_scale);
+    for (unsigned rr = 0; rr < CL; rr++) cluster.map_shared_rank(sc, rr)[g * cs + t0 + tl] = v;
+  }
+  cluster.sync();
+
+  if (n_t > 0) {
+    // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16 for this CTA's steps
+    for (size_t g = warp; g < group; g += nwarp) {
+      float mx = -INFINITY;
+      for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * cs + t]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[g] = mx;
+    }
+    __syncthreads();
+    for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
+      const size_t g = i / T, t = i % T;
+      sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
+    }
+    __syncthreads();
+    for (size_t g = warp; g < group; g += nwarp) {
+      if (lane == 0) {
+        float sum = 0.0f;
+        const float* e = sc + g * cs;
+        for (int t = 0; t < T; t++) sum = __fadd_rn(sum, e[t]);
+        red[g] = sum;
+      }
+    }
+    __syncthreads();
+    for (size_t i = tid; i < group * (size_t)n_t; i += blockDim.x) {
+      const size_t g = i / n_t, tl = i % n_t;
+      float pv = sc[g * cs + t0 + tl];
+      if (red[g] > 0.0f) pv = __fdiv_rn(pv, red[g]);
+      p16[g * chunk + tl] = f32_to_f16_bits(pv);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // partial[g][d] = sum_f64 over this CTA's steps of v[t][d] * p[g][t]  -> rank 0
+  double* part0 = cluster.map_shared_rank(part, 0);
+  for (size_t o = tid; o < group * hd; o += blockDim.x) {
+    const size_t g = o / hd, d = o % hd;
+    const uint16_t* vc = reinterpret_cast<const uint16_t*>(vbuf) + d;
+    const uint16_t* pr = p16 + g * chunk;
+    double s = 0.0;
+    for (int tl = 0; tl < n_t; tl++)
+      s += (double)__fmul_rn(f16_bits_to_f32(vc[(size_t)tl * hd]), f16_bits_to_f32(pr[tl]));
+    part0[(size_t)rank * group * hd + o] = s;
+  }
+  cluster.sync();
+  if (rank != 0) return;
+
+  for (size_t o = tid; o < group * hd; o += blockDim.x) {
+    double s = 0.0;
+    for (unsigned rr = 0; rr < CL; rr++) s += part[(size_t)rr * group * hd + o];
     outv[o] = (float)s;
   }
   __syncthreads();
@@ -296,33 +367,58 @@ int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* 
   return rmi_post_launch(ctx, "qk_norm_rope_kv");
 }
 
+// Cluster size: up to 8 CTAs per (sequence, kv head), at least 16 time steps per CTA.
+static unsigned attention_cluster(const decode_dims& d) {
+  unsigned cl = 1;
+  while (cl < 8 && d.capacity / (cl * 2) >= 16) cl *= 2;
+  return cl;
+}
+
 size_t attention_smem_bytes(const decode_dims& d) {
-  const size_t group = d.n_head / d.n_head_kv;
-  return (group * d.capacity + group * d.hd + 2 * group + 2) * 4 + group * d.capacity * 2 + 16;
+  const size_t group = d.n_head / d.n_head_kv, cl = attention_cluster(d);
+  const size_t chunk = (d.capacity + cl - 1) / cl;
+  size_t b = cl * group * d.hd * 8;                           // partials
+  b += (group * ((d.capacity + 3) & ~(size_t)3) + group * d.hd + ((group + 3) & ~(size_t)3)) * 4;  // scores, out, sums
+  b += (group * d.hd + ((group * chunk + 7) & ~(size_t)7)) * 2;  // q, p
+  b += chunk * (d.hd * 2 + 16) + chunk * d.hd * 2;            // K, V
+  return b + 32;
 }
 
 int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
                          const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                          float* scales) {
+  RMI_REQUIRE(d.hd % 8 == 0 && (d.n_head / d.n_head_kv) * d.hd % 32 == 0, RMI_ERR_UNSUPPORTED,
+              "attention needs head_dim %% 8 == 0 and group*head_dim %% 32 == 0");
   const size_t smem = attention_smem_bytes(d);
-  dim3 grid((unsigned)d.batch, (unsigned)d.n_head_kv);
-#define RMI_ATT(SEMV)                                                                                             \
-  do {                                                                                                            \
-    auto kern = attention_kernel<SEMV>;                                                                           \
-    if (smem > 48 * 1024 &&                                                                                       \
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {      \
-      rmi_set_error("attention needs %zu B of shared memory", smem);                                              \
-      return RMI_ERR_UNSUPPORTED;                                                                                 \
-    }                                                                                                             \
-    kern<<<grid, 256, smem, ctx->stream>>>(q16, k_cache, v_cache, d_step, d.n_head, d.n_head_kv, d.hd, layer,      \
-                                           d.n_layer, d.capacity, attn_out, q8, scales);                          \
-  } while (0)
-  switch (ctx->sem) {
-    case RMI_SEM_AVX2: RMI_ATT(RMI_SEM_AVX2); break;
-    case RMI_SEM_NEON: RMI_ATT(RMI_SEM_NEON); break;
-    default: RMI_ATT(RMI_SEM_SCALAR); break;
+  const unsigned cl = attention_cluster(d);
+  const size_t chunk = (d.capacity + cl - 1) / cl;
+  void (*kern)(const uint16_t*, const uint16_t*, const uint16_t*, const int*, size_t, size_t, size_t, size_t, size_t,
+               size_t, size_t, float*, uint8_t*, float*) =
+      ctx->sem == RMI_SEM_AVX2 ? attention_kernel<RMI_SEM_AVX2>
+                               : (ctx->sem == RMI_SEM_NEON ? attention_kernel<RMI_SEM_NEON> : attention_kernel<RMI_SEM_SCALAR>);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rmi_set_error("attention needs %zu B of shared memory", smem);
+    return RMI_ERR_UNSUPPORTED;
   }
-#undef RMI_ATT
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(d.n_head_kv * cl), (unsigned)d.batch, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cl;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q16, k_cache, v_cache, d_step, d.n_head, d.n_head_kv, d.hd, layer,
+                                     d.n_layer, d.capacity, chunk, attn_out, q8, scales);
+  if (e != cudaSuccess) {
+    rmi_set_error("attention launch failed: %s", cudaGetErrorString(e));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "attention");
 }
 

@@ -9,9 +9,11 @@
 // fresh 128 x NT int32 tile into one of NBUF tensor-memory buffers and the epilogue warps
 // drain it (tcgen05.ld), rescale and accumulate in f32 registers while the next MMAs run.
 //
-// Roles (320 threads): warp 0 = bulk-copy producer (cp.async.bulk into a 4-stage ring of
-// 128-byte K slabs), warp 1 = TMEM owner + single-thread MMA issuer, warps 2..9 = epilogue
-// (warp w may touch TMEM lanes 32*(w%4).., two warps per lane quadrant split the columns).
+// Roles (576 threads): warp 0 = bulk-copy producer (cp.async.bulk into a 4-stage ring of
+// 128-byte K slabs: A image, B image, both scale slabs), warp 1 = TMEM owner + single-thread
+// MMA issuer, warps 2..17 = epilogue (warp w may touch TMEM lanes 32*(w%4).., the four warps
+// of a lane quadrant split the tile columns).  The epilogue math is packed two columns per
+// instruction (mul/fma.rn.f32x2), each half rounded exactly like the scalar instruction.
 //
 // Operands arrive pre-tiled in HBM in the tcgen05 K-major no-swizzle core-matrix order
 // (8 rows x 16 B, LBO = 128 B along K, SBO = 1024 B along rows), so a stage is filled by
@@ -155,6 +157,63 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- packed f32x2 arithmetic (two independent IEEE round-to-nearest operations) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float* lo, float* hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(*lo), "=f"(*hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int* r);
+template <>
+__device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, int* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, int* r) {
+  tmem_ld16(taddr, r);
+}
+template <>
+__device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, int* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+      "[%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+constexpr int EPI_WARPS = 16;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+
 struct __align__(128) smem_layout_hdr {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -164,29 +223,43 @@ struct __align__(128) smem_layout_hdr {
   int abort_flag;
 };
 
+// Per-stage shared memory: A image (16 KiB) | B image (NT*128 B) | weight scales [4][NT] f32 |
+// activation scales [4][128] f32.
+template <int NT>
+struct stage_layout {
+  static constexpr int A = 0;
+  static constexpr int B = SLAB_BYTES_A;
+  static constexpr int WS = B + NT * 128;
+  static constexpr int XS = WS + 4 * NT * 4;
+  static constexpr int BYTES = XS + 4 * 128 * 4;
+};
+
 // NT: tile columns (32, 64, 128).  EPI: GEMM_EPI_*.  SEM: RMI_SEM_NEON or RMI_SEM_SCALAR.
+// For GEMM_EPI_SWIGLU_Q8 (NT = 64) the weight is in the gate/up-interleaved order: rows
+// [64t, 64t+32) are gate columns 32t.., rows [64t+32, 64t+64) the matching up columns.
 template <int NT, int EPI, int SEM>
-__global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const gemm_params p) {
-  constexpr int CPW = NT / 2;              // columns per epilogue warp
-  constexpr int B_STAGE = NT * 128;        // bytes of B per stage
-  constexpr uint32_t TMEM_COLS = NBUF * NT < 32 ? 32 : NBUF * NT;  // 128, 256 or 512 (powers of two)
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p) {
+  using SL = stage_layout<NT>;
+  constexpr int CPW = NT / 4;  // columns per epilogue warp
+  constexpr uint32_t TMEM_COLS = NBUF * NT < 32 ? 32 : NBUF * NT;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   smem_layout_hdr* hdr = reinterpret_cast<smem_layout_hdr*>(smem_raw);
-  uint8_t* stage_a = smem_raw + 1024;
-  uint8_t* stage_b = stage_a + STAGES * SLAB_BYTES_A;
+  uint8_t* stages = smem_raw + 1024;
   volatile int* abort_flag = &hdr->abort_flag;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
   const size_t tile_n = blockIdx.x % p.n_tiles_n, tile_m = blockIdx.x / p.n_tiles_n;
+  const size_t wrow_tile = p.col_begin + tile_n * NT;  // first weight row of this tile
+  constexpr bool kScales = EPI != GEMM_EPI_BLOCK_SUMS;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; i++) {
       mbar_init(&hdr->full[i], 1);
-      mbar_init(&hdr->empty[i], 1);
+      mbar_init(&hdr->empty[i], 1 + EPI_WARPS);
     }
     for (int i = 0; i < NBUF; i++) {
       mbar_init(&hdr->tfull[i], 1);
-      mbar_init(&hdr->tempty[i], 8);
+      mbar_init(&hdr->tempty[i], EPI_WARPS);
     }
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -205,27 +278,23 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const gemm_params p) {
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
+      const uint8_t* bsrc0 = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
+      const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 + (wrow_tile % 128) : nullptr;
+      const float* xs0 = kScales ? p.a_scales + tile_m * p.blocks * 128 : nullptr;
       for (size_t s = 0; s < p.n_slabs; s++) {
         const int st = (int)(s % STAGES);
         const uint32_t ph = (uint32_t)((s / STAGES) & 1);
         if (s >= STAGES && !mbar_wait(&hdr->empty[st], ph ^ 1, abort_flag, p.status, 1, (int)s)) break;
-        mbar_expect_tx(&hdr->full[st], SLAB_BYTES_A + B_STAGE);
-        bulk_g2s(stage_a + st * SLAB_BYTES_A, p.a_img + (tile_m * p.n_slabs + s) * SLAB_BYTES_A, SLAB_BYTES_A,
-                 &hdr->full[st]);
-        uint8_t* bdst = stage_b + st * B_STAGE;
-        if (EPI == GEMM_EPI_SWIGLU_Q8) {
-          // rows: gate[j0..+31], up[j0..+31], gate[j0+32..+63], up[j0+32..+63]
-          const size_t j0 = p.col_begin + tile_n * 64;
-#pragma unroll
-          for (int piece = 0; piece < 4; piece++) {
-            const size_t wr = (piece & 1 ? p.n_ff : 0) + j0 + (piece >> 1) * 32;  // weight row
-            const uint8_t* src = p.b_img + ((wr / 128) * p.n_slabs + s) * SLAB_BYTES_A + ((wr % 128) / 8) * 1024;
-            bulk_g2s(bdst + piece * 4096, src, 4096, &hdr->full[st]);
-          }
-        } else {
-          const size_t wr = p.col_begin + tile_n * NT;
-          const uint8_t* src = p.b_img + ((wr / 128) * p.n_slabs + s) * SLAB_BYTES_A + ((wr % 128) / 8) * 1024;
-          bulk_g2s(bdst, src, B_STAGE, &hdr->full[st]);
+        uint8_t* sb = stages + st * SL::BYTES;
+        const uint32_t kb_n = (uint32_t)(p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4);
+        const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (NT * 4 + 512) : 0);
+        mbar_expect_tx(&hdr->full[st], tx);
+        bulk_g2s(sb + SL::A, p.a_img + (tile_m * p.n_slabs + s) * SLAB_BYTES_A, SLAB_BYTES_A, &hdr->full[st]);
+        bulk_g2s(sb + SL::B, bsrc0 + s * SLAB_BYTES_A, NT * 128, &hdr->full[st]);
+        if (kScales) {
+          for (uint32_t kb = 0; kb < kb_n; kb++)
+            bulk_g2s(sb + SL::WS + kb * NT * 4, ws0 + (s * 4 + kb) * 128, NT * 4, &hdr->full[st]);
+          bulk_g2s(sb + SL::XS, xs0 + s * 4 * 128, kb_n * 512, &hdr->full[st]);
         }
       }
     }
@@ -239,7 +308,7 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const gemm_params p) {
         const int st = (int)(s % STAGES);
         if (!mbar_wait(&hdr->full[st], (uint32_t)((s / STAGES) & 1), abort_flag, p.status, 2, (int)s)) break;
         tc_fence_after();
-        const uint32_t a0 = smem_u32(stage_a + st * SLAB_BYTES_A), b0 = smem_u32(stage_b + st * B_STAGE);
+        const uint32_t a0 = smem_u32(stages + st * SL::BYTES + SL::A), b0 = smem_u32(stages + st * SL::BYTES + SL::B);
         const size_t kb_n = p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4;
         for (size_t kb = 0; kb < kb_n; kb++, g++) {
           const int buf = (int)(g % NBUF);
@@ -252,128 +321,145 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const gemm_params p) {
                   umma_desc(b0 + (uint32_t)kb * 256u), idesc);
           umma_commit(&hdr->tfull[buf]);
         }
-        umma_commit(&hdr->empty[st]);  // smem stage is free once these MMAs have read it
+        umma_commit(&hdr->empty[st]);  // A/B of this stage are free once these MMAs have read them
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (8 warps)
-    const int q = warp % 4;                // TMEM lane quadrant this warp may access
-    const int h = (warp - 2) / 4;          // which half of the tile columns
-    const int r_tile = q * 32 + lane;      // row inside the 128-row tile
+    // ------------------------------------------------------------ epilogue (16 warps)
+    const int q = warp % 4;             // TMEM lane quadrant this warp may access
+    const int cg = (warp - 2) / 4;      // which quarter of the tile columns
+    const int r_tile = q * 32 + lane;   // row inside the 128-row tile
     const size_t row = tile_m * 128 + r_tile;
-    float acc[CPW];
+    const int col0 = cg * CPW;
+    uint64_t acc[CPW / 2];
 #pragma unroll
-    for (int c = 0; c < CPW; c++) acc[c] = 0.0f;
-
-    // weight-scale base pointers: scales are [tile128][block][128 rows]
-    size_t wrow0, wrow1 = 0;  // first weight row of this warp's columns (second: up half)
-    if (EPI == GEMM_EPI_SWIGLU_Q8) {
-      wrow0 = p.col_begin + tile_n * 64 + h * 32;
-      wrow1 = p.n_ff + wrow0;
-    } else {
-      wrow0 = p.col_begin + tile_n * NT + h * CPW;
-    }
-    const float* ws0 = p.b_scales ? p.b_scales + (wrow0 / 128) * p.blocks * 128 + (wrow0 % 128) : nullptr;
-    const float* ws1 = p.b_scales ? p.b_scales + (wrow1 / 128) * p.blocks * 128 + (wrow1 % 128) : nullptr;
-    const float* xsp = p.a_scales ? p.a_scales + tile_m * p.blocks * 128 + r_tile : nullptr;
+    for (int c = 0; c < CPW / 2; c++) acc[c] = 0ull;
 
     bool ok = true;
-    for (size_t g = 0; g < p.blocks && ok; g++) {
-      const int buf = (int)(g % NBUF);
-      float xs = 0.0f;
-      if (EPI != GEMM_EPI_BLOCK_SUMS) xs = __ldg(xsp + g * 128);
-      if (!mbar_wait(&hdr->tfull[buf], (uint32_t)((g / NBUF) & 1), abort_flag, p.status, 4, (int)g)) {
+    size_t g = 0;
+    for (size_t s = 0; s < p.n_slabs && ok; s++) {
+      const int st = (int)(s % STAGES);
+      const uint8_t* sb = stages + st * SL::BYTES;
+      if (kScales && !mbar_wait(&hdr->full[st], (uint32_t)((s / STAGES) & 1), abort_flag, p.status, 5, (int)s)) {
         ok = false;
         break;
       }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NT + h * CPW);
-#pragma unroll
-      for (int c0 = 0; c0 < CPW; c0 += 16) {
-        int d[16];
-        tmem_ld16(taddr + c0, d);
-        tmem_ld_wait();
-        if (c0 + 16 == CPW) {
-          // all TMEM reads of this buffer are complete: hand it back to the MMA warp
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&hdr->tempty[buf]);
+      const size_t kb_n = p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4;
+      for (size_t kb = 0; kb < kb_n; kb++, g++) {
+        const int buf = (int)(g % NBUF);
+        float xs = 0.0f;
+        if (kScales) xs = reinterpret_cast<const float*>(sb + SL::XS)[kb * 128 + r_tile];
+        if (!mbar_wait(&hdr->tfull[buf], (uint32_t)((g / NBUF) & 1), abort_flag, p.status, 4, (int)g)) {
+          ok = false;
+          break;
         }
+        tc_fence_after();
+        int d[CPW];
+        tmem_ld<CPW>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NT + col0), d);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hdr->tempty[buf]);  // TMEM buffer back to the MMA warp
         if (EPI == GEMM_EPI_BLOCK_SUMS) {
           if (row < p.m) {
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-              size_t n = wrow0 + c0 + c;
+            for (int c = 0; c < CPW; c++) {
+              const size_t n = wrow_tile + col0 + c;
               if (n < p.col_end) p.sums[(row * p.n_rows_w + n) * p.blocks + g] = d[c];
             }
           }
         } else {
-          const float* wsp = (EPI == GEMM_EPI_SWIGLU_Q8 && c0 >= 32) ? ws1 + g * 128 + (c0 - 32) : ws0 + g * 128 + c0;
+          const float2* wsp = reinterpret_cast<const float2*>(sb + SL::WS + (kb * NT + col0) * 4);
+          const uint64_t xs2 = pack2(xs, xs);
 #pragma unroll
-          for (int c4 = 0; c4 < 16; c4 += 4) {
-            const float4 wd4 = __ldg(reinterpret_cast<const float4*>(wsp + c4));
-            const float wdv[4] = {wd4.x, wd4.y, wd4.z, wd4.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const float s = __fmul_rn(wdv[j], xs);
-              const float f = small_int_to_f32(d[c4 + j]);
-              if (SEM == RMI_SEM_SCALAR) {
-                acc[c0 + c4 + j] = __fadd_rn(acc[c0 + c4 + j], __fmul_rn(s, f));
-              } else {
-                acc[c0 + c4 + j] = __fmaf_rn(f, s, acc[c0 + c4 + j]);
-              }
+          for (int c = 0; c < CPW / 2; c++) {
+            const float2 wd = wsp[c];
+            const uint64_t s2 = mul2(pack2(wd.x, wd.y), xs2);
+#ifdef RMI_GEMM_MAGIC_CVT
+            const uint64_t f2 = pack2(small_int_to_f32(d[2 * c]), small_int_to_f32(d[2 * c + 1]));
+#else
+            const uint64_t f2 = pack2(__int2float_rn(d[2 * c]), __int2float_rn(d[2 * c + 1]));
+#endif
+            if (SEM == RMI_SEM_SCALAR) {
+              // scalar.rs:55: separate multiply and add.  Written with scalar instructions: the
+              // packed mul/add pair did not reproduce the two roundings on the device.
+              float s_lo, s_hi, f_lo, f_hi, a_lo, a_hi;
+              unpack2(s2, &s_lo, &s_hi);
+              unpack2(f2, &f_lo, &f_hi);
+              unpack2(acc[c], &a_lo, &a_hi);
+              acc[c] = pack2(__fadd_rn(a_lo, __fmul_rn(s_lo, f_lo)), __fadd_rn(a_hi, __fmul_rn(s_hi, f_hi)));
+            } else {
+              acc[c] = fma2(f2, s2, acc[c]);         // neon.rs:69
             }
           }
         }
       }
+      // this warp no longer reads the stage's scale slabs
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&hdr->empty[st]);
     }
 
-    if (ok) {
-      if (EPI == GEMM_EPI_F32) {
-        if (row < p.m) {
-          float* o = p.out + row * p.out_stride + wrow0;
-          if (wrow0 + CPW <= p.col_end && ((p.out_stride | wrow0) & 3) == 0) {
+    if (EPI == GEMM_EPI_F32 && ok) {
+      if (row < p.m) {
+        const size_t n0 = wrow_tile + col0;
+        float* o = p.out + row * p.out_stride + n0;
+        float v[CPW];
 #pragma unroll
-            for (int c = 0; c < CPW; c += 4)
-              *reinterpret_cast<float4*>(o + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
-          } else {
+        for (int c = 0; c < CPW / 2; c++) unpack2(acc[c], &v[2 * c], &v[2 * c + 1]);
+        if (n0 + CPW <= p.col_end && ((p.out_stride | n0) & 3) == 0) {
 #pragma unroll
-            for (int c = 0; c < CPW; c++)
-              if (wrow0 + c < p.col_end) o[c] = acc[c];
-          }
+          for (int c = 0; c < CPW; c += 4) *reinterpret_cast<float4*>(o + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < CPW; c++)
+            if (n0 + c < p.col_end) o[c] = v[c];
         }
-      } else if (EPI == GEMM_EPI_SWIGLU_Q8) {
-        // src/ops/activation/mod.rs:137-151 then src/ops/quant/q8_0.rs (NEON / scalar form):
-        // the 32 columns of this thread are exactly one Q8_0 block of the FFN activation.
-        float v[32];
-        float amax = 0.0f;
+      }
+    }
+    if (EPI == GEMM_EPI_SWIGLU_Q8) {
+      // All MMAs have completed and every stage has been consumed: the stage ring is reused
+      // as a [128][65] f32 exchange buffer (gate columns 0..31, up columns 32..63).
+      float* fin = reinterpret_cast<float*>(stages);
+      epi_bar_sync();  // slower warps may still be reading scale slabs out of the ring
 #pragma unroll
-        for (int c = 0; c < 32; c++) {
-          const float gte = acc[c % CPW], up = acc[(32 + c) % CPW];
-          const float sl = __fdiv_rn(gte, __fadd_rn(1.0f, exp_cr(-gte)));
-          v[c] = __fmul_rn(up, sl);
-          amax = fmaxf(amax, fabsf(v[c]));
+      for (int c = 0; c < CPW / 2; c++) {
+        float a, b;
+        unpack2(acc[c], &a, &b);
+        fin[r_tile * 65 + col0 + 2 * c] = a;
+        fin[r_tile * 65 + col0 + 2 * c + 1] = b;
+      }
+      epi_bar_sync();
+      // src/ops/activation/mod.rs:137-151 then the Q8_0 quantizer: 4 threads per row, 8 columns each;
+      // the tile's 32 activation columns are exactly one Q8_0 block of the FFN activation.
+      const int e = threadIdx.x - 64;
+      const int fr = e / 4, sub = e % 4;
+      float v[8];
+      float amax = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        const float gte = fin[fr * 65 + sub * 8 + c], up = fin[fr * 65 + 32 + sub * 8 + c];
+        const float sl = __fdiv_rn(gte, __fadd_rn(1.0f, exp_cr(-gte)));
+        v[c] = __fmul_rn(up, sl);
+        amax = fmaxf(amax, fabsf(v[c]));
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      float dsc, inv;
+      q8_scale_pair<SEM>(amax, &dsc, &inv);
+      const size_t k0 = (wrow_tile / 64) * 32 + sub * 8;  // column inside n_ff
+      const size_t frow = tile_m * 128 + fr;
+      if (ok) {
+        if (p.act_f32 && frow < p.m) {
+#pragma unroll
+          for (int c = 0; c < 8; c++) p.act_f32[frow * p.n_ff + k0 + c] = v[c];
         }
-        float dsc, inv;
-        q8_scale_pair<SEM>(amax, &dsc, &inv);
-        const size_t k0 = wrow0;  // column index inside n_ff
-        if (p.act_f32 && row < p.m) {
+        uint32_t pk[2] = {0u, 0u};
 #pragma unroll
-          for (int c = 0; c < 32; c++) p.act_f32[row * p.n_ff + k0 + c] = v[c];
-        }
-        uint32_t packed[8];
-#pragma unroll
-        for (int w4 = 0; w4 < 8; w4++) {
-          uint32_t u = 0;
-#pragma unroll
-          for (int j = 0; j < 4; j++) u |= (uint32_t)(uint8_t)(int8_t)q8_quant_value<SEM>(v[w4 * 4 + j], inv) << (8 * j);
-          packed[w4] = u;
-        }
-        const size_t slab = k0 / 128, cc = (k0 % 128) / 16;
-        uint8_t* img = p.act_img + (tile_m * p.act_slabs + slab) * SLAB_BYTES_A + (r_tile / 8) * 1024 + (r_tile % 8) * 16;
-        *reinterpret_cast<uint4*>(img + cc * 128) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        *reinterpret_cast<uint4*>(img + (cc + 1) * 128) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        p.act_scales[(tile_m * p.act_blocks + k0 / 32) * 128 + r_tile] = f16_round_trip(dsc);
+        for (int c = 0; c < 8; c++) pk[c / 4] |= (uint32_t)(uint8_t)(int8_t)q8_quant_value<SEM>(v[c], inv) << (8 * (c % 4));
+        uint8_t* img = p.act_img + (tile_m * p.act_slabs + k0 / 128) * SLAB_BYTES_A + (fr / 8) * 1024 + (fr % 8) * 16 +
+                       ((k0 % 128) / 16) * 128 + (k0 % 16);
+        *reinterpret_cast<uint2*>(img) = make_uint2(pk[0], pk[1]);
+        if (sub == 0) p.act_scales[(tile_m * p.act_blocks + k0 / 32) * 128 + fr] = f16_round_trip(dsc);
       }
     }
   }
@@ -388,7 +474,8 @@ __global__ void __launch_bounds__(320, 1) gemm_tc_kernel(const gemm_params p) {
 
 template <int NT, int EPI>
 int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
-  constexpr size_t smem = 1024 + STAGES * (SLAB_BYTES_A + NT * 128);
+  constexpr size_t smem = 1024 + STAGES * stage_layout<NT>::BYTES;
+  static_assert(EPI != GEMM_EPI_SWIGLU_Q8 || STAGES * stage_layout<NT>::BYTES >= 128 * 65 * 4, "exchange buffer must fit");
   auto kern = ctx->sem == RMI_SEM_SCALAR ? gemm_tc_kernel<NT, EPI, RMI_SEM_SCALAR> : gemm_tc_kernel<NT, EPI, RMI_SEM_NEON>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -397,7 +484,7 @@ int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
   }
   size_t grid = m_tiles * p.n_tiles_n;
   const int pr = rmi_prof_begin(ctx, EPI == GEMM_EPI_SWIGLU_Q8 ? "gemm_tc_swiglu" : "gemm_tc");
-  kern<<<(unsigned)grid, 320, smem, ctx->stream>>>(p);
+  kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(p);
   rmi_prof_end(ctx, pr);
   return rmi_post_launch(ctx, "gemm_tc");
 }
@@ -406,14 +493,16 @@ int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
 
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
   const rmi_weight* w = a.w;
-  RMI_REQUIRE(w->d_umma_q != nullptr, RMI_ERR_BAD_HANDLE, "tcgen05 weight layout was not built");
+  const bool swiglu = a.epilogue == GEMM_EPI_SWIGLU_Q8;
+  RMI_REQUIRE((swiglu ? w->d_umma_gu_q : w->d_umma_q) != nullptr, RMI_ERR_BAD_HANDLE,
+              "tcgen05 weight layout was not built");
   RMI_REQUIRE(ctx->sem != RMI_SEM_AVX2 || a.epilogue == GEMM_EPI_BLOCK_SUMS, RMI_ERR_UNSUPPORTED,
               "the tcgen05 GEMM accumulates whole-block sums (NEON or SCALAR semantics)");
   gemm_params p = {};
   p.a_img = a.a_img;
   p.a_scales = a.a_scales;
-  p.b_img = w->d_umma_q;
-  p.b_scales = w->d_umma_s;
+  p.b_img = swiglu ? w->d_umma_gu_q : w->d_umma_q;
+  p.b_scales = swiglu ? w->d_umma_gu_s : w->d_umma_s;
   p.m = a.m;
   p.n_rows_w = w->n_rows;
   p.blocks = w->n_in / 32;
@@ -431,18 +520,21 @@ int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
   const size_t m_tiles = (a.m + 127) / 128;
   const size_t n_cols = a.col_end - a.col_begin;
   if (a.m == 0 || n_cols == 0) return RMI_OK;
-  if (a.epilogue == GEMM_EPI_SWIGLU_Q8) {
-    RMI_REQUIRE(a.n_ff % 64 == 0 && a.col_begin % 64 == 0 && n_cols % 64 == 0, RMI_ERR_BAD_SHAPE,
-                "fused SwiGLU GEMM needs n_ff and the column range to be multiples of 64");
-    p.n_tiles_n = n_cols / 64;
+  if (swiglu) {
+    // col range is given in FFN columns; a tile of 64 interleaved weight rows covers 32 of them
+    RMI_REQUIRE(a.n_ff % 32 == 0 && a.col_begin % 64 == 0 && n_cols % 32 == 0, RMI_ERR_BAD_SHAPE,
+                "fused SwiGLU GEMM needs n_ff and the column range to be multiples of 32 (start: 64)");
+    p.col_begin = a.col_begin * 2;
+    p.col_end = a.col_end * 2;
+    p.n_tiles_n = n_cols / 32;
     p.act_slabs = (a.n_ff + 127) / 128;
     p.act_blocks = a.n_ff / 32;
-    return launch_nt<128, GEMM_EPI_SWIGLU_Q8>(ctx, p, m_tiles);
+    return launch_nt<64, GEMM_EPI_SWIGLU_Q8>(ctx, p, m_tiles);
   }
   RMI_REQUIRE(a.col_begin % 128 == 0, RMI_ERR_BAD_SHAPE, "column range must start on a multiple of 128");
-  // largest tile width that still gives every SM a tile
+  // largest tile width that still gives every SM about two tiles
   int nt = 128;
-  while (nt > 32 && m_tiles * ((n_cols + nt - 1) / nt) < (size_t)ctx->sm_count) nt >>= 1;
+  while (nt > 32 && m_tiles * ((n_cols + nt - 1) / nt) < 2 * (size_t)ctx->sm_count) nt >>= 1;
   p.n_tiles_n = (n_cols + nt - 1) / nt;
   if (a.epilogue == GEMM_EPI_BLOCK_SUMS) {
     switch (nt) {

@@ -5,7 +5,7 @@
 // q8_0.cu
 int32_t launch_q8_repack_tile16(rmi_ctx* ctx, const uint8_t* raw, uint8_t* dst, size_t n_rows, size_t blocks);
 int32_t launch_q8_copy_rows_tile16(rmi_ctx* ctx, const uint8_t* src, uint8_t* dst, size_t n_rows, size_t blocks, size_t row_off);
-int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, float* us, size_t n_rows, size_t blocks);
+int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, float* us, size_t n_rows, size_t blocks, size_t n_ff_perm);
 int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8, float* scales, int out_mode);
 int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
                        float* out, size_t out_stride, size_t row_begin, size_t row_end);
@@ -33,7 +33,7 @@ struct gemm_tc_args {
   int32_t* sums;         // BLOCK_SUMS: [m][n_rows][blocks]
 };
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
-int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w);
+int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w, bool gate_up_interleaved = false);
 
 // q4k.cu
 int32_t launch_q8k_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, float* d, int8_t* qs, int16_t* bsums);

@@ -47,7 +47,7 @@ __global__ void q8_copy_rows_tile16_kernel(const uint8_t* __restrict__ src, uint
 // tile16 -> tcgen05 K-major core-matrix images + f32 scales [tile128][block][128].
 __global__ void q8_build_umma_kernel(const uint8_t* __restrict__ t16, uint8_t* __restrict__ uq,
                                      float* __restrict__ us, size_t n_rows, size_t blocks,
-                                     size_t n_slabs) {
+                                     size_t n_slabs, size_t n_ff_perm) {
   // one thread per (row, 16-byte chunk)
   size_t chunks = blocks * 2;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -58,10 +58,14 @@ __global__ void q8_build_umma_kernel(const uint8_t* __restrict__ t16, uint8_t* _
   int4 v = make_int4(0, 0, 0, 0);
   size_t b = c_all / 2;
   float s = 0.0f;
-  if (row < n_rows && c_all < chunks) {
-    const uint8_t* rec = t16 + ((row / 16) * blocks + b) * Q8_REC_BYTES;
-    v = *reinterpret_cast<const int4*>(rec + 32 + 32 * (row % 16) + 16 * (c_all & 1));
-    s = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(rec + 2 * (row % 16)));
+  // n_ff_perm != 0: destination rows [64t,64t+32) take gate rows 32t.., [64t+32,64t+64) the up
+  // rows n_ff+32t.. of the v-stacked source
+  size_t srow = row;
+  if (n_ff_perm) srow = (row % 64 < 32) ? (row / 64) * 32 + row % 64 : n_ff_perm + (row / 64) * 32 + (row % 64 - 32);
+  if (row < n_rows && srow < n_rows && c_all < chunks) {
+    const uint8_t* rec = t16 + ((srow / 16) * blocks + b) * Q8_REC_BYTES;
+    v = *reinterpret_cast<const int4*>(rec + 32 + 32 * (srow % 16) + 16 * (c_all & 1));
+    s = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(rec + 2 * (srow % 16)));
   }
   size_t tile = row / 128, r = row % 128;
   uint8_t* img = uq + (tile * n_slabs + slab) * 16384;
@@ -299,12 +303,12 @@ int32_t launch_q8_copy_rows_tile16(rmi_ctx* ctx, const uint8_t* src, uint8_t* ds
 }
 
 int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, float* us, size_t n_rows,
-                             size_t blocks) {
+                             size_t blocks, size_t n_ff_perm) {
   size_t n_slabs = (blocks * 32 + 127) / 128;
   size_t rows_pad = (n_rows + 127) / 128 * 128;
   size_t n = rows_pad * n_slabs * 8;
   if (n == 0) return RMI_OK;
-  q8_build_umma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(t16, uq, us, n_rows, blocks, n_slabs);
+  q8_build_umma_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(t16, uq, us, n_rows, blocks, n_slabs, n_ff_perm);
   return rmi_post_launch(ctx, "q8_build_umma");
 }
 
