@@ -6,8 +6,9 @@
 //   SCALAR  sum += (wd*xs) * f32(dot)           src/ops/kernel/q8_0/scalar.rs:42-56
 //
 // tcgen05.mma.kind::i8 has K = 32 per instruction = one Q8_0 block, so every MMA writes a
-// fresh 128 x NT int32 tile into one of NBUF tensor-memory buffers and the epilogue warps
-// drain it (tcgen05.ld), rescale and accumulate in f32 registers while the next MMAs run.
+// fresh 128 x NT int32 tile into tensor memory (two buffers of four blocks each) and the
+// epilogue warps drain it (tcgen05.ld), rescale and accumulate in f32 registers while the
+// MMAs of the next K slab run.
 //
 // Roles (576 threads): warp 0 = bulk-copy producer (cp.async.bulk into a 4-stage ring of
 // 128-byte K slabs: A image, B image, both scale slabs), warp 1 = TMEM owner + single-thread
@@ -69,14 +70,16 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One try: the hardware may suspend the thread for up to `hint_ns` before returning false,
+// which keeps waiting warps from burning issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 20000) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
@@ -94,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint64_t t0 = 0;
   for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255) == 255) {
+    if ((i & 15) == 15) {
       if (*abort_flag) return false;
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
@@ -234,22 +237,75 @@ struct stage_layout {
   static constexpr int BYTES = XS + 4 * 128 * 4;
 };
 
-// NT: tile columns (32, 64, 128).  EPI: GEMM_EPI_*.  SEM: RMI_SEM_NEON or RMI_SEM_SCALAR.
+// Out-of-line slow path of a wait: keeps polling with the time limit, records the failure.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
+                                            rmi_dev_status* status, int site, int detail) {
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity), "r"(20000u)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > WAIT_NS) break;
+  }
+  *abort_flag = 1;
+  if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
+    status->where = site;
+    status->detail = detail;
+  }
+  return false;
+}
+
+// Hot path of a bounded wait: one try (the hardware suspends the thread until the phase
+// completes or a time slice passes), then the slow path.
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
+                                            rmi_dev_status* status, int site, int detail) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_addr), "r"(parity), "r"(20000u)
+      : "memory");
+  if (ok) return true;
+  return mbar_wait_slow(bar_addr, parity, abort_flag, status, site, detail);
+}
+
+__device__ __forceinline__ void mbar_arrive_a(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+
+// NT: tile columns (32 or 64).  EPI: GEMM_EPI_*.  SEM: RMI_SEM_NEON or RMI_SEM_SCALAR.
+// Tensor memory holds two slab buffers of four K-blocks each (2 * 4 * NT columns): the MMA
+// warp fills one slab buffer (four MMAs, one commit) while the epilogue drains the other,
+// so barriers are exchanged once per 128-byte K slab instead of once per block.
 // For GEMM_EPI_SWIGLU_Q8 (NT = 64) the weight is in the gate/up-interleaved order: rows
 // [64t, 64t+32) are gate columns 32t.., rows [64t+32, 64t+64) the matching up columns.
 template <int NT, int EPI, int SEM>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p) {
   using SL = stage_layout<NT>;
   constexpr int CPW = NT / 4;  // columns per epilogue warp
-  constexpr uint32_t TMEM_COLS = NBUF * NT < 32 ? 32 : NBUF * NT;
+  constexpr uint32_t TMEM_COLS = 8 * NT;
+  static_assert(TMEM_COLS <= 512 && CPW >= 8, "tile width must be 32 or 64");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   smem_layout_hdr* hdr = reinterpret_cast<smem_layout_hdr*>(smem_raw);
   uint8_t* stages = smem_raw + 1024;
   volatile int* abort_flag = &hdr->abort_flag;
+  const uint32_t full_a = smem_u32(&hdr->full[0]), empty_a = smem_u32(&hdr->empty[0]);
+  const uint32_t tfull_a = smem_u32(&hdr->tfull[0]), tempty_a = smem_u32(&hdr->tempty[0]);
+  const uint32_t stages_a = smem_u32(stages);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
-  const size_t tile_n = blockIdx.x % p.n_tiles_n, tile_m = blockIdx.x / p.n_tiles_n;
-  const size_t wrow_tile = p.col_begin + tile_n * NT;  // first weight row of this tile
+  const int tile_n = (int)(blockIdx.x % p.n_tiles_n), tile_m = (int)(blockIdx.x / p.n_tiles_n);
+  const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;  // first weight row of this tile
+  const int n_slabs = (int)p.n_slabs, blocks = (int)p.blocks;
   constexpr bool kScales = EPI != GEMM_EPI_BLOCK_SUMS;
 
   if (threadIdx.x == 0) {
@@ -257,7 +313,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       mbar_init(&hdr->full[i], 1);
       mbar_init(&hdr->empty[i], 1 + EPI_WARPS);
     }
-    for (int i = 0; i < NBUF; i++) {
+    for (int i = 0; i < 2; i++) {
       mbar_init(&hdr->tfull[i], 1);
       mbar_init(&hdr->tempty[i], EPI_WARPS);
     }
@@ -280,21 +336,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     if (lane == 0) {
       const uint8_t* bsrc0 = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
       const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 + (wrow_tile % 128) : nullptr;
-      const float* xs0 = kScales ? p.a_scales + tile_m * p.blocks * 128 : nullptr;
-      for (size_t s = 0; s < p.n_slabs; s++) {
-        const int st = (int)(s % STAGES);
-        const uint32_t ph = (uint32_t)((s / STAGES) & 1);
-        if (s >= STAGES && !mbar_wait(&hdr->empty[st], ph ^ 1, abort_flag, p.status, 1, (int)s)) break;
+      const float* xs0 = kScales ? p.a_scales + (size_t)tile_m * p.blocks * 128 : nullptr;
+      const uint8_t* asrc0 = p.a_img + (size_t)tile_m * p.n_slabs * SLAB_BYTES_A;
+      for (int s = 0; s < n_slabs; s++) {
+        const int st = s % STAGES;
+        if (s >= STAGES && !mbar_wait_a(empty_a + 8 * st, ((s / STAGES) & 1) ^ 1, abort_flag, p.status, 1, s)) break;
         uint8_t* sb = stages + st * SL::BYTES;
-        const uint32_t kb_n = (uint32_t)(p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4);
+        const uint32_t kb_n = (uint32_t)(blocks - s * 4 < 4 ? blocks - s * 4 : 4);
         const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (NT * 4 + 512) : 0);
         mbar_expect_tx(&hdr->full[st], tx);
-        bulk_g2s(sb + SL::A, p.a_img + (tile_m * p.n_slabs + s) * SLAB_BYTES_A, SLAB_BYTES_A, &hdr->full[st]);
-        bulk_g2s(sb + SL::B, bsrc0 + s * SLAB_BYTES_A, NT * 128, &hdr->full[st]);
+        bulk_g2s(sb + SL::A, asrc0 + (size_t)s * SLAB_BYTES_A, SLAB_BYTES_A, &hdr->full[st]);
+        bulk_g2s(sb + SL::B, bsrc0 + (size_t)s * SLAB_BYTES_A, NT * 128, &hdr->full[st]);
         if (kScales) {
           for (uint32_t kb = 0; kb < kb_n; kb++)
-            bulk_g2s(sb + SL::WS + kb * NT * 4, ws0 + (s * 4 + kb) * 128, NT * 4, &hdr->full[st]);
-          bulk_g2s(sb + SL::XS, xs0 + s * 4 * 128, kb_n * 512, &hdr->full[st]);
+            bulk_g2s(sb + SL::WS + kb * NT * 4, ws0 + (size_t)(s * 4 + kb) * 128, NT * 4, &hdr->full[st]);
+          bulk_g2s(sb + SL::XS, xs0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
         }
       }
     }
@@ -302,26 +358,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8<NT>();
-      size_t g = 0;
-      bool ok = true;
-      for (size_t s = 0; s < p.n_slabs && ok; s++) {
-        const int st = (int)(s % STAGES);
-        if (!mbar_wait(&hdr->full[st], (uint32_t)((s / STAGES) & 1), abort_flag, p.status, 2, (int)s)) break;
+      for (int s = 0; s < n_slabs; s++) {
+        const int st = s % STAGES, tb = s & 1;
+        if (!mbar_wait_a(full_a + 8 * st, (s / STAGES) & 1, abort_flag, p.status, 2, s)) break;
+        if (s >= 2 && !mbar_wait_a(tempty_a + 8 * tb, ((s >> 1) & 1) ^ 1, abort_flag, p.status, 3, s)) break;
         tc_fence_after();
-        const uint32_t a0 = smem_u32(stages + st * SL::BYTES + SL::A), b0 = smem_u32(stages + st * SL::BYTES + SL::B);
-        const size_t kb_n = p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4;
-        for (size_t kb = 0; kb < kb_n; kb++, g++) {
-          const int buf = (int)(g % NBUF);
-          if (g >= NBUF && !mbar_wait(&hdr->tempty[buf], (uint32_t)(((g / NBUF) & 1) ^ 1), abort_flag, p.status, 3, (int)g)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          umma_i8(tmem_base + (uint32_t)(buf * NT), umma_desc(a0 + (uint32_t)kb * 256u),
+        const uint32_t a0 = stages_a + st * SL::BYTES + SL::A, b0 = stages_a + st * SL::BYTES + SL::B;
+        const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
+        for (int kb = 0; kb < kb_n; kb++)
+          umma_i8(tmem_base + (uint32_t)((tb * 4 + kb) * NT), umma_desc(a0 + (uint32_t)kb * 256u),
                   umma_desc(b0 + (uint32_t)kb * 256u), idesc);
-          umma_commit(&hdr->tfull[buf]);
-        }
-        umma_commit(&hdr->empty[st]);  // A/B of this stage are free once these MMAs have read them
+        umma_commit(&hdr->tfull[tb]);  // the slab's accumulators are complete
+        umma_commit(&hdr->empty[st]);  // A/B of this stage have been read
       }
     }
   } else {
@@ -329,74 +377,83 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     const int q = warp % 4;             // TMEM lane quadrant this warp may access
     const int cg = (warp - 2) / 4;      // which quarter of the tile columns
     const int r_tile = q * 32 + lane;   // row inside the 128-row tile
-    const size_t row = tile_m * 128 + r_tile;
+    const size_t row = (size_t)tile_m * 128 + r_tile;
     const int col0 = cg * CPW;
+    const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
     uint64_t acc[CPW / 2];
 #pragma unroll
     for (int c = 0; c < CPW / 2; c++) acc[c] = 0ull;
 
     bool ok = true;
-    size_t g = 0;
-    for (size_t s = 0; s < p.n_slabs && ok; s++) {
-      const int st = (int)(s % STAGES);
+    for (int s = 0; s < n_slabs; s++) {
+      const int st = s % STAGES, tb = s & 1;
       const uint8_t* sb = stages + st * SL::BYTES;
-      if (kScales && !mbar_wait(&hdr->full[st], (uint32_t)((s / STAGES) & 1), abort_flag, p.status, 5, (int)s)) {
+      const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
+      // tfull[tb] completes after the MMAs of slab s, which were issued after full[st] completed;
+      // waiting on full[st] as well makes the bulk-copied scale slabs visible to this thread.
+      if (kScales && !mbar_wait_a(full_a + 8 * st, (s / STAGES) & 1, abort_flag, p.status, 5, s)) {
         ok = false;
         break;
       }
-      const size_t kb_n = p.blocks - s * 4 < 4 ? p.blocks - s * 4 : 4;
-      for (size_t kb = 0; kb < kb_n; kb++, g++) {
-        const int buf = (int)(g % NBUF);
-        float xs = 0.0f;
-        if (kScales) xs = reinterpret_cast<const float*>(sb + SL::XS)[kb * 128 + r_tile];
-        if (!mbar_wait(&hdr->tfull[buf], (uint32_t)((g / NBUF) & 1), abort_flag, p.status, 4, (int)g)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        int d[CPW];
-        tmem_ld<CPW>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NT + col0), d);
+      if (!mbar_wait_a(tfull_a + 8 * tb, (s >> 1) & 1, abort_flag, p.status, 4, s)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        int d[2][CPW];
+        tmem_ld<CPW>(tmem_lane + (uint32_t)((tb * 4 + half * 2) * NT), d[0]);
+        tmem_ld<CPW>(tmem_lane + (uint32_t)((tb * 4 + half * 2 + 1) * NT), d[1]);
         tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&hdr->tempty[buf]);  // TMEM buffer back to the MMA warp
-        if (EPI == GEMM_EPI_BLOCK_SUMS) {
-          if (row < p.m) {
+        if (half == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_a(tempty_a + 8 * tb);  // slab buffer back to the MMA warp
+        }
 #pragma unroll
-            for (int c = 0; c < CPW; c++) {
-              const size_t n = wrow_tile + col0 + c;
-              if (n < p.col_end) p.sums[(row * p.n_rows_w + n) * p.blocks + g] = d[c];
-            }
-          }
-        } else {
-          const float2* wsp = reinterpret_cast<const float2*>(sb + SL::WS + (kb * NT + col0) * 4);
-          const uint64_t xs2 = pack2(xs, xs);
+        for (int j = 0; j < 2; j++) {
+          const int kb = half * 2 + j;
+          if (kb < kb_n) {
+            if (EPI == GEMM_EPI_BLOCK_SUMS) {
+              if (row < p.m) {
 #pragma unroll
-          for (int c = 0; c < CPW / 2; c++) {
-            const float2 wd = wsp[c];
-            const uint64_t s2 = mul2(pack2(wd.x, wd.y), xs2);
-#ifdef RMI_GEMM_MAGIC_CVT
-            const uint64_t f2 = pack2(small_int_to_f32(d[2 * c]), small_int_to_f32(d[2 * c + 1]));
-#else
-            const uint64_t f2 = pack2(__int2float_rn(d[2 * c]), __int2float_rn(d[2 * c + 1]));
-#endif
-            if (SEM == RMI_SEM_SCALAR) {
-              // scalar.rs:55: separate multiply and add.  Written with scalar instructions: the
-              // packed mul/add pair did not reproduce the two roundings on the device.
-              float s_lo, s_hi, f_lo, f_hi, a_lo, a_hi;
-              unpack2(s2, &s_lo, &s_hi);
-              unpack2(f2, &f_lo, &f_hi);
-              unpack2(acc[c], &a_lo, &a_hi);
-              acc[c] = pack2(__fadd_rn(a_lo, __fmul_rn(s_lo, f_lo)), __fadd_rn(a_hi, __fmul_rn(s_hi, f_hi)));
+                for (int c = 0; c < CPW; c++) {
+                  const size_t n = wrow_tile + col0 + c;
+                  if (n < p.col_end) p.sums[(row * p.n_rows_w + n) * p.blocks + (size_t)(s * 4 + kb)] = d[j][c];
+                }
+              }
             } else {
-              acc[c] = fma2(f2, s2, acc[c]);         // neon.rs:69
+              const float xs = reinterpret_cast<const float*>(sb + SL::XS)[kb * 128 + r_tile];
+              const uint64_t* wsp = reinterpret_cast<const uint64_t*>(sb + SL::WS + (kb * NT + col0) * 4);
+              const uint64_t xs2 = pack2(xs, xs);
+#pragma unroll
+              for (int c = 0; c < CPW / 2; c++) {
+                const uint64_t s2 = mul2(wsp[c], xs2);
+#ifdef RMI_GEMM_MAGIC_CVT
+                const uint64_t f2 = pack2(small_int_to_f32(d[j][2 * c]), small_int_to_f32(d[j][2 * c + 1]));
+#else
+                const uint64_t f2 = pack2(__int2float_rn(d[j][2 * c]), __int2float_rn(d[j][2 * c + 1]));
+#endif
+                if (SEM == RMI_SEM_SCALAR) {
+                  // scalar.rs:55: separate multiply and add.  Written with scalar instructions: the
+                  // packed mul/add pair did not reproduce the two roundings on the device.
+                  float s_lo, s_hi, f_lo, f_hi, a_lo, a_hi;
+                  unpack2(s2, &s_lo, &s_hi);
+                  unpack2(f2, &f_lo, &f_hi);
+                  unpack2(acc[c], &a_lo, &a_hi);
+                  acc[c] = pack2(__fadd_rn(a_lo, __fmul_rn(s_lo, f_lo)), __fadd_rn(a_hi, __fmul_rn(s_hi, f_hi)));
+                } else {
+                  acc[c] = fma2(f2, s2, acc[c]);  // neon.rs:69
+                }
+              }
             }
           }
         }
       }
       // this warp no longer reads the stage's scale slabs
       __syncwarp();
-      if (lane == 0) mbar_arrive(&hdr->empty[st]);
+      if (lane == 0) mbar_arrive_a(empty_a + 8 * st);
     }
 
     if (EPI == GEMM_EPI_F32 && ok) {
@@ -447,7 +504,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       float dsc, inv;
       q8_scale_pair<SEM>(amax, &dsc, &inv);
       const size_t k0 = (wrow_tile / 64) * 32 + sub * 8;  // column inside n_ff
-      const size_t frow = tile_m * 128 + fr;
+      const size_t frow = (size_t)tile_m * 128 + fr;
       if (ok) {
         if (p.act_f32 && frow < p.m) {
 #pragma unroll
@@ -456,10 +513,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         uint32_t pk[2] = {0u, 0u};
 #pragma unroll
         for (int c = 0; c < 8; c++) pk[c / 4] |= (uint32_t)(uint8_t)(int8_t)q8_quant_value<SEM>(v[c], inv) << (8 * (c % 4));
-        uint8_t* img = p.act_img + (tile_m * p.act_slabs + k0 / 128) * SLAB_BYTES_A + (fr / 8) * 1024 + (fr % 8) * 16 +
-                       ((k0 % 128) / 16) * 128 + (k0 % 16);
+        uint8_t* img = p.act_img + ((size_t)tile_m * p.act_slabs + k0 / 128) * SLAB_BYTES_A + (fr / 8) * 1024 +
+                       (fr % 8) * 16 + ((k0 % 128) / 16) * 128 + (k0 % 16);
         *reinterpret_cast<uint2*>(img) = make_uint2(pk[0], pk[1]);
-        if (sub == 0) p.act_scales[(tile_m * p.act_blocks + k0 / 32) * 128 + fr] = f16_round_trip(dsc);
+        if (sub == 0) p.act_scales[((size_t)tile_m * p.act_blocks + k0 / 32) * 128 + fr] = f16_round_trip(dsc);
       }
     }
   }
@@ -532,20 +589,14 @@ int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
     return launch_nt<64, GEMM_EPI_SWIGLU_Q8>(ctx, p, m_tiles);
   }
   RMI_REQUIRE(a.col_begin % 128 == 0, RMI_ERR_BAD_SHAPE, "column range must start on a multiple of 128");
-  // largest tile width that still gives every SM about two tiles
-  int nt = 128;
-  while (nt > 32 && m_tiles * ((n_cols + nt - 1) / nt) < 2 * (size_t)ctx->sm_count) nt >>= 1;
+  // 64-column tiles unless that leaves SMs without work
+  int nt = 64;
+  if (m_tiles * ((n_cols + nt - 1) / nt) < 2 * (size_t)ctx->sm_count) nt = 32;
   p.n_tiles_n = (n_cols + nt - 1) / nt;
   if (a.epilogue == GEMM_EPI_BLOCK_SUMS) {
-    switch (nt) {
-      case 128: return launch_nt<128, GEMM_EPI_BLOCK_SUMS>(ctx, p, m_tiles);
-      case 64: return launch_nt<64, GEMM_EPI_BLOCK_SUMS>(ctx, p, m_tiles);
-      default: return launch_nt<32, GEMM_EPI_BLOCK_SUMS>(ctx, p, m_tiles);
-    }
+    if (nt == 64) return launch_nt<64, GEMM_EPI_BLOCK_SUMS>(ctx, p, m_tiles);
+    return launch_nt<32, GEMM_EPI_BLOCK_SUMS>(ctx, p, m_tiles);
   }
-  switch (nt) {
-    case 128: return launch_nt<128, GEMM_EPI_F32>(ctx, p, m_tiles);
-    case 64: return launch_nt<64, GEMM_EPI_F32>(ctx, p, m_tiles);
-    default: return launch_nt<32, GEMM_EPI_F32>(ctx, p, m_tiles);
-  }
+  if (nt == 64) return launch_nt<64, GEMM_EPI_F32>(ctx, p, m_tiles);
+  return launch_nt<32, GEMM_EPI_F32>(ctx, p, m_tiles);
 }
