@@ -20,6 +20,9 @@
 // (8 rows x 16 B, LBO = 128 B along K, SBO = 1024 B along rows), so a stage is filled by
 // contiguous bulk copies and no tensor map is needed.
 //
+// The kernel is persistent: one CTA per SM walks the output tiles, the barrier phases run on
+// across tiles, so the bulk copies and MMAs of the next tile overlap the tail of the current one.
+//
 // Every wait is bounded: after two seconds of failed polls a role records a site id in the
 // context's status word, raises a shared abort flag that all other waits observe, and the
 // CTA falls through to the common teardown (TMEM is always deallocated).
@@ -49,6 +52,7 @@ struct gemm_params {
   float* act_f32;
   int32_t* sums;
   size_t n_tiles_n;
+  size_t n_tiles;  // m_tiles * n_tiles_n; CTAs walk tiles blockIdx.x, +gridDim.x, ...
   size_t act_slabs, act_blocks;
   rmi_dev_status* status;
 };
@@ -303,8 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
   const uint32_t stages_a = smem_u32(stages);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x & 31;
-  const int tile_n = (int)(blockIdx.x % p.n_tiles_n), tile_m = (int)(blockIdx.x / p.n_tiles_n);
-  const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;  // first weight row of this tile
+  const int n_tiles = (int)p.n_tiles, n_tiles_n = (int)p.n_tiles_n;
   const int n_slabs = (int)p.n_slabs, blocks = (int)p.blocks;
   constexpr bool kScales = EPI != GEMM_EPI_BLOCK_SUMS;
 
@@ -334,13 +337,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
+      int gs = 0;  // slabs issued so far (all tiles)
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
+      const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
       const uint8_t* bsrc0 = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
       const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 + (wrow_tile % 128) : nullptr;
       const float* xs0 = kScales ? p.a_scales + (size_t)tile_m * p.blocks * 128 : nullptr;
       const uint8_t* asrc0 = p.a_img + (size_t)tile_m * p.n_slabs * SLAB_BYTES_A;
-      for (int s = 0; s < n_slabs; s++) {
-        const int st = s % STAGES;
-        if (s >= STAGES && !mbar_wait_a(empty_a + 8 * st, ((s / STAGES) & 1) ^ 1, abort_flag, p.status, 1, s)) break;
+      for (int s = 0; s < n_slabs; s++, gs++) {
+        const int st = gs % STAGES;
+        if (gs >= STAGES && !mbar_wait_a(empty_a + 8 * st, ((gs / STAGES) & 1) ^ 1, abort_flag, p.status, 1, s)) {
+          tile = n_tiles;
+          break;
+        }
         uint8_t* sb = stages + st * SL::BYTES;
         const uint32_t kb_n = (uint32_t)(blocks - s * 4 < 4 ? blocks - s * 4 : 4);
         const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (NT * 4 + 512) : 0);
@@ -353,15 +363,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
           bulk_g2s(sb + SL::XS, xs0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
         }
       }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8<NT>();
-      for (int s = 0; s < n_slabs; s++) {
-        const int st = s % STAGES, tb = s & 1;
-        if (!mbar_wait_a(full_a + 8 * st, (s / STAGES) & 1, abort_flag, p.status, 2, s)) break;
-        if (s >= 2 && !mbar_wait_a(tempty_a + 8 * tb, ((s >> 1) & 1) ^ 1, abort_flag, p.status, 3, s)) break;
+      int gs = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x)
+      for (int s = 0; s < n_slabs; s++, gs++) {
+        const int st = gs % STAGES, tb = gs & 1;
+        if (!mbar_wait_a(full_a + 8 * st, (gs / STAGES) & 1, abort_flag, p.status, 2, s) ||
+            (gs >= 2 && !mbar_wait_a(tempty_a + 8 * tb, ((gs >> 1) & 1) ^ 1, abort_flag, p.status, 3, s))) {
+          tile = n_tiles;
+          break;
+        }
         tc_fence_after();
         const uint32_t a0 = stages_a + st * SL::BYTES + SL::A, b0 = stages_a + st * SL::BYTES + SL::B;
         const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
@@ -377,25 +393,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     const int q = warp % 4;             // TMEM lane quadrant this warp may access
     const int cg = (warp - 2) / 4;      // which quarter of the tile columns
     const int r_tile = q * 32 + lane;   // row inside the 128-row tile
-    const size_t row = (size_t)tile_m * 128 + r_tile;
     const int col0 = cg * CPW;
     const uint32_t tmem_lane = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
+    bool ok = true;
+    int gs = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
+    const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
+    const size_t row = (size_t)tile_m * 128 + r_tile;
     uint64_t acc[CPW / 2];
 #pragma unroll
     for (int c = 0; c < CPW / 2; c++) acc[c] = 0ull;
 
-    bool ok = true;
-    for (int s = 0; s < n_slabs; s++) {
-      const int st = s % STAGES, tb = s & 1;
+    for (int s = 0; s < n_slabs; s++, gs++) {
+      const int st = gs % STAGES, tb = gs & 1;
       const uint8_t* sb = stages + st * SL::BYTES;
       const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
       // tfull[tb] completes after the MMAs of slab s, which were issued after full[st] completed;
       // waiting on full[st] as well makes the bulk-copied scale slabs visible to this thread.
-      if (kScales && !mbar_wait_a(full_a + 8 * st, (s / STAGES) & 1, abort_flag, p.status, 5, s)) {
+      if (kScales && !mbar_wait_a(full_a + 8 * st, (gs / STAGES) & 1, abort_flag, p.status, 5, s)) {
         ok = false;
         break;
       }
-      if (!mbar_wait_a(tfull_a + 8 * tb, (s >> 1) & 1, abort_flag, p.status, 4, s)) {
+      if (!mbar_wait_a(tfull_a + 8 * tb, (gs >> 1) & 1, abort_flag, p.status, 4, s)) {
         ok = false;
         break;
       }
@@ -474,10 +494,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       }
     }
     if (EPI == GEMM_EPI_SWIGLU_Q8) {
-      // All MMAs have completed and every stage has been consumed: the stage ring is reused
-      // as a [128][65] f32 exchange buffer (gate columns 0..31, up columns 32..63).
-      float* fin = reinterpret_cast<float*>(stages);
-      epi_bar_sync();  // slower warps may still be reading scale slabs out of the ring
+      // [128][65] f32 exchange buffer behind the stage ring (gate columns 0..31, up columns 32..63)
+      float* fin = reinterpret_cast<float*>(stages + STAGES * SL::BYTES);
+      epi_bar_sync();  // the previous tile's readers are done with the buffer
+      if (*abort_flag) ok = false;  // read after the barrier: every epilogue warp leaves at the same tile
 #pragma unroll
       for (int c = 0; c < CPW / 2; c++) {
         float a, b;
@@ -519,6 +539,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         if (sub == 0) p.act_scales[((size_t)tile_m * p.act_blocks + k0 / 32) * 128 + fr] = f16_round_trip(dsc);
       }
     }
+    }  // tile loop
   }
 
   tc_fence_before();
@@ -531,17 +552,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
 
 template <int NT, int EPI>
 int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
-  constexpr size_t smem = 1024 + STAGES * stage_layout<NT>::BYTES;
-  static_assert(EPI != GEMM_EPI_SWIGLU_Q8 || STAGES * stage_layout<NT>::BYTES >= 128 * 65 * 4, "exchange buffer must fit");
+  constexpr size_t smem = 1024 + STAGES * stage_layout<NT>::BYTES + (EPI == GEMM_EPI_SWIGLU_Q8 ? 128 * 65 * 4 : 0);
   auto kern = ctx->sem == RMI_SEM_SCALAR ? gemm_tc_kernel<NT, EPI, RMI_SEM_SCALAR> : gemm_tc_kernel<NT, EPI, RMI_SEM_NEON>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed: %s", smem, cudaGetErrorString(e));
     return RMI_ERR_CUDA;
   }
-  size_t grid = m_tiles * p.n_tiles_n;
+  gemm_params pp = p;
+  pp.n_tiles = m_tiles * p.n_tiles_n;
+  size_t grid = pp.n_tiles < (size_t)ctx->sm_count ? pp.n_tiles : (size_t)ctx->sm_count;
   const int pr = rmi_prof_begin(ctx, EPI == GEMM_EPI_SWIGLU_Q8 ? "gemm_tc_swiglu" : "gemm_tc");
-  kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(p);
+  kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(pp);
   rmi_prof_end(ctx, pr);
   return rmi_post_launch(ctx, "gemm_tc");
 }
