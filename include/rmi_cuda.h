@@ -139,6 +139,16 @@ int32_t rmi_matmul_q8_0_prequantized_dev(rmi_ctx* ctx, const rmi_weight* w, cons
 int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
 int32_t rmi_matmul_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
                             float* output);
+/* No counterpart in the reference.  Same result as rmi_matmul_q8_0_dev for m <= 32, but the call
+ * allocates nothing: the quantized activations live in a 576 KiB array compiled into the library
+ * (held by every GPU that loads it) instead of context scratch obtained with cudaMalloc.  It is
+ * meant for hosts whose own allocator already owns all device memory, or whose loops cannot take
+ * the device-wide synchronisation of cudaMalloc/cudaFree.  Limits: m <= 32 and m * n_in <= 524288
+ * (RMI_ERR_BAD_SHAPE beyond that); per-kernel timing must be off.  The first call on a device
+ * resolves the array's address, so issue it before any stream capture begins.  All calls on a
+ * device share the array: calls that overlap on the GPU race, the caller orders them. */
+int32_t rmi_matmul_q8_0_dev_noalloc(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                    float* output);
 /* Exact int32 dot of every 32-block, sums[(t*n_rows + r)*(n_in/32) + b]; debug/parity aid
  * with no counterpart in the reference API (it is the integer part of
  * src/ops/kernel/q8_0/scalar.rs:49-55).  use_tensor_cores != 0 routes through the

@@ -421,6 +421,12 @@ def matmul_q8_0_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
     _check(lib().rmi_matmul_q8_0_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m), C.c_void_p(out_ptr)))
 
 
+def matmul_q8_0_dev_noalloc(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    """Allocation-free variant of matmul_q8_0_dev (m <= 32, m * n_in <= 524288): see include/rmi_cuda.h."""
+    _check(lib().rmi_matmul_q8_0_dev_noalloc(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m),
+                                             C.c_void_p(out_ptr)))
+
+
 def matmul_q8_0_prequantized_dev(weight: QuantizedTensor, q8_ptr: int, scales_ptr: int, m: int, out_ptr: int,
                                  row_begin: int = 0, row_end: int | None = None):
     row_end = weight.n_out if row_end is None else row_end
