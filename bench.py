@@ -200,6 +200,54 @@ def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem):
     return res, toks
 
 
+def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak):
+    """BASELINE config 5: W [32768, 8192] Q8_0 sharded by row across the ranks, x [M, 8192] replicated,
+    all-gather of [M, 32768] f32.  One JSON line with per-M device times (max over ranks)."""
+    n, k = 32768, 8192
+    ctx.set_semantics(pkg.SEM_NEON)
+    s, e = pkg.sharding.shard_rows(n, world, rank)
+    lin = pkg.sharding.ShardedLinear(pkg, pkg.synth.q8_0_weight_rows(n, k, seed=0, row_begin=s, row_end=e), k, n, rank, world)
+    results = {}
+    for m in (1, 16, 256, 4096):
+        x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
+        out_local = torch.empty((m, n // world), dtype=torch.float32, device="cuda")
+        gathered = torch.empty((world, m, n // world), dtype=torch.float32, device="cuda")
+        out_full = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        iters = max(3, min(args.steps, 50 if m <= 256 else 10))
+        times = {}
+        for mode in ("local", "gathered"):
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    lin.forward_dev(x, out_local, gathered if mode == "gathered" else None, out_full)
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(iters):
+                    lin.forward_dev(x, out_local, gathered if mode == "gathered" else None, out_full)
+                e1.record(stream)
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times[mode] = float(t.item())
+        w_bytes = (n // world) * (k // 32) * 34
+        ops = 2.0 * m * k * n
+        results[f"M={m}"] = {"ms_local": times["local"], "ms_with_allgather": times["gathered"],
+                             "per_gpu_weight_gbs": w_bytes / (times["local"] / 1e3) / 1e9,
+                             "frac_of_hbm_peak": w_bytes / (times["local"] / 1e3) / 1e9 / hbm_peak,
+                             "whole_job_tops": ops / (times["local"] / 1e3) / 1e12,
+                             "allgather_bytes_in_per_gpu": (world - 1) * m * (n // world) * 4}
+    if rank == 0:
+        print(json.dumps({"metric": "sharded Q8_0 GEMM sweep (N=32768,K=8192), rows split across GPUs + all-gather",
+                          "n_gpus": world, "scaling": "strong", "dtype": "int8", "data": "synthetic",
+                          "config": {"workload": "configs[4]: sharded Q8_0 GEMM sweep", "semantics": "neon"},
+                          "results": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -209,6 +257,8 @@ def main():
     ap.add_argument("--threads", type=int, default=0, help="CPU threads of the reference arm / cpu baseline (0 = all)")
     ap.add_argument("--semantics", default="neon", choices=["neon", "scalar", "avx2"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary figures (GEMV, decode)")
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded"],
+                    help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -233,6 +283,11 @@ def main():
     ctx.set_stream(stream.cuda_stream)
     hbm_peak, bf16_peak, bf16_sus, peak_kind = measured_peaks()
     sm_count, l2_bytes, _ = ctx.device_info()
+    if args.workload == "sharded":
+        run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # R distinct weight/input/output sets, > L2 in total, rotated every step
     g, u, d = ffn_weights_bytes(pkg)

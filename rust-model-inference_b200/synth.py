@@ -52,6 +52,23 @@ def q8_0_weight(n: int, k: int, seed: int, std: float = 0.02) -> np.ndarray:
     return out
 
 
+def q8_0_weight_rows(n: int, k: int, seed: int, row_begin: int, row_end: int, std: float = 0.02,
+                     chunk: int = 1024) -> np.ndarray:
+    """Rows [row_begin,row_end) of an [n,k] matrix whose row chunk c is drawn from
+    default_rng([seed, c]): every rank can generate exactly its shard of the same matrix."""
+    rb = k // 32 * 34
+    out = np.empty((row_end - row_begin) * rb, np.uint8)
+    r = row_begin
+    while r < row_end:
+        c = r // chunk
+        lo, hi = c * chunk, min((c + 1) * chunk, n)
+        w = np.random.default_rng([seed, c]).standard_normal((hi - lo, k), dtype=np.float32) * np.float32(std)
+        take_hi = min(hi, row_end)
+        out[(r - row_begin) * rb:(take_hi - row_begin) * rb] = encode_q8_0(w[r - lo:take_hi - lo])
+        r = take_hi
+    return out
+
+
 def q4_k_weight(n: int, k: int, seed: int) -> np.ndarray:
     """A valid Q4_K super-block stream [n, k/256, 144]: uniform random 6-bit scales/mins and
     nibbles with f16 d/dmin sized so decoded weights have roughly N(0,0.02) spread.  Parity

@@ -1,0 +1,111 @@
+// The reference's own Q8Kernel unit tests (src/ops/kernel/q8_0/mod.rs:58-157) and the Q4_K
+// known answer (tests/quantized_inference.rs:233-249), written against the C++ mirror of the
+// trait and run on the device.  Exit code 0 = all passed.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "../../rust-model-inference_b200/host/rmi_kernel.hpp"
+
+static int failures = 0;
+#define EXPECT(cond)                                         \
+  do {                                                       \
+    if (!(cond)) {                                           \
+      std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); \
+      failures++;                                            \
+    }                                                        \
+  } while (0)
+
+static uint16_t f16_bits(float v) {  // exact for the powers of two used here
+  uint32_t u;
+  std::memcpy(&u, &v, 4);
+  return (uint16_t)(((u >> 16) & 0x8000) | ((((u >> 23) & 0xff) - 112) << 10) | ((u >> 13) & 0x3ff));
+}
+
+static std::vector<uint8_t> q8_0_uniform_row(int8_t value, float scale) {
+  std::vector<uint8_t> row(34, (uint8_t)value);
+  uint16_t b = f16_bits(scale);
+  std::memcpy(row.data(), &b, 2);
+  return row;
+}
+
+int main() {
+  try {
+    std::vector<uint8_t> q8(32, 1);
+    std::vector<float> sc(1, 1.0f);
+    {  // q8_kernel_uniform_weights_sum_to_dot_product / multi_row / scale_applied
+      auto w = q8_0_uniform_row(1, 1.0f);
+      rmi::Q8Kernel k(w.data(), w.size(), 32, 1);
+      float out[1] = {0};
+      k.forward_prequantized(q8.data(), sc.data(), out, 32, 1, 0, 1);
+      EXPECT(out[0] == 32.0f);
+      auto w2 = w;
+      w2.insert(w2.end(), w.begin(), w.end());
+      rmi::Q8Kernel k2(w2.data(), w2.size(), 32, 2);
+      float out2[2] = {0, 0};
+      k2.forward_prequantized(q8.data(), sc.data(), out2, 32, 2, 0, 1);
+      EXPECT(out2[0] == 32.0f && out2[1] == 32.0f);
+      auto wh = q8_0_uniform_row(1, 0.5f);
+      rmi::Q8Kernel k3(wh.data(), wh.size(), 32, 1);
+      k3.forward_prequantized(q8.data(), sc.data(), out, 32, 1, 0, 1);
+      EXPECT(out[0] == 16.0f);
+      // q8_kernel_forward_quantizes_internally
+      std::vector<float> ones(32, 1.0f);
+      k.forward(ones.data(), out, 32, 1);
+      EXPECT(std::fabs(out[0] - 32.0f) < 5e-3f);
+    }
+    {  // q8_kernel_thread_partition
+      std::vector<uint8_t> w;
+      for (int i = 0; i < 4; i++) {
+        auto r = q8_0_uniform_row(1, 1.0f);
+        w.insert(w.end(), r.begin(), r.end());
+      }
+      rmi::Q8Kernel k(w.data(), w.size(), 32, 4);
+      float a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+      k.forward_prequantized(q8.data(), sc.data(), a, 32, 4, 0, 2);
+      k.forward_prequantized(q8.data(), sc.data(), b, 32, 4, 1, 2);
+      EXPECT(a[0] == 32.0f && a[1] == 32.0f && a[2] == 0.0f && a[3] == 0.0f);
+      EXPECT(b[0] == 0.0f && b[1] == 0.0f && b[2] == 32.0f && b[3] == 32.0f);
+      // forward_batched == per-token forward, bit for bit
+      std::vector<float> x(3 * 32), o1(12), o2(12);
+      for (size_t i = 0; i < x.size(); i++) x[i] = 0.013f * (float)i - 1.0f;
+      k.forward_batched(x.data(), 3, o1.data(), 32, 4);
+      for (int t = 0; t < 3; t++) k.forward(x.data() + 32 * t, o2.data() + 4 * t, 32, 4);
+      EXPECT(std::memcmp(o1.data(), o2.data(), 48) == 0);
+    }
+    {  // q4_k_kernel_multiplies_uniform_block + QuantizedLinear
+      std::vector<uint8_t> w(144, 0);
+      uint16_t one = f16_bits(1.0f);
+      std::memcpy(w.data(), &one, 2);
+      const uint8_t scales[12] = {1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1};
+      std::memcpy(w.data() + 4, scales, 12);
+      std::memset(w.data() + 16, 0x11, 128);
+      rmi::Q4_KKernel k(w.data(), w.size(), 256, 1);
+      std::vector<uint8_t> q(256, 1);
+      std::vector<float> s(8, 1.0f);
+      float out[1] = {0};
+      k.forward_prequantized(q.data(), s.data(), out, 256, 1, 0, 1);
+      EXPECT(out[0] == 256.0f);
+      auto lin = rmi::QuantizedLinear::from_weight_slice(w.data(), w.size(), 256, 1, "uniform");
+      std::vector<float> ones(256, 1.0f);
+      lin.forward(ones.data(), out);
+      EXPECT(out[0] == 256.0f && lin.input_dim() == 256 && lin.output_dim() == 1 && lin.name() == "uniform");
+    }
+    {  // error convention: shape errors surface as exceptions with the library's status code
+      bool threw = false;
+      try {
+        std::vector<uint8_t> w(34);
+        rmi::Q8Kernel bad(w.data(), w.size(), 33, 1);
+      } catch (const rmi::Error& e) {
+        threw = e.status == RMI_ERR_BAD_SHAPE;
+      }
+      EXPECT(threw);
+    }
+  } catch (const std::exception& e) {
+    std::printf("FAIL exception: %s\n", e.what());
+    failures++;
+  }
+  std::printf(failures ? "%d failure(s)\n" : "all kernel-trait checks passed\n", failures);
+  return failures ? 1 : 0;
+}
