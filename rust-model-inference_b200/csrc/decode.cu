@@ -276,46 +276,73 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// First maximal index per sequence; raises *flag when a logit is not finite.
-__global__ void argmax_kernel(const float* __restrict__ logits, size_t vocab, const int* __restrict__ d_step,
-                              size_t n_prompt, uint32_t* __restrict__ gen, size_t n_gen, int* __restrict__ flag) {
-  __shared__ float s_v[32];
-  __shared__ uint32_t s_i[32];
-  const size_t b = blockIdx.x;
-  const float* l = logits + b * vocab;
-  float best = -INFINITY;
-  uint32_t bi = 0xffffffffu;
-  bool bad = false;
-  for (size_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = l[i];
-    if (!isfinite(v)) bad = true;
-    if (v > best || (v == best && (uint32_t)i < bi)) {
-      best = v;
-      bi = (uint32_t)i;
-    }
+// Greedy token in two stages: ARGMAX_SLICES CTAs per sequence each reduce a slice of the logits to
+// (value, first index), then one CTA per sequence combines the slices.  Larger value wins, equal
+// values keep the lower index (first maximum); a non-finite logit raises *flag.
+constexpr int ARGMAX_SLICES = 64;
+
+__device__ __forceinline__ void argmax_combine(float& best, uint32_t& bi, float ov, uint32_t oi) {
+  if (ov > best || (ov == best && oi < bi)) {
+    best = ov;
+    bi = oi;
   }
-  if (bad) atomicExch(flag, 1);
+}
+
+__device__ __forceinline__ void argmax_block_reduce(float& best, uint32_t& bi, float* s_v, uint32_t* s_i) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
+    argmax_combine(best, bi, ov, oi);
   }
   if (lane == 0) {
     s_v[warp] = best;
     s_i[warp] = bi;
   }
   __syncthreads();
+  if (threadIdx.x == 0)
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_combine(best, bi, s_v[w], s_i[w]);
+}
+
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, size_t vocab, float* __restrict__ part_v,
+                                      uint32_t* __restrict__ part_i, int* __restrict__ flag) {
+  __shared__ float s_v[32];
+  __shared__ uint32_t s_i[32];
+  const size_t b = blockIdx.y, slice = blockIdx.x;
+  const size_t per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+  const size_t lo = slice * per, hi = lo + per < vocab ? lo + per : vocab;
+  const float* l = logits + b * vocab;
+  float best = -INFINITY;
+  uint32_t bi = 0xffffffffu;
+  bool bad = false;
+  for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = l[i];
+    if (!isfinite(v)) bad = true;
+    argmax_combine(best, bi, v, (uint32_t)i);
+  }
+  if (bad) atomicExch(flag, 1);
+  argmax_block_reduce(best, bi, s_v, s_i);
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); w++)
-      if (s_v[w] > best || (s_v[w] == best && s_i[w] < bi)) {
-        best = s_v[w];
-        bi = s_i[w];
-      }
+    part_v[b * ARGMAX_SLICES + slice] = best;
+    part_i[b * ARGMAX_SLICES + slice] = bi;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const uint32_t* __restrict__ part_i,
+                                    const int* __restrict__ d_step, size_t n_prompt, uint32_t* __restrict__ gen,
+                                    size_t n_gen) {
+  __shared__ float s_v[32];
+  __shared__ uint32_t s_i[32];
+  const size_t b = blockIdx.x;
+  float best = -INFINITY;
+  uint32_t bi = 0xffffffffu;
+  if (threadIdx.x < ARGMAX_SLICES) {
+    best = part_v[b * ARGMAX_SLICES + threadIdx.x];
+    bi = part_i[b * ARGMAX_SLICES + threadIdx.x];
+  }
+  argmax_block_reduce(best, bi, s_v, s_i);
+  if (threadIdx.x == 0) {
     const int step = *d_step;
     const size_t gi = (size_t)step + 1 - n_prompt;  // step >= n_prompt-1 when this kernel runs
     if (gi < n_gen) gen[b * n_gen + gi] = bi == 0xffffffffu ? 0u : bi;
@@ -422,10 +449,15 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
   return rmi_post_launch(ctx, "attention");
 }
 
+size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }
+
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
-                      size_t n_gen, int* flag, size_t batch) {
-  argmax_kernel<<<(unsigned)batch, 1024, 0, ctx->stream>>>(logits, vocab, d_step, n_prompt, gen, n_gen, flag);
-  return rmi_post_launch(ctx, "argmax");
+                      size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i) {
+  dim3 grid(ARGMAX_SLICES, (unsigned)batch);
+  argmax_partial_kernel<<<grid, 256, 0, ctx->stream>>>(logits, vocab, part_v, part_i, flag);
+  RMI_TRY(rmi_post_launch(ctx, "argmax_partial"));
+  argmax_final_kernel<<<(unsigned)batch, 64, 0, ctx->stream>>>(part_v, part_i, d_step, n_prompt, gen, n_gen);
+  return rmi_post_launch(ctx, "argmax_final");
 }
 
 int32_t launch_step_inc(rmi_ctx* ctx, int* d_step) {

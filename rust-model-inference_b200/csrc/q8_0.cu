@@ -111,7 +111,89 @@ __global__ void q8_quantize_kernel(const float* __restrict__ x, size_t m, size_t
 // ---------------------------------------------------------------- GEMV
 
 // LB bytes of each row's 32-byte block per lane; a warp covers LB rows of one 16-row tile.
-// MP activation rows are processed per pass with the weights read once.
+// MP activation rows are processed per pass with the weights read once.  Weights are fetched
+// in register batches of U blocks, two batches in flight (the next one is requested before the
+// current one is consumed), so a warp keeps 2*U*32*LB bytes outstanding.
+template <int LB>
+struct gemv_batch {
+  static constexpr int NL = LB / 4;
+  static constexpr int U = LB == 16 ? 4 : (LB == 8 ? 8 : 16);
+  int wq[U][NL];
+  uint16_t wd[U];
+};
+
+template <int LB>
+__device__ __forceinline__ void gemv_load_batch(gemv_batch<LB>& t, const uint8_t* qp, const uint8_t* sp, size_t b0,
+                                                size_t blocks) {
+  constexpr int U = gemv_batch<LB>::U;
+#pragma unroll
+  for (int u = 0; u < U; u++) {
+    if (b0 + u < blocks) {
+      const uint8_t* p = qp + (b0 + u) * Q8_REC_BYTES;
+      if constexpr (LB == 16) {
+        const int4 v = __ldg(reinterpret_cast<const int4*>(p));
+        t.wq[u][0] = v.x; t.wq[u][1] = v.y; t.wq[u][2] = v.z; t.wq[u][3] = v.w;
+      } else if constexpr (LB == 8) {
+        const int2 v = __ldg(reinterpret_cast<const int2*>(p));
+        t.wq[u][0] = v.x; t.wq[u][1] = v.y;
+      } else {
+        t.wq[u][0] = __ldg(reinterpret_cast<const int*>(p));
+      }
+      t.wd[u] = __ldg(reinterpret_cast<const uint16_t*>(sp + (b0 + u) * Q8_REC_BYTES));
+    }
+  }
+}
+
+template <int SEM, int LB, int MP>
+__device__ __forceinline__ void gemv_consume_batch(const gemv_batch<LB>& t, size_t b0, size_t blocks, const int8_t* xq_s,
+                                                   const float* xs_s, size_t K, int part,
+                                                   float (&acc)[MP][SEM == RMI_SEM_AVX2 ? LB / 4 : 1]) {
+  constexpr int U = gemv_batch<LB>::U, NL = LB / 4, LPR = 32 / LB;
+#pragma unroll
+  for (int u = 0; u < U; u++) {
+    if (b0 + u < blocks) {
+      const size_t b = b0 + u;
+      const float wd = f16_bits_to_f32(t.wd[u]);
+#pragma unroll
+      for (int m = 0; m < MP; m++) {
+        const int* xp = reinterpret_cast<const int*>(xq_s + m * K + b * 32 + part * LB);
+        int xv[NL];
+        if constexpr (LB == 16) {
+          const int4 v = *reinterpret_cast<const int4*>(xp);
+          xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+        } else if constexpr (LB == 8) {
+          const int2 v = *reinterpret_cast<const int2*>(xp);
+          xv[0] = v.x; xv[1] = v.y;
+        } else {
+          xv[0] = *xp;
+        }
+        const float da = __fmul_rn(wd, xs_s[m * blocks + b]);
+        if constexpr (SEM == RMI_SEM_AVX2) {
+          // avx2.rs:96-148: eight partial sums of four products, one FMA each
+#pragma unroll
+          for (int j = 0; j < NL; j++) {
+            const int p = dp4a_s8(t.wq[u][j], xv[j], 0x4B400000);
+            const float f = __fsub_rn(__int_as_float(p), 12582912.0f);
+            acc[m][j] = __fmaf_rn(da, f, acc[m][j]);
+          }
+        } else {
+          int dot = 0;
+#pragma unroll
+          for (int j = 0; j < NL; j++) dot = dp4a_s8(t.wq[u][j], xv[j], dot);
+#pragma unroll
+          for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          const float f = small_int_to_f32(dot);
+          if constexpr (SEM == RMI_SEM_NEON) {
+            acc[m][0] = __fmaf_rn(f, da, acc[m][0]);  // neon.rs:69
+          } else {
+            acc[m][0] = __fadd_rn(acc[m][0], __fmul_rn(da, f));  // scalar.rs:55
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int SEM, int LB, int MP>
 __global__ void __launch_bounds__(256)
     q8_gemv_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
@@ -120,20 +202,15 @@ __global__ void __launch_bounds__(256)
   constexpr int LPR = 32 / LB;      // lanes per row
   constexpr int NL = LB / 4;        // AVX2 lanes (dp4a groups) per thread
   constexpr int WPT = 16 / LB;      // warps per 16-row tile
-  constexpr int U = LB == 16 ? 4 : 8;
+  constexpr int U = gemv_batch<LB>::U;
   extern __shared__ __align__(16) uint8_t smem[];
   const size_t K = blocks * 32;
   int8_t* xq_s = reinterpret_cast<int8_t*>(smem);
   float* xs_s = reinterpret_cast<float*>(smem + MP * K);
-
-  // stage the quantized activations (shared by every row)
-  {
-    const int4* src = reinterpret_cast<const int4*>(xq);
-    int4* dst = reinterpret_cast<int4*>(xq_s);
-    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = src[i];
-    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = xs[i];
-  }
-  __syncthreads();
+  // blockIdx.y selects a group of MP activation rows: all groups stream the weights concurrently
+  xq += (size_t)blockIdx.y * MP * K;
+  xs += (size_t)blockIdx.y * MP * blocks;
+  out += (size_t)blockIdx.y * MP * out_stride;
 
   const int lane = threadIdx.x & 31;
   const size_t gw = (size_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
@@ -142,11 +219,22 @@ __global__ void __launch_bounds__(256)
   const int rit = sub * LB + lane / LPR;  // row in tile
   const int part = lane % LPR;
   const size_t row = tile * 16 + rit;
-  if (tile * 16 >= row_end) return;  // whole warp out of range (uniform)
-
+  const bool active = tile * 16 < row_end;  // warp-uniform
   const uint8_t* rec0 = w + tile * blocks * Q8_REC_BYTES;
   const uint8_t* qp = rec0 + 32 + rit * 32 + part * LB;
   const uint8_t* sp = rec0 + 2 * rit;
+
+  // first weight batch is requested before the activations are staged
+  gemv_batch<LB> ba, bb;
+  if (active) gemv_load_batch<LB>(ba, qp, sp, 0, blocks);
+  {
+    const int4* src = reinterpret_cast<const int4*>(xq);
+    int4* dst = reinterpret_cast<int4*>(xq_s);
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+  }
+  __syncthreads();
+  if (!active) return;
 
   float acc[MP][SEM == RMI_SEM_AVX2 ? NL : 1];
 #pragma unroll
@@ -154,58 +242,11 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int j = 0; j < (SEM == RMI_SEM_AVX2 ? NL : 1); j++) acc[m][j] = 0.0f;
 
-  for (size_t b0 = 0; b0 < blocks; b0 += U) {
-    int wq[U][NL];
-    uint16_t wd_bits[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      if (b0 + u < blocks) {
-        const uint8_t* p = qp + (b0 + u) * Q8_REC_BYTES;
-        if (LB == 16) {
-          int4 v = __ldg(reinterpret_cast<const int4*>(p));
-          wq[u][0] = v.x; wq[u][NL > 1 ? 1 : 0] = v.y; wq[u][NL > 2 ? 2 : 0] = v.z; wq[u][NL > 3 ? 3 : 0] = v.w;
-        } else if (LB == 8) {
-          int2 v = __ldg(reinterpret_cast<const int2*>(p));
-          wq[u][0] = v.x; wq[u][NL > 1 ? 1 : 0] = v.y;
-        } else {
-          wq[u][0] = __ldg(reinterpret_cast<const int*>(p));
-        }
-        wd_bits[u] = __ldg(reinterpret_cast<const uint16_t*>(sp + (b0 + u) * Q8_REC_BYTES));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      if (b0 + u < blocks) {
-        const size_t b = b0 + u;
-        const float wd = f16_bits_to_f32(wd_bits[u]);
-#pragma unroll
-        for (int m = 0; m < MP; m++) {
-          const int* xp = reinterpret_cast<const int*>(xq_s + m * K + b * 32 + part * LB);
-          const float da = __fmul_rn(wd, xs_s[m * blocks + b]);
-          if (SEM == RMI_SEM_AVX2) {
-            // avx2.rs:96-148: eight partial sums of four products, one FMA each
-#pragma unroll
-            for (int j = 0; j < NL; j++) {
-              int p = dp4a_s8(wq[u][j], xp[j], 0x4B400000);
-              float f = __fsub_rn(__int_as_float(p), 12582912.0f);
-              acc[m][j] = __fmaf_rn(da, f, acc[m][j]);
-            }
-          } else {
-            int dot = 0;
-#pragma unroll
-            for (int j = 0; j < NL; j++) dot = dp4a_s8(wq[u][j], xp[j], dot);
-#pragma unroll
-            for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            float f = small_int_to_f32(dot);
-            if (SEM == RMI_SEM_NEON) {
-              acc[m][0] = __fmaf_rn(f, da, acc[m][0]);  // neon.rs:69
-            } else {
-              acc[m][0] = __fadd_rn(acc[m][0], __fmul_rn(da, f));  // scalar.rs:55
-            }
-          }
-        }
-      }
-    }
+  for (size_t b0 = 0; b0 < blocks; b0 += 2 * U) {
+    if (b0 + U < blocks) gemv_load_batch<LB>(bb, qp, sp, b0 + U, blocks);
+    gemv_consume_batch<SEM, LB, MP>(ba, b0, blocks, xq_s, xs_s, K, part, acc);
+    if (b0 + 2 * U < blocks) gemv_load_batch<LB>(ba, qp, sp, b0 + 2 * U, blocks);
+    if (b0 + U < blocks) gemv_consume_batch<SEM, LB, MP>(bb, b0 + U, blocks, xq_s, xs_s, K, part, acc);
   }
 
 #pragma unroll
@@ -327,7 +368,7 @@ int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uin
 
 template <int SEM, int LB, int MP>
 static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
-                               float* out, size_t out_stride, size_t row_begin, size_t row_end) {
+                               float* out, size_t out_stride, size_t row_begin, size_t row_end, size_t n_groups) {
   const size_t blocks = w->n_in / 32;
   const size_t first_tile = row_begin / 16;
   const size_t last_tile = (row_end + 15) / 16;
@@ -342,8 +383,8 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
     }
   }
   // fewer warps per CTA when the problem is small so that more SMs take part
-  int wpc = warps >= (size_t)ctx->sm_count * 16 ? 8 : (warps >= (size_t)ctx->sm_count * 4 ? 4 : 2);
-  unsigned grid = (unsigned)((warps + wpc - 1) / wpc);
+  int wpc = warps * n_groups >= (size_t)ctx->sm_count * 8 ? 4 : 2;
+  dim3 grid((unsigned)((warps + wpc - 1) / wpc), (unsigned)n_groups);
   const int pr = rmi_prof_begin(ctx, "q8_gemv");
   kern<<<grid, wpc * 32, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin,
                                               row_end, first_tile);
@@ -351,7 +392,20 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
   return rmi_post_launch(ctx, "q8_gemv");
 }
 
-template <int SEM, int LB>
+template <int SEM, int MP>
+static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, float* out,
+                                size_t out_stride, size_t row_begin, size_t row_end, size_t n_groups) {
+  // Enough warps to keep every SM streaming: a pass over MP activation rows does MP times the
+  // arithmetic per weight byte, so fewer (fatter) warps are needed as MP grows.
+  const size_t tiles = ((row_end + 15) / 16 - row_begin / 16) * n_groups;
+  const size_t per_sm = MP >= 8 ? 6 : (MP >= 4 ? 8 : 16);
+  const size_t want = (size_t)ctx->sm_count * per_sm;
+  if (tiles >= want) return gemv_launch_one<SEM, 16, MP>(ctx, w, xq, xs, out, out_stride, row_begin, row_end, n_groups);
+  if (tiles * 2 >= want) return gemv_launch_one<SEM, 8, MP>(ctx, w, xq, xs, out, out_stride, row_begin, row_end, n_groups);
+  return gemv_launch_one<SEM, 4, MP>(ctx, w, xq, xs, out, out_stride, row_begin, row_end, n_groups);
+}
+
+template <int SEM>
 static int32_t gemv_dispatch_mp(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
                                 size_t m, float* out, size_t out_stride, size_t row_begin,
                                 size_t row_end) {
@@ -366,40 +420,30 @@ static int32_t gemv_dispatch_mp(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
     size_t left = m - t;
     size_t mp = left >= 8 ? 8 : (left >= 4 ? 4 : (left >= 2 ? 2 : 1));
     if (mp > max_mp) mp = max_mp;
+    const size_t groups = left / mp;  // all full groups of this width in one launch
     const uint8_t* q = xq + t * w->n_in;
     const float* s = xs + t * blocks;
     float* o = out + t * out_stride;
     int32_t st;
     switch (mp) {
-      case 8: st = gemv_launch_one<SEM, LB, 8>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
-      case 4: st = gemv_launch_one<SEM, LB, 4>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
-      case 2: st = gemv_launch_one<SEM, LB, 2>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
-      default: st = gemv_launch_one<SEM, LB, 1>(ctx, w, q, s, o, out_stride, row_begin, row_end); break;
+      case 8: st = gemv_dispatch_lb<SEM, 8>(ctx, w, q, s, o, out_stride, row_begin, row_end, groups); break;
+      case 4: st = gemv_dispatch_lb<SEM, 4>(ctx, w, q, s, o, out_stride, row_begin, row_end, groups); break;
+      case 2: st = gemv_dispatch_lb<SEM, 2>(ctx, w, q, s, o, out_stride, row_begin, row_end, groups); break;
+      default: st = gemv_dispatch_lb<SEM, 1>(ctx, w, q, s, o, out_stride, row_begin, row_end, groups); break;
     }
     if (st != RMI_OK) return st;
-    t += mp;
+    t += mp * groups;
   }
   return RMI_OK;
-}
-
-template <int SEM>
-static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs,
-                                size_t m, float* out, size_t out_stride, size_t row_begin,
-                                size_t row_end) {
-  const size_t tiles = (row_end + 15) / 16 - row_begin / 16;
-  const size_t want = (size_t)ctx->sm_count * 16;  // warps that keep every SM streaming
-  if (tiles >= want) return gemv_dispatch_mp<SEM, 16>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
-  if (tiles * 2 >= want) return gemv_dispatch_mp<SEM, 8>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
-  return gemv_dispatch_mp<SEM, 4>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
 }
 
 int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
                        float* out, size_t out_stride, size_t row_begin, size_t row_end) {
   if (row_begin >= row_end || m == 0) return RMI_OK;
   switch (ctx->sem) {
-    case RMI_SEM_AVX2: return gemv_dispatch_lb<RMI_SEM_AVX2>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
-    case RMI_SEM_NEON: return gemv_dispatch_lb<RMI_SEM_NEON>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
-    default: return gemv_dispatch_lb<RMI_SEM_SCALAR>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+    case RMI_SEM_AVX2: return gemv_dispatch_mp<RMI_SEM_AVX2>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+    case RMI_SEM_NEON: return gemv_dispatch_mp<RMI_SEM_NEON>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
+    default: return gemv_dispatch_mp<RMI_SEM_SCALAR>(ctx, w, xq, xs, m, out, out_stride, row_begin, row_end);
   }
 }
 

@@ -49,6 +49,8 @@ struct rmi_session {
   uint32_t *prompts, *gen;
   size_t prompts_cap, gen_cap;
   int *d_step, *d_flag;
+  float* argmax_v;
+  uint32_t* argmax_i;
   cudaGraph_t graph_body, graph_full;
   cudaGraphExec_t exec_body, exec_full;
   size_t graph_n_prompt, graph_n_gen;
@@ -265,6 +267,8 @@ static void free_session(rmi_session* s) {
   cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8);
   cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
   cudaFree(s->attn_dbg);
+  cudaFree(s->argmax_v);
+  cudaFree(s->argmax_i);
   s->magic = 0;
   delete s;
 }
@@ -330,6 +334,8 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->d_step, 4);
   SESSION_ALLOC(s->d_flag, 4);
   SESSION_ALLOC(s->attn_dbg, batch * nq * 4);
+  SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
+  SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   cudaMemset(s->k_cache, 0, kv);
   cudaMemset(s->v_cache, 0, kv);
   // rope_neox (src/ops/rope.rs:21-37): theta_0 = pos, theta_{i+1} = theta_i * base^(-2/d) in f32,
@@ -381,7 +387,7 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   RMI_TRY(launch_rmsnorm_quant(ctx, s->x, pending, m->output_norm, d.n_embd, d.eps, s->q8, s->xs, B));
   if (with_logits) {
     RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
-    RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B));
+    RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i));
   }
   return launch_step_inc(ctx, s->d_step);
 }
@@ -466,13 +472,13 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
   // steps 0 .. n_prompt+n_gen-2 (src/models/qwen3.rs:118-126); logits from step n_prompt-1 on
   const size_t steps = n_prompt + n_gen - 1;
   // kernels per graph: the GEMV launcher issues one kernel per pass of 8/4/2/1 activation rows
-  uint64_t passes = d.batch / 8;
-  for (size_t rem = d.batch % 8, p2 = 4; p2 >= 1; p2 >>= 1)
+  uint64_t passes = 0;
+  for (size_t rem = d.batch, p2 = 8; p2 >= 1; p2 >>= 1)
     if (rem >= p2) {
       passes++;
-      rem -= p2;
+      rem %= p2;
     }
-  const uint64_t launches_per_body = 3 + d.n_layer * (5 + 4 * passes), launches_full = launches_per_body + passes + 1;
+  const uint64_t launches_per_body = 3 + d.n_layer * (5 + 4 * passes), launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;
   for (size_t st = 0; st < steps && ce == cudaSuccess; st++) {
