@@ -278,6 +278,121 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ---------------------------------------------------------------- GEMV, small problems
+
+// Latency-bound shapes (a few hundred 16-row tiles): one CTA of 128 threads per tile fetches the
+// tile's whole record stream (blocks * 544 contiguous bytes) with a single bulk async copy, so
+// the tile costs one memory round trip; thread (row r, lane l) then runs the reference's
+// per-lane chain over the blocks out of shared memory.
+template <int SEM, int MP>
+__global__ void __launch_bounds__(128)
+    q8_gemv_staged_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
+                          const float* __restrict__ xs, float* __restrict__ out, size_t out_stride, size_t row_begin,
+                          size_t row_end, size_t first_tile, rmi_dev_status* status) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const size_t K = blocks * 32;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
+  uint8_t* wt = smem + 128;                                   // [blocks][544]
+  int8_t* xq_s = reinterpret_cast<int8_t*>(wt + blocks * Q8_REC_BYTES);  // [MP][K]
+  float* xs_s = reinterpret_cast<float*>(xq_s + MP * K);      // [MP][blocks]
+  xq += (size_t)blockIdx.y * MP * K;
+  xs += (size_t)blockIdx.y * MP * blocks;
+  out += (size_t)blockIdx.y * MP * out_stride;
+  const size_t tile = first_tile + blockIdx.x;
+  const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bar);
+  const uint32_t bytes = (uint32_t)(blocks * Q8_REC_BYTES);
+
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(bytes) : "memory");
+    // bulk copies are limited in size: issue 32 KiB pieces
+    for (uint32_t off = 0; off < bytes; off += 32768) {
+      const uint32_t n = bytes - off < 32768 ? bytes - off : 32768;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       (uint32_t)__cvta_generic_to_shared(wt + off)),
+                   "l"(w + tile * blocks * Q8_REC_BYTES + off), "r"(n), "r"(bar_a)
+                   : "memory");
+    }
+  }
+  {  // activations, in parallel with the weight copy
+    const int4* src = reinterpret_cast<const int4*>(xq);
+    int4* dst = reinterpret_cast<int4*>(xq_s);
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+  }
+  __syncthreads();  // barrier initialised and activations staged
+  {
+    // bounded wait for the bulk copy (two seconds), all threads observe the phase themselves
+    uint64_t t0 = 0;
+    bool done = false;
+    for (uint32_t i = 0; i < (1u << 26) && !done; i++) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(bar_a), "r"(0u), "r"(20000u)
+          : "memory");
+      done = ok != 0;
+      if (!done && (i & 15) == 15) {
+        uint64_t now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 2000000000ull) break;
+      }
+    }
+    if (!done) {
+      if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
+        status->where = 10;
+        status->detail = (int)tile;
+      }
+      return;
+    }
+  }
+
+  const int rit = threadIdx.x >> 3, l = threadIdx.x & 7;
+  const size_t row = tile * 16 + rit;
+  float acc[MP];
+#pragma unroll
+  for (int m = 0; m < MP; m++) acc[m] = 0.0f;
+  const uint8_t* qp = wt + 32 + rit * 32 + l * 4;
+  const uint8_t* sp = wt + 2 * rit;
+#pragma unroll 4
+  for (size_t b = 0; b < blocks; b++) {
+    const int wq = *reinterpret_cast<const int*>(qp + b * Q8_REC_BYTES);
+    const float wd = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + b * Q8_REC_BYTES));
+#pragma unroll
+    for (int m = 0; m < MP; m++) {
+      const int xv = *reinterpret_cast<const int*>(xq_s + m * K + b * 32 + l * 4);
+      const float da = __fmul_rn(wd, xs_s[m * blocks + b]);
+      if (SEM == RMI_SEM_AVX2) {
+        const float f = __fsub_rn(__int_as_float(dp4a_s8(wq, xv, 0x4B400000)), 12582912.0f);
+        acc[m] = __fmaf_rn(da, f, acc[m]);  // avx2.rs:96-148, lane l of the eight
+      } else {
+        int dot = dp4a_s8(wq, xv, 0);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        const float f = small_int_to_f32(dot);
+        if (SEM == RMI_SEM_NEON) acc[m] = __fmaf_rn(f, da, acc[m]);   // neon.rs:69
+        else acc[m] = __fadd_rn(acc[m], __fmul_rn(da, f));            // scalar.rs:55
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MP; m++) {
+    float r = acc[m];
+    if (SEM == RMI_SEM_AVX2) {  // dot.rs:447-456
+      const float s = __fadd_rn(__shfl_xor_sync(0xffffffffu, r, 4), r);
+      const float t = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+      r = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
+    }
+    if (l == 0 && row >= row_begin && row < row_end) out[m * out_stride + row] = r;
+  }
+}
+
 // ---------------------------------------------------------------- exact block sums
 
 __global__ void q8_block_sums_kernel(const uint8_t* __restrict__ w, size_t blocks, size_t n_rows,
@@ -397,6 +512,25 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
                                 size_t out_stride, size_t row_begin, size_t row_end, size_t n_groups) {
   // Enough warps to keep every SM streaming: a pass over MP activation rows does MP times the
   // arithmetic per weight byte, so fewer (fatter) warps are needed as MP grows.
+  {
+    // small problem: one CTA per tile with the tile staged by a single bulk copy
+    const size_t t1 = (row_end + 15) / 16 - row_begin / 16, blocks = w->n_in / 32;
+    const size_t smem = 128 + blocks * Q8_REC_BYTES + (size_t)MP * (w->n_in + blocks * 4);
+    if (MP <= 2 && t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024) {
+      auto kern = q8_gemv_staged_kernel<SEM, MP>;
+      if (smem > 48 * 1024 &&
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed", smem);
+        return RMI_ERR_CUDA;
+      }
+      dim3 grid((unsigned)t1, (unsigned)n_groups);
+      const int pr = rmi_prof_begin(ctx, "q8_gemv");
+      kern<<<grid, 128, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin, row_end,
+                                             row_begin / 16, ctx->d_status);
+      rmi_prof_end(ctx, pr);
+      return rmi_post_launch(ctx, "q8_gemv_staged");
+    }
+  }
   const size_t tiles = ((row_end + 15) / 16 - row_begin / 16) * n_groups;
   const size_t per_sm = MP >= 8 ? 6 : (MP >= 4 ? 8 : 16);
   const size_t want = (size_t)ctx->sm_count * per_sm;
