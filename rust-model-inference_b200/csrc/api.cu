@@ -168,6 +168,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->sem = RMI_SEM_AVX2;
   c->launches = 0;
   c->prof_on = false;
+  c->pdl = false;
   for (int i = 0; i < 8; i++) {
     c->scratch[i] = nullptr;
     c->scratch_bytes[i] = 0;

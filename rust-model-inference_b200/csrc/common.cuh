@@ -82,6 +82,8 @@ struct rmi_ctx {
   // optional per-kernel timing (rmi_prof_*): event pairs recorded around tagged launches
   bool prof_on;
   std::vector<rmi_prof_rec> prof;
+  // decode chain: launch kernels with programmatic stream serialization (see pdl_wait below)
+  bool pdl;
 };
 
 // Q8_0 / Q4_K weight resident in HBM.
@@ -131,6 +133,31 @@ void rmi_prof_end(rmi_ctx* ctx, int idx);
 // ---------------------------------------------------------------- device helpers
 
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream is still running; it must call
+// pdl_wait() before it touches anything the predecessor writes (or still reads).  Code before
+// the wait may only read data that no kernel of the chain writes (weights) and use shared
+// memory.  Without the launch attribute both calls are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch through cudaLaunchKernelEx so that the attribute can be attached when ctx->pdl is set.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t rmi_launch(const rmi_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // IEEE f16 -> f32 (exact)
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {

@@ -35,6 +35,8 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
 __global__ void embed_kernel(const uint8_t* __restrict__ emb, size_t blocks, const uint32_t* __restrict__ prompts,
                              size_t n_prompt, const uint32_t* __restrict__ gen, size_t n_gen,
                              const int* __restrict__ d_step, float* __restrict__ x, uint32_t vocab) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.x;
   const int step = *d_step;
   uint32_t tok = (size_t)step < n_prompt ? prompts[b * n_prompt + step] : gen[b * n_gen + (step - n_prompt)];
@@ -56,6 +58,8 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
                                      uint8_t* __restrict__ q8, float* __restrict__ scales) {
   __shared__ double s_part[8];
   __shared__ float s_scale;
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t blocks = n / 32;
@@ -100,6 +104,8 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
                                        uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
                                        size_t capacity) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.x, head = blockIdx.y;
   const int lane = threadIdx.x;
   const int step = *d_step;
@@ -156,6 +162,8 @@ __global__ void __launch_bounds__(256)
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned CL = cluster.num_blocks(), rank = cluster.block_rank();
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.y, kvh = blockIdx.x / CL;
   const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
   const int T = *d_step + 1;
@@ -309,6 +317,8 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, size_t v
                                       uint32_t* __restrict__ part_i, int* __restrict__ flag) {
   __shared__ float s_v[32];
   __shared__ uint32_t s_i[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.y, slice = blockIdx.x;
   const size_t per = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
   const size_t lo = slice * per, hi = lo + per < vocab ? lo + per : vocab;
@@ -334,6 +344,8 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_v, const uint
                                     size_t n_gen) {
   __shared__ float s_v[32];
   __shared__ uint32_t s_i[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t b = blockIdx.x;
   float best = -INFINITY;
   uint32_t bi = 0xffffffffu;
@@ -349,7 +361,11 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_v, const uint
   }
 }
 
-__global__ void step_inc_kernel(int* d_step) { *d_step += 1; }
+__global__ void step_inc_kernel(int* d_step) {
+  pdl_wait();
+  pdl_launch_dependents();
+  *d_step += 1;
+}
 
 __global__ void unshard_cols_kernel(const float* __restrict__ gathered, size_t g, size_t m, size_t npr,
                                     float* __restrict__ out) {
@@ -370,17 +386,22 @@ int32_t launch_unshard_cols(rmi_ctx* ctx, const float* gathered, size_t g, size_
 
 int32_t launch_embed(rmi_ctx* ctx, const rmi_weight* emb, const uint32_t* prompts, size_t n_prompt, const uint32_t* gen,
                      size_t n_gen, const int* d_step, float* x, size_t batch) {
-  embed_kernel<<<(unsigned)batch, 256, 0, ctx->stream>>>(emb->d_tile16, emb->n_in / 32, prompts, n_prompt, gen, n_gen,
-                                                         d_step, x, (uint32_t)emb->n_rows);
+  if (rmi_launch(ctx, embed_kernel, dim3((unsigned)batch), dim3(256), 0, emb->d_tile16, emb->n_in / 32, prompts, n_prompt,
+                 gen, n_gen, d_step, x, (uint32_t)emb->n_rows) != cudaSuccess) {
+    rmi_set_error("launch of embed failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "embed");
 }
 
 int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const float* weight, size_t n, float eps,
                              uint8_t* q8, float* scales, size_t batch) {
-  switch (ctx->sem) {
-    case RMI_SEM_AVX2: rmsnorm_quant_kernel<RMI_SEM_AVX2><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
-    case RMI_SEM_NEON: rmsnorm_quant_kernel<RMI_SEM_NEON><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
-    default: rmsnorm_quant_kernel<RMI_SEM_SCALAR><<<(unsigned)batch, 256, 0, ctx->stream>>>(x, add, weight, n, eps, q8, scales); break;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? rmsnorm_quant_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? rmsnorm_quant_kernel<RMI_SEM_NEON>
+                                                                   : rmsnorm_quant_kernel<RMI_SEM_SCALAR>);
+  if (rmi_launch(ctx, kern, dim3((unsigned)batch), dim3(256), 0, x, add, weight, n, eps, q8, scales) != cudaSuccess) {
+    rmi_set_error("launch of rmsnorm_quant failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "rmsnorm_quant");
 }
@@ -389,8 +410,11 @@ int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* 
                                const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
                                uint16_t* k_cache, uint16_t* v_cache, size_t layer) {
   dim3 grid((unsigned)d.batch, (unsigned)(d.n_head + 2 * d.n_head_kv));
-  qk_norm_rope_kv_kernel<<<grid, 32, 0, ctx->stream>>>(qkv, d.n_head, d.n_head_kv, d.hd, q_norm, k_norm, d.eps, rope,
-                                                       d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity);
+  if (rmi_launch(ctx, qk_norm_rope_kv_kernel, grid, dim3(32), 0, qkv, d.n_head, d.n_head_kv, d.hd, q_norm, k_norm, d.eps,
+                 rope, d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity) != cudaSuccess) {
+    rmi_set_error("launch of qk_norm_rope_kv failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "qk_norm_rope_kv");
 }
 
@@ -433,13 +457,15 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
   cfg.blockDim = dim3(256, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cl;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = ctx->pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q16, k_cache, v_cache, d_step, d.n_head, d.n_head_kv, d.hd, layer,
                                      d.n_layer, d.capacity, chunk, attn_out, q8, scales);
   if (e != cudaSuccess) {
@@ -454,13 +480,20 @@ size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
                       size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i) {
   dim3 grid(ARGMAX_SLICES, (unsigned)batch);
-  argmax_partial_kernel<<<grid, 256, 0, ctx->stream>>>(logits, vocab, part_v, part_i, flag);
-  RMI_TRY(rmi_post_launch(ctx, "argmax_partial"));
-  argmax_final_kernel<<<(unsigned)batch, 64, 0, ctx->stream>>>(part_v, part_i, d_step, n_prompt, gen, n_gen);
-  return rmi_post_launch(ctx, "argmax_final");
+  if (rmi_launch(ctx, argmax_partial_kernel, grid, dim3(256), 0, logits, vocab, part_v, part_i, flag) != cudaSuccess ||
+      rmi_launch(ctx, argmax_final_kernel, dim3((unsigned)batch), dim3(64), 0, part_v, part_i, d_step, n_prompt, gen,
+                 n_gen) != cudaSuccess) {
+    rmi_set_error("launch of argmax failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
+  ctx->launches.fetch_add(1, std::memory_order_relaxed);
+  return rmi_post_launch(ctx, "argmax");
 }
 
 int32_t launch_step_inc(rmi_ctx* ctx, int* d_step) {
-  step_inc_kernel<<<1, 1, 0, ctx->stream>>>(d_step);
+  if (rmi_launch(ctx, step_inc_kernel, dim3(1), dim3(1), 0, d_step) != cudaSuccess) {
+    rmi_set_error("launch of step_inc failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "step_inc");
 }

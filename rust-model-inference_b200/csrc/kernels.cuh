@@ -9,6 +9,10 @@ int32_t launch_q8_build_umma(rmi_ctx* ctx, const uint8_t* t16, uint8_t* uq, floa
 int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8, float* scales, int out_mode);
 int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
                        float* out, size_t out_stride, size_t row_begin, size_t row_end);
+bool q8_gemv_fused_norm_eligible(const rmi_ctx* ctx, const rmi_weight* w, size_t m);
+// x = x_in (+ add); rms_norm(x, norm_w, eps); quantize; out = W x.  x is also written to x_out (!= x_in).
+int32_t launch_q8_gemv_fused_norm(rmi_ctx* ctx, const rmi_weight* w, const float* x_in, const float* add,
+                                  const float* norm_w, float eps, float* x_out, size_t m, float* out, size_t out_stride);
 int32_t launch_q8_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, size_t m, int32_t* sums);
 int32_t launch_silu_mul_quantize(rmi_ctx* ctx, const float* gate, const float* up, size_t in_stride, size_t m,
                                  size_t n_ff, float* act, uint8_t* q8, float* scales);

@@ -227,6 +227,8 @@ __global__ void __launch_bounds__(256)
   // first weight batch is requested before the activations are staged
   gemv_batch<LB> ba, bb;
   if (active) gemv_load_batch<LB>(ba, qp, sp, 0, blocks);
+  pdl_wait();
+  pdl_launch_dependents();
   {
     const int4* src = reinterpret_cast<const int4*>(xq);
     int4* dst = reinterpret_cast<int4*>(xq_s);
@@ -284,19 +286,35 @@ __global__ void __launch_bounds__(256)
 // tile's whole record stream (blocks * 544 contiguous bytes) with a single bulk async copy, so
 // the tile costs one memory round trip; thread (row r, lane l) then runs the reference's
 // per-lane chain over the blocks out of shared memory.
-template <int SEM, int MP>
+//
+// FUSED: the activations are not read pre-quantized; every CTA derives them itself while its
+// weight copy is in flight: x = x_in (+ add), rms_norm(x, norm_w) (src/ops/norm.rs:3-11), Q8_0
+// quantization.  The updated residual stream is written to x_out by the CTAs of tile 0 only
+// (x_out must not alias x_in: other CTAs are still reading it).
+struct gemv_norm_args {
+  const float* x_in;
+  const float* add;     // may be null
+  const float* norm_w;
+  float* x_out;         // may be null
+  float eps;
+};
+
+template <int SEM, int MP, bool FUSED>
 __global__ void __launch_bounds__(128)
     q8_gemv_staged_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
                           const float* __restrict__ xs, float* __restrict__ out, size_t out_stride, size_t row_begin,
-                          size_t row_end, size_t first_tile, rmi_dev_status* status) {
+                          size_t row_end, size_t first_tile, rmi_dev_status* status, gemv_norm_args na) {
   extern __shared__ __align__(128) uint8_t smem[];
   const size_t K = blocks * 32;
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
   uint8_t* wt = smem + 128;                                   // [blocks][544]
   int8_t* xq_s = reinterpret_cast<int8_t*>(wt + blocks * Q8_REC_BYTES);  // [MP][K]
   float* xs_s = reinterpret_cast<float*>(xq_s + MP * K);      // [MP][blocks]
-  xq += (size_t)blockIdx.y * MP * K;
-  xs += (size_t)blockIdx.y * MP * blocks;
+  float* xf = xs_s + MP * blocks;                             // [MP][K], FUSED only
+  if (!FUSED) {
+    xq += (size_t)blockIdx.y * MP * K;
+    xs += (size_t)blockIdx.y * MP * blocks;
+  }
   out += (size_t)blockIdx.y * MP * out_stride;
   const size_t tile = first_tile + blockIdx.x;
   const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bar);
@@ -315,11 +333,55 @@ __global__ void __launch_bounds__(128)
                    : "memory");
     }
   }
-  {  // activations, in parallel with the weight copy
+  pdl_wait();  // the weight copy above is in flight; everything below depends on the previous kernel
+  pdl_launch_dependents();
+  if (!FUSED) {  // activations, in parallel with the weight copy
     const int4* src = reinterpret_cast<const int4*>(xq);
     int4* dst = reinterpret_cast<int4*>(xq_s);
     for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
     for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+  } else {
+    __shared__ double s_part[MP][4];
+    __shared__ float s_scale[MP];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t seq0 = (size_t)blockIdx.y * MP;
+#pragma unroll
+    for (int m = 0; m < MP; m++) {
+      const float* xi = na.x_in + (seq0 + m) * K;
+      const float* ad = na.add ? na.add + (seq0 + m) * K : nullptr;
+      double part = 0.0;
+      for (size_t blk = warp; blk < blocks; blk += 4) {
+        float v = __ldg(xi + blk * 32 + lane);
+        if (ad) v = __fadd_rn(v, __ldg(ad + blk * 32 + lane));
+        xf[m * K + blk * 32 + lane] = v;
+        if (na.x_out && blockIdx.x == 0) na.x_out[(seq0 + m) * K + blk * 32 + lane] = v;
+        part += (double)__fmul_rn(v, v);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (lane == 0) s_part[m][warp] = part;
+    }
+    __syncthreads();
+    if (threadIdx.x < MP) {
+      const double sum = s_part[threadIdx.x][0] + s_part[threadIdx.x][1] + s_part[threadIdx.x][2] + s_part[threadIdx.x][3];
+      const float mean_sq = (float)(sum / (double)K);
+      s_scale[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, na.eps)));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < MP; m++) {
+      const float sc = s_scale[m];
+      for (size_t blk = warp; blk < blocks; blk += 4) {
+        const float v = __fmul_rn(__fmul_rn(xf[m * K + blk * 32 + lane], sc), __ldg(na.norm_w + blk * 32 + lane));
+        float a = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        float d, inv;
+        q8_scale_pair<SEM>(a, &d, &inv);
+        xq_s[m * K + blk * 32 + lane] = (int8_t)q8_quant_value<SEM>(v, inv);
+        if (lane == 0) xs_s[m * blocks + blk] = f16_round_trip(d);
+      }
+    }
   }
   __syncthreads();  // barrier initialised and activations staged
   {
@@ -419,6 +481,8 @@ __global__ void silu_mul_quantize_kernel(const float* __restrict__ gate, const f
                                          size_t in_stride, size_t m, size_t n_ff,
                                          float* __restrict__ act, uint8_t* __restrict__ q8,
                                          float* __restrict__ scales) {
+  pdl_wait();
+  pdl_launch_dependents();
   size_t blocks = n_ff / 32;
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
   int lane = threadIdx.x & 31;
@@ -501,9 +565,13 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
   int wpc = warps * n_groups >= (size_t)ctx->sm_count * 8 ? 4 : 2;
   dim3 grid((unsigned)((warps + wpc - 1) / wpc), (unsigned)n_groups);
   const int pr = rmi_prof_begin(ctx, "q8_gemv");
-  kern<<<grid, wpc * 32, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin,
-                                              row_end, first_tile);
+  cudaError_t le = rmi_launch(ctx, kern, grid, dim3(wpc * 32), smem, w->d_tile16, blocks, xq, xs, out, out_stride,
+                              row_begin, row_end, first_tile);
   rmi_prof_end(ctx, pr);
+  if (le != cudaSuccess) {
+    rmi_set_error("launch of q8_gemv failed: %s", cudaGetErrorString(le));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "q8_gemv");
 }
 
@@ -517,7 +585,7 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
     const size_t t1 = (row_end + 15) / 16 - row_begin / 16, blocks = w->n_in / 32;
     const size_t smem = 128 + blocks * Q8_REC_BYTES + (size_t)MP * (w->n_in + blocks * 4);
     if (MP <= 2 && t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024) {
-      auto kern = q8_gemv_staged_kernel<SEM, MP>;
+      auto kern = q8_gemv_staged_kernel<SEM, MP, false>;
       if (smem > 48 * 1024 &&
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed", smem);
@@ -525,9 +593,13 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
       }
       dim3 grid((unsigned)t1, (unsigned)n_groups);
       const int pr = rmi_prof_begin(ctx, "q8_gemv");
-      kern<<<grid, 128, smem, ctx->stream>>>(w->d_tile16, blocks, xq, xs, out, out_stride, row_begin, row_end,
-                                             row_begin / 16, ctx->d_status);
+      cudaError_t le = rmi_launch(ctx, kern, grid, dim3(128), smem, w->d_tile16, blocks, xq, xs, out, out_stride,
+                                  row_begin, row_end, row_begin / 16, ctx->d_status, gemv_norm_args{});
       rmi_prof_end(ctx, pr);
+      if (le != cudaSuccess) {
+        rmi_set_error("launch of q8_gemv_staged failed: %s", cudaGetErrorString(le));
+        return RMI_ERR_CUDA;
+      }
       return rmi_post_launch(ctx, "q8_gemv_staged");
     }
   }
@@ -571,6 +643,49 @@ static int32_t gemv_dispatch_mp(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
   return RMI_OK;
 }
 
+// ---- rms_norm + quantize fused into the staged GEMV (decode, one or two sequences) ----
+static size_t gemv_fused_smem(const rmi_weight* w, size_t mp) {
+  const size_t blocks = w->n_in / 32;
+  return 128 + blocks * Q8_REC_BYTES + mp * (w->n_in + blocks * 4) + mp * w->n_in * 4;
+}
+
+bool q8_gemv_fused_norm_eligible(const rmi_ctx* ctx, const rmi_weight* w, size_t m) {
+  return (m == 1 || m == 2) && w->n_tiles16 <= (size_t)ctx->sm_count * 6 && gemv_fused_smem(w, m) <= ctx->smem_optin - 1024;
+}
+
+template <int SEM, int MP>
+static int32_t gemv_fused_launch(rmi_ctx* ctx, const rmi_weight* w, const gemv_norm_args& na, float* out, size_t out_stride) {
+  const size_t smem = gemv_fused_smem(w, MP), blocks = w->n_in / 32;
+  auto kern = q8_gemv_staged_kernel<SEM, MP, true>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed", smem);
+    return RMI_ERR_CUDA;
+  }
+  const int pr = rmi_prof_begin(ctx, "q8_gemv");
+  cudaError_t le = rmi_launch(ctx, kern, dim3((unsigned)w->n_tiles16, 1), dim3(128), smem, w->d_tile16, blocks,
+                              (const uint8_t*)nullptr, (const float*)nullptr, out, out_stride, (size_t)0, w->n_rows,
+                              (size_t)0, ctx->d_status, na);
+  rmi_prof_end(ctx, pr);
+  if (le != cudaSuccess) {
+    rmi_set_error("launch of q8_gemv_fused_norm failed: %s", cudaGetErrorString(le));
+    return RMI_ERR_CUDA;
+  }
+  return rmi_post_launch(ctx, "q8_gemv_fused_norm");
+}
+
+int32_t launch_q8_gemv_fused_norm(rmi_ctx* ctx, const rmi_weight* w, const float* x_in, const float* add,
+                                  const float* norm_w, float eps, float* x_out, size_t m, float* out, size_t out_stride) {
+  RMI_REQUIRE(q8_gemv_fused_norm_eligible(ctx, w, m), RMI_ERR_UNSUPPORTED, "fused norm GEMV: shape not eligible");
+  gemv_norm_args na = {x_in, add, norm_w, x_out, eps};
+#define RMI_FUSED(SEMV) (m == 1 ? gemv_fused_launch<SEMV, 1>(ctx, w, na, out, out_stride) : gemv_fused_launch<SEMV, 2>(ctx, w, na, out, out_stride))
+  switch (ctx->sem) {
+    case RMI_SEM_AVX2: return RMI_FUSED(RMI_SEM_AVX2);
+    case RMI_SEM_NEON: return RMI_FUSED(RMI_SEM_NEON);
+    default: return RMI_FUSED(RMI_SEM_SCALAR);
+  }
+#undef RMI_FUSED
+}
+
 int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m,
                        float* out, size_t out_stride, size_t row_begin, size_t row_end) {
   if (row_begin >= row_end || m == 0) return RMI_OK;
@@ -595,10 +710,12 @@ int32_t launch_silu_mul_quantize(rmi_ctx* ctx, const float* gate, const float* u
   size_t warps = m * (n_ff / 32);
   if (warps == 0) return RMI_OK;
   unsigned grid = (unsigned)((warps + 7) / 8);
-  switch (ctx->sem) {
-    case RMI_SEM_AVX2: silu_mul_quantize_kernel<RMI_SEM_AVX2><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
-    case RMI_SEM_NEON: silu_mul_quantize_kernel<RMI_SEM_NEON><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
-    default: silu_mul_quantize_kernel<RMI_SEM_SCALAR><<<grid, 256, 0, ctx->stream>>>(gate, up, in_stride, m, n_ff, act, q8, scales); break;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? silu_mul_quantize_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? silu_mul_quantize_kernel<RMI_SEM_NEON>
+                                                                   : silu_mul_quantize_kernel<RMI_SEM_SCALAR>);
+  if (rmi_launch(ctx, kern, dim3(grid), dim3(256), 0, gate, up, in_stride, m, n_ff, act, q8, scales) != cudaSuccess) {
+    rmi_set_error("launch of silu_mul_quantize failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "silu_mul_quantize");
 }

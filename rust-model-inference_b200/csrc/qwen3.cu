@@ -11,6 +11,7 @@
 
 #include <new>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -42,7 +43,8 @@ struct rmi_session {
   const rmi_qwen3* model;
   decode_dims d;
   uint16_t *k_cache, *v_cache;
-  float *x, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;
+  float *x, *x2, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;  // x2: second residual buffer of the fused-norm path
+  bool fused_norm;
   uint16_t* q16;
   uint8_t* q8;
   float* xs;
@@ -263,7 +265,7 @@ static void drop_graphs(rmi_session* s) {
 static void free_session(rmi_session* s) {
   if (!s) return;
   drop_graphs(s);
-  cudaFree(s->k_cache); cudaFree(s->v_cache); cudaFree(s->x); cudaFree(s->qkv); cudaFree(s->proj);
+  cudaFree(s->k_cache); cudaFree(s->v_cache); cudaFree(s->x); cudaFree(s->x2); cudaFree(s->qkv); cudaFree(s->proj);
   cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8);
   cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
   cudaFree(s->attn_dbg);
@@ -323,6 +325,7 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->k_cache, kv);
   SESSION_ALLOC(s->v_cache, kv);
   SESSION_ALLOC(s->x, batch * d.n_embd * 4);
+  SESSION_ALLOC(s->x2, batch * d.n_embd * 4);
   SESSION_ALLOC(s->qkv, batch * (nq + 2 * nk) * 4);
   SESSION_ALLOC(s->proj, batch * d.n_embd * 4);
   SESSION_ALLOC(s->gu, batch * 2 * d.n_ff * 4);
@@ -336,6 +339,9 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->attn_dbg, batch * nq * 4);
   SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
+  s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
+  for (const auto& l : model->layers)
+    s->fused_norm = s->fused_norm && q8_gemv_fused_norm_eligible(ctx, l.wqkv, batch) && q8_gemv_fused_norm_eligible(ctx, l.wgu, batch);
   cudaMemset(s->k_cache, 0, kv);
   cudaMemset(s->v_cache, 0, kv);
   // rope_neox (src/ops/rope.rs:21-37): theta_0 = pos, theta_{i+1} = theta_i * base^(-2/d) in f32,
@@ -369,22 +375,36 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   const size_t B = d.batch, nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
   RMI_TRY(launch_embed(ctx, m->token_embd, s->prompts, n_prompt, s->gen, n_gen, s->d_step, s->x, B));
   const float* pending = nullptr;  // residual branch still to be added to x
+  float* xc = s->x;                  // current residual stream (ping-pongs with x2 on the fused path)
+  float* xn = s->x2;
   for (size_t l = 0; l < d.n_layer; l++) {
     const layer_weights& w = m->layers[l];
-    RMI_TRY(launch_rmsnorm_quant(ctx, s->x, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
-    RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
+    if (s->fused_norm) {
+      // residual add + rms_norm + quantize happen inside the GEMV's prologue; it writes the updated x to xn
+      RMI_TRY(launch_q8_gemv_fused_norm(ctx, w.wqkv, xc, pending, w.attn_norm, d.eps, xn, B, s->qkv, nq + 2 * nk));
+      std::swap(xc, xn);
+    } else {
+      RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+      RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
+    }
     RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
                                    s->v_cache, l));
     RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
     RMI_TRY(launch_q8_gemv(ctx, w.wo, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
-    RMI_TRY(launch_rmsnorm_quant(ctx, s->x, s->proj, w.ffn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
-    RMI_TRY(launch_q8_gemv(ctx, w.wgu, s->q8, s->xs, B, s->gu, 2 * d.n_ff, 0, 2 * d.n_ff));
+    if (s->fused_norm) {
+      RMI_TRY(launch_q8_gemv_fused_norm(ctx, w.wgu, xc, s->proj, w.ffn_norm, d.eps, xn, B, s->gu, 2 * d.n_ff));
+      std::swap(xc, xn);
+    } else {
+      RMI_TRY(launch_rmsnorm_quant(ctx, xc, s->proj, w.ffn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+      RMI_TRY(launch_q8_gemv(ctx, w.wgu, s->q8, s->xs, B, s->gu, 2 * d.n_ff, 0, 2 * d.n_ff));
+    }
     RMI_TRY(launch_silu_mul_quantize(ctx, s->gu, s->gu + d.n_ff, 2 * d.n_ff, B, d.n_ff, nullptr, s->q8, s->xs));
     RMI_TRY(launch_q8_gemv(ctx, w.wdown, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
     pending = s->proj;
   }
-  // x += last down projection; output norm; logits; greedy token
-  RMI_TRY(launch_rmsnorm_quant(ctx, s->x, pending, m->output_norm, d.n_embd, d.eps, s->q8, s->xs, B));
+  // x += last down projection; output norm; logits; greedy token.  After an even number of swaps the
+  // stream is back in s->x, which is what rmi_session_read_hidden returns.
+  RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, m->output_norm, d.n_embd, d.eps, s->q8, s->xs, B));
   if (with_logits) {
     RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
     RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i));
@@ -399,7 +419,11 @@ static int32_t build_graphs(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   drop_graphs(s);
   for (int which = 0; which < 2; which++) {
     RMI_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    // programmatic dependent launch along the step's kernel chain: the next kernel's weight copy
+    // overlaps the tail of the current one.  Measured gain for small batches only (large grids lose).
+    ctx->pdl = s->d.batch <= 4 && getenv("RMI_NO_PDL") == nullptr;
     int32_t st = enqueue_step(ctx, s, n_prompt, n_gen, which == 1);
+    ctx->pdl = false;
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
     if (st != RMI_OK) {
@@ -478,7 +502,7 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
       passes++;
       rem %= p2;
     }
-  const uint64_t launches_per_body = 3 + d.n_layer * (5 + 4 * passes), launches_full = launches_per_body + passes + 2;
+  const uint64_t launches_per_body = 3 + d.n_layer * (s->fused_norm ? 7 : 5 + 4 * passes), launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;
   for (size_t st = 0; st < steps && ce == cudaSuccess; st++) {
