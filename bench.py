@@ -206,7 +206,10 @@ def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16
     n, k = 32768, 8192
     ctx.set_semantics(pkg.SEM_NEON)
     s, e = pkg.sharding.shard_rows(n, world, rank)
-    lin = pkg.sharding.ShardedLinear(pkg, pkg.synth.q8_0_weight_rows(n, k, seed=0, row_begin=s, row_end=e), k, n, rank, world)
+    shard_bytes = pkg.synth.q8_0_weight_rows(n, k, seed=0, row_begin=s, row_end=e)
+    lin = pkg.sharding.ShardedLinear(pkg, shard_bytes, k, n, rank, world)
+    # fused variant: the matmul stores its columns into every rank's [M, N] buffer over peer pointers
+    peer = pkg.sharding.PeerShardedLinear(pkg, shard_bytes, k, n, rank, world, m_max=4096)
     results = {}
     for m in (1, 16, 256, 4096):
         x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
@@ -234,13 +237,37 @@ def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
             times[mode] = float(t.item())
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                peer.forward_dev(x.data_ptr(), m)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(iters):
+                peer.forward_dev(x.data_ptr(), m)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ctx.check_status()
+            if world > 1:
+                dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times["fused"] = float(t.item())
+        fused = np.empty((m, n), np.float32)
+        ctx.d2h(fused, peer.out_ptr)
+        same = bool(np.array_equal(fused.view(np.uint32), out_full.cpu().numpy().view(np.uint32)))
         w_bytes = (n // world) * (k // 32) * 34
         ops = 2.0 * m * k * n
         results[f"M={m}"] = {"ms_local": times["local"], "ms_with_allgather": times["gathered"],
+                             "ms_fused_peer_stores": times["fused"], "fused_equals_allgather_bits": same,
                              "per_gpu_weight_gbs": w_bytes / (times["local"] / 1e3) / 1e9,
                              "frac_of_hbm_peak": w_bytes / (times["local"] / 1e3) / 1e9 / hbm_peak,
                              "whole_job_tops": ops / (times["local"] / 1e3) / 1e12,
                              "allgather_bytes_in_per_gpu": (world - 1) * m * (n // world) * 4}
+    peer.close()
     if rank == 0:
         print(json.dumps({"metric": "sharded Q8_0 GEMM sweep (N=32768,K=8192), rows split across GPUs + all-gather",
                           "n_gpus": world, "scaling": "strong", "dtype": "int8", "data": "synthetic",

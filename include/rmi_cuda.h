@@ -232,6 +232,33 @@ int32_t rmi_session_read_logits(rmi_ctx* ctx, rmi_session* s, float* logits);
 int32_t rmi_unshard_cols_dev(rmi_ctx* ctx, const float* gathered, size_t g, size_t m,
                              size_t n_per_rank, float* out);
 
+/* Fused alternative to all-gather + un-shard (no counterpart in the reference; it realises the
+ * same Rows placement, src/format/load_plan.rs:19-22): the matmul stores every f32 result into
+ * each of `n_outs` (1..8) buffers of identical layout [m][out_stride], at columns
+ * [col_offset, col_offset + n_rows of w).  outs[0] is normally this rank's own final buffer and
+ * the others are peers' buffers mapped with rmi_ipc_open, so each rank writes its column slice
+ * straight into every rank's [m, n] result over NVLink (plain stores, no multicast).  Device
+ * pointers; returns after enqueueing. */
+int32_t rmi_matmul_q8_0_fanout_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                   float* const* outs, int32_t n_outs, size_t out_stride,
+                                   size_t col_offset);
+/* CUDA IPC for buffers from rmi_dev_alloc (one process per GPU, same node): a 64-byte handle
+ * to send to the peers, and the peer's mapping of it (peer access is enabled on open). */
+int32_t rmi_ipc_export(rmi_ctx* ctx, const void* dev_ptr, uint8_t* handle64);
+int32_t rmi_ipc_open(rmi_ctx* ctx, const uint8_t* handle64, void** out_ptr);
+int32_t rmi_ipc_close(rmi_ctx* ctx, void* ptr);
+/* Closes one exchange round.  flags[p] is rank p's flag array (`world` uint32, zero-initialised;
+ * flags[rank] is this rank's own, the others are IPC mappings).  Enqueues a kernel that writes
+ * `epoch` into slot `rank` of every array after all earlier stores of this stream, then waits
+ * until all slots of its own array reached `epoch`.  Epochs must increase by one per round.
+ * The wait gives up after two seconds and records RMI_ERR_TIMEOUT in the context's device
+ * status, which rmi_check_status reports.  Every rank must run on its own GPU. */
+int32_t rmi_peer_signal_wait_dev(rmi_ctx* ctx, uint32_t* const* flags, int32_t world, int32_t rank,
+                                 uint32_t epoch);
+/* Synchronises the stream and returns RMI_ERR_TIMEOUT if a device-side wait gave up since the
+ * last check (the `_dev` entry points return before their kernels finish). */
+int32_t rmi_check_status(rmi_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

@@ -135,6 +135,24 @@ class Context:
     def d2h(self, dst: np.ndarray, src: int):
         _check(lib().rmi_d2h(self._h, _p(dst), C.c_void_p(src), _sz(dst.nbytes)))
 
+    def check_status(self):
+        """Synchronise and raise RMI_ERR_TIMEOUT if a device-side wait gave up."""
+        _check(lib().rmi_check_status(self._h))
+
+    def ipc_export(self, dev_ptr: int) -> bytes:
+        buf = (C.c_uint8 * 64)()
+        _check(lib().rmi_ipc_export(self._h, C.c_void_p(dev_ptr), buf))
+        return bytes(buf)
+
+    def ipc_open(self, handle: bytes) -> int:
+        buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+        out = C.c_void_p()
+        _check(lib().rmi_ipc_open(self._h, buf, C.byref(out)))
+        return out.value
+
+    def ipc_close(self, ptr: int):
+        _check(lib().rmi_ipc_close(self._h, C.c_void_p(ptr)))
+
 
 _ctx = None
 
@@ -448,6 +466,19 @@ def matmul_q4_k_dequant_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr
 def unshard_cols_dev(ctx: Context, gathered_ptr: int, g: int, m: int, n_per_rank: int, out_ptr: int):
     _check(lib().rmi_unshard_cols_dev(ctx.handle, C.c_void_p(gathered_ptr), _sz(g), _sz(m), _sz(n_per_rank),
                                       C.c_void_p(out_ptr)))
+
+
+def matmul_q8_0_fanout_dev(w: "QuantizedTensor", x_ptr: int, m: int, out_ptrs, out_stride: int, col_offset: int):
+    """y = x W^T stored into every buffer of `out_ptrs` ([m][out_stride] f32) at columns col_offset.."""
+    arr = (C.c_void_p * len(out_ptrs))(*[C.c_void_p(p) for p in out_ptrs])
+    _check(lib().rmi_matmul_q8_0_fanout_dev(w._ctx.handle, w._h, C.c_void_p(x_ptr), _sz(m), arr,
+                                            C.c_int32(len(out_ptrs)), _sz(out_stride), _sz(col_offset)))
+
+
+def peer_signal_wait_dev(ctx: Context, flag_ptrs, rank: int, epoch: int):
+    arr = (C.c_void_p * len(flag_ptrs))(*[C.c_void_p(p) for p in flag_ptrs])
+    _check(lib().rmi_peer_signal_wait_dev(ctx.handle, arr, C.c_int32(len(flag_ptrs)), C.c_int32(rank),
+                                          C.c_uint32(epoch & 0xffffffff)))
 
 
 def quantize_row_q8_k(x, ctx: Context | None = None):

@@ -169,6 +169,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->launches = 0;
   c->prof_on = false;
   c->pdl = false;
+  c->fanout = out_fanout{};
   for (int i = 0; i < 8; i++) {
     c->scratch[i] = nullptr;
     c->scratch_bytes[i] = 0;
@@ -563,8 +564,11 @@ extern "C" int32_t rmi_matmul_q8_0_prequantized(rmi_ctx* ctx, const rmi_weight* 
   return RMI_OK;
 }
 
-static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float* dx, size_t m, float* dout) {
+// dout: [m][out_stride] f32, the weight's rows land in columns [0, n_rows); out_stride 0 = n_rows
+static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float* dx, size_t m, float* dout,
+                                  size_t out_stride = 0) {
   const size_t blocks = w->n_in / 32;
+  if (out_stride == 0) out_stride = w->n_rows;
   if (use_tensor_cores(ctx, m)) {
     RMI_TRY(ensure_umma_layout(ctx, w));
     const size_t m_tiles = (m + 127) / 128, n_slabs = (w->n_in + 127) / 128;
@@ -586,7 +590,7 @@ static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float
     g.col_end = w->n_rows;
     g.epilogue = GEMM_EPI_F32;
     g.out = dout;
-    g.out_stride = w->n_rows;
+    g.out_stride = out_stride;
     return launch_gemm_tc(ctx, g);
   }
   uint8_t* dq;
@@ -594,7 +598,30 @@ static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float
   RMI_TRY(rmi_scratch(ctx, 0, m * w->n_in, (void**)&dq));
   RMI_TRY(rmi_scratch(ctx, 1, m * blocks * 4, (void**)&ds));
   RMI_TRY(launch_q8_quantize(ctx, dx, m, w->n_in, dq, ds, 0));
-  return launch_q8_gemv(ctx, w, dq, ds, m, dout, w->n_rows, 0, w->n_rows);
+  return launch_q8_gemv(ctx, w, dq, ds, m, dout, out_stride, 0, w->n_rows);
+}
+
+extern "C" int32_t rmi_matmul_q8_0_fanout_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                              float* const* outs, int32_t n_outs, size_t out_stride,
+                                              size_t col_offset) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q8_0));
+  RMI_REQUIRE(outs && n_outs >= 1 && n_outs <= RMI_MAX_FANOUT, RMI_ERR_BAD_SHAPE,
+              "rmi_matmul_q8_0_fanout_dev: between 1 and %d output buffers", RMI_MAX_FANOUT);
+  RMI_REQUIRE(out_stride >= col_offset + w->n_rows, RMI_ERR_BAD_SHAPE,
+              "rmi_matmul_q8_0_fanout_dev: out_stride %zu < col_offset %zu + %zu rows", out_stride, col_offset, w->n_rows);
+  for (int32_t i = 0; i < n_outs; i++)
+    RMI_REQUIRE(outs[i] != nullptr && (reinterpret_cast<uintptr_t>(outs[i]) & 3) == 0, RMI_ERR_BAD_HANDLE,
+                "rmi_matmul_q8_0_fanout_dev: output %d is null or misaligned", i);
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  RMI_REQUIRE(x != nullptr, RMI_ERR_BAD_HANDLE, "rmi_matmul_q8_0_fanout_dev: null input");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->fanout.n = n_outs - 1;
+  for (int32_t i = 1; i < n_outs; i++)
+    ctx->fanout.delta[i - 1] = (long long)(reinterpret_cast<const char*>(outs[i]) - reinterpret_cast<const char*>(outs[0]));
+  const int32_t st = matmul_q8_0_device(ctx, w, x, m, outs[0] + col_offset, out_stride);
+  ctx->fanout = out_fanout{};
+  return st;
 }
 
 extern "C" int32_t rmi_matmul_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output) {

@@ -62,6 +62,14 @@ struct rmi_prof_rec {
   cudaEvent_t a, b;
 };
 
+// Extra copies of every f32 output store of a matmul: `delta[i]` is the byte offset from the primary
+// output buffer to copy i (another buffer of the same layout, possibly in a peer GPU's memory).
+constexpr int RMI_MAX_FANOUT = 8;
+struct out_fanout {
+  int n;
+  long long delta[RMI_MAX_FANOUT - 1];
+};
+
 struct rmi_ctx {
   uint32_t magic;
   int device;
@@ -84,6 +92,8 @@ struct rmi_ctx {
   std::vector<rmi_prof_rec> prof;
   // decode chain: launch kernels with programmatic stream serialization (see pdl_wait below)
   bool pdl;
+  // set by rmi_matmul_q8_0_fanout_dev for the duration of its launches
+  out_fanout fanout;
 };
 
 // Q8_0 / Q4_K weight resident in HBM.
@@ -157,6 +167,12 @@ static inline cudaError_t rmi_launch(const rmi_ctx* ctx, void (*kern)(KArgs...),
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// One f32 result to the primary output and to every extra copy.
+__device__ __forceinline__ void store_fanout(float* o, float v, const out_fanout& fo) {
+  *o = v;
+  for (int i = 0; i < fo.n; i++) *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + fo.delta[i]) = v;
 }
 
 // IEEE f16 -> f32 (exact)

@@ -55,6 +55,7 @@ struct gemm_params {
   size_t n_tiles;  // m_tiles * n_tiles_n; CTAs walk tiles blockIdx.x, +gridDim.x, ...
   size_t act_slabs, act_blocks;
   rmi_dev_status* status;
+  out_fanout fo;  // extra copies of the f32 output (GEMM_EPI_F32)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -483,13 +484,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         float v[CPW];
 #pragma unroll
         for (int c = 0; c < CPW / 2; c++) unpack2(acc[c], &v[2 * c], &v[2 * c + 1]);
-        if (n0 + CPW <= p.col_end && ((p.out_stride | n0) & 3) == 0) {
+        for (int copy = 0; copy <= p.fo.n; copy++) {
+          if (copy > 0) o = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out + row * p.out_stride + n0) + p.fo.delta[copy - 1]);
+          if (n0 + CPW <= p.col_end && ((p.out_stride | n0) & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-          for (int c = 0; c < CPW; c += 4) *reinterpret_cast<float4*>(o + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-        } else {
+            for (int c = 0; c < CPW; c += 4) *reinterpret_cast<float4*>(o + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+          } else {
 #pragma unroll
-          for (int c = 0; c < CPW; c++)
-            if (n0 + c < p.col_end) o[c] = v[c];
+            for (int c = 0; c < CPW; c++)
+              if (n0 + c < p.col_end) o[c] = v[c];
+          }
         }
       }
     }
@@ -596,6 +600,7 @@ int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
   p.act_f32 = a.act_f32;
   p.sums = a.sums;
   p.status = ctx->d_status;
+  p.fo = ctx->fanout;
   const size_t m_tiles = (a.m + 127) / 128;
   const size_t n_cols = a.col_end - a.col_begin;
   if (a.m == 0 || n_cols == 0) return RMI_OK;

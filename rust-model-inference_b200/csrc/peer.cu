@@ -1,0 +1,97 @@
+// Peer-memory plumbing for the row-sharded matmul: one process per GPU on one node.
+//
+// Each rank owns the final [M, N] output buffer and a small flag array, both exported through
+// CUDA IPC; every rank maps its peers' buffers and the matmul stores its column slice straight
+// into all of them (rmi_matmul_q8_0_fanout_dev).  The exchange is closed by a flag round:
+// rank r writes the epoch into slot r of every peer's flag array (release, system scope) and
+// waits, with a time limit, until every slot of its own array shows the epoch.
+#include "common.cuh"
+#include "kernels.cuh"
+
+#include <cstring>
+
+namespace {
+
+struct peer_flags {
+  uint32_t* p[RMI_MAX_FANOUT];
+};
+
+constexpr uint64_t PEER_WAIT_NS = 2000000000ull;  // 2 s
+
+__global__ void peer_signal_wait_kernel(peer_flags flags, int world, int rank, uint32_t epoch, rmi_dev_status* status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  // everything this GPU stored before this kernel (the matmul's peer stores) is ordered before the flag
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[p] + rank), "r"(epoch) : "memory");
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  const uint32_t* mine = flags.p[rank] + p;
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - epoch) >= 0) break;
+    uint64_t now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - t0 > PEER_WAIT_NS) {  // give up: the host reads the status word
+      if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
+        status->where = 20;
+        status->detail = p;
+      }
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+}  // namespace
+
+extern "C" int32_t rmi_ipc_export(rmi_ctx* ctx, const void* dev_ptr, uint8_t* handle64) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_REQUIRE(dev_ptr && handle64, RMI_ERR_BAD_HANDLE, "rmi_ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  RMI_CUDA_CHECK(cudaSetDevice(ctx->device));
+  RMI_CUDA_CHECK(cudaIpcGetMemHandle(&h, const_cast<void*>(dev_ptr)));
+  memcpy(handle64, &h, 64);
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_ipc_open(rmi_ctx* ctx, const uint8_t* handle64, void** out_ptr) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_REQUIRE(handle64 && out_ptr, RMI_ERR_BAD_HANDLE, "rmi_ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  RMI_CUDA_CHECK(cudaSetDevice(ctx->device));
+  RMI_CUDA_CHECK(cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_ipc_close(rmi_ctx* ctx, void* ptr) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  if (!ptr) return RMI_OK;
+  RMI_CUDA_CHECK(cudaSetDevice(ctx->device));
+  RMI_CUDA_CHECK(cudaIpcCloseMemHandle(ptr));
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_peer_signal_wait_dev(rmi_ctx* ctx, uint32_t* const* flags, int32_t world, int32_t rank,
+                                            uint32_t epoch) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_REQUIRE(flags && world >= 1 && world <= RMI_MAX_FANOUT && rank >= 0 && rank < world, RMI_ERR_BAD_SHAPE,
+              "rmi_peer_signal_wait_dev: world %d rank %d", world, rank);
+  peer_flags f = {};
+  for (int32_t i = 0; i < world; i++) {
+    RMI_REQUIRE(flags[i] != nullptr, RMI_ERR_BAD_HANDLE, "rmi_peer_signal_wait_dev: flag array %d is null", i);
+    f.p[i] = flags[i];
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  peer_signal_wait_kernel<<<1, 32, 0, ctx->stream>>>(f, world, rank, epoch, ctx->d_status);
+  return rmi_post_launch(ctx, "peer_signal_wait");
+}
+
+extern "C" int32_t rmi_check_status(rmi_ctx* ctx) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return rmi_check_dev_status(ctx, "rmi_check_status");
+}

@@ -198,7 +198,7 @@ template <int SEM, int LB, int MP>
 __global__ void __launch_bounds__(256)
     q8_gemv_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
                    const float* __restrict__ xs, float* __restrict__ out, size_t out_stride,
-                   size_t row_begin, size_t row_end, size_t first_tile) {
+                   size_t row_begin, size_t row_end, size_t first_tile, const out_fanout fo) {
   constexpr int LPR = 32 / LB;      // lanes per row
   constexpr int NL = LB / 4;        // AVX2 lanes (dp4a groups) per thread
   constexpr int WPT = 16 / LB;      // warps per 16-row tile
@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(256)
     } else {
       r = acc[m][0];
     }
-    if (part == 0 && row >= row_begin && row < row_end) out[m * out_stride + row] = r;
+    if (part == 0 && row >= row_begin && row < row_end) store_fanout(out + m * out_stride + row, r, fo);
   }
 }
 
@@ -303,7 +303,8 @@ template <int SEM, int MP, bool FUSED>
 __global__ void __launch_bounds__(128)
     q8_gemv_staged_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
                           const float* __restrict__ xs, float* __restrict__ out, size_t out_stride, size_t row_begin,
-                          size_t row_end, size_t first_tile, rmi_dev_status* status, gemv_norm_args na) {
+                          size_t row_end, size_t first_tile, rmi_dev_status* status, gemv_norm_args na,
+                          const out_fanout fo) {
   extern __shared__ __align__(128) uint8_t smem[];
   const size_t K = blocks * 32;
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(128)
       const float t = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
       r = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
     }
-    if (l == 0 && row >= row_begin && row < row_end) out[m * out_stride + row] = r;
+    if (l == 0 && row >= row_begin && row < row_end) store_fanout(out + m * out_stride + row, r, fo);
   }
 }
 
@@ -566,7 +567,7 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
   dim3 grid((unsigned)((warps + wpc - 1) / wpc), (unsigned)n_groups);
   const int pr = rmi_prof_begin(ctx, "q8_gemv");
   cudaError_t le = rmi_launch(ctx, kern, grid, dim3(wpc * 32), smem, w->d_tile16, blocks, xq, xs, out, out_stride,
-                              row_begin, row_end, first_tile);
+                              row_begin, row_end, first_tile, ctx->fanout);
   rmi_prof_end(ctx, pr);
   if (le != cudaSuccess) {
     rmi_set_error("launch of q8_gemv failed: %s", cudaGetErrorString(le));
@@ -594,7 +595,7 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
       dim3 grid((unsigned)t1, (unsigned)n_groups);
       const int pr = rmi_prof_begin(ctx, "q8_gemv");
       cudaError_t le = rmi_launch(ctx, kern, grid, dim3(128), smem, w->d_tile16, blocks, xq, xs, out, out_stride,
-                                  row_begin, row_end, row_begin / 16, ctx->d_status, gemv_norm_args{});
+                                  row_begin, row_end, row_begin / 16, ctx->d_status, gemv_norm_args{}, ctx->fanout);
       rmi_prof_end(ctx, pr);
       if (le != cudaSuccess) {
         rmi_set_error("launch of q8_gemv_staged failed: %s", cudaGetErrorString(le));
@@ -664,7 +665,7 @@ static int32_t gemv_fused_launch(rmi_ctx* ctx, const rmi_weight* w, const gemv_n
   const int pr = rmi_prof_begin(ctx, "q8_gemv");
   cudaError_t le = rmi_launch(ctx, kern, dim3((unsigned)w->n_tiles16, 1), dim3(128), smem, w->d_tile16, blocks,
                               (const uint8_t*)nullptr, (const float*)nullptr, out, out_stride, (size_t)0, w->n_rows,
-                              (size_t)0, ctx->d_status, na);
+                              (size_t)0, ctx->d_status, na, out_fanout{});
   rmi_prof_end(ctx, pr);
   if (le != cudaSuccess) {
     rmi_set_error("launch of q8_gemv_fused_norm failed: %s", cudaGetErrorString(le));

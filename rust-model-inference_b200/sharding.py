@@ -4,7 +4,9 @@ The path shards by weight row (= output column): rank r of g holds rows [r*N/g, 
 partition the reference uses across threads (src/ops/kernel/q8_0/parallel.rs:124-139) and plans
 across devices (PlacementSlice::Rows, src/format/load_plan.rs:19-22).  The activation is
 replicated and quantized locally (deterministic, so identical on every rank); the only exchange
-is an all-gather of the [M, N/g] results, after which a device kernel restores row-major [M, N].
+is an all-gather of the [M, N/g] results, after which a device kernel restores row-major [M, N]
+(ShardedLinear), or -- fused -- the matmul stores its column slice straight into every rank's
+[M, N] buffer through peer-mapped pointers and a flag round closes the step (PeerShardedLinear).
 """
 from __future__ import annotations
 
@@ -61,3 +63,86 @@ class ShardedLinear:
         self.pkg.unshard_cols_dev(self.pkg.context(), gathered.data_ptr(), self.world, m, self.n_out // self.world,
                                   out_full.data_ptr())
         return out_full
+
+
+def exchange_handles(local: bytes, rank: int, world: int, all_gather_object) -> list:
+    """Every rank contributes one opaque handle; returns the list indexed by rank.
+    `all_gather_object(out_list, obj)` has torch.distributed's signature."""
+    out = [None] * world
+    all_gather_object(out, (rank, local))
+    table = [None] * world
+    for r, h in out:
+        if table[r] is not None:
+            raise ValueError(f"rank {r} reported twice")
+        table[r] = h
+    if any(h is None for h in table):
+        raise ValueError("a rank did not report its handle")
+    return table
+
+
+def peer_pointer_table(handles: list, rank: int, own_ptr: int, open_handle) -> list:
+    """Pointer of every rank's buffer as seen from `rank`: its own allocation, IPC mappings for the others."""
+    return [own_ptr if r == rank else open_handle(h) for r, h in enumerate(handles)]
+
+
+def rotate_own_first(ptrs: list, rank: int) -> list:
+    """Fan-out order: this rank's buffer first (the primary store), then the peers starting at
+    rank+1 so that the ranks do not all write to the same peer at the same time."""
+    return [ptrs[(rank + i) % len(ptrs)] for i in range(len(ptrs))]
+
+
+class PeerShardedLinear:
+    """Row-sharded Q8_0 linear whose result lands complete on every rank without a collective call:
+    the matmul's epilogue stores this rank's columns into all ranks' [m_max, n_out] buffers."""
+
+    def __init__(self, pkg, weight_bytes_of_shard, n_in: int, n_out: int, rank: int, world: int, m_max: int, group=None):
+        import torch.distributed as dist
+        if n_out % world != 0:
+            raise ValueError("equal shards: n_out must be a multiple of the world size")
+        if world > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch domain)")
+        self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
+        self.n_in, self.n_out, self.m_max = n_in, n_out, m_max
+        self.row_begin, self.row_end = shard_rows(n_out, world, rank)
+        self.ctx = pkg.context()
+        self.weight = pkg.QuantizedTensor.from_bytes(weight_bytes_of_shard, pkg.GGML_Q8_0, n_in,
+                                                     self.row_end - self.row_begin)
+        self.out_ptr = self.ctx.dev_alloc(m_max * n_out * 4)
+        self.flag_ptr = self.ctx.dev_alloc(256)
+        self.ctx.h2d(self.flag_ptr, np.zeros(64, np.uint32))
+        self.ctx.sync()
+        if world > 1:
+            gather = lambda out, obj: dist.all_gather_object(out, obj, group=group)
+            outs = exchange_handles(self.ctx.ipc_export(self.out_ptr), rank, world, gather)
+            flags = exchange_handles(self.ctx.ipc_export(self.flag_ptr), rank, world, gather)
+            self._out_all = peer_pointer_table(outs, rank, self.out_ptr, self.ctx.ipc_open)
+            self._flag_all = peer_pointer_table(flags, rank, self.flag_ptr, self.ctx.ipc_open)
+            dist.barrier(group=group)  # every rank has mapped every buffer before the first store
+        else:
+            self._out_all, self._flag_all = [self.out_ptr], [self.flag_ptr]
+        self._fan = rotate_own_first(self._out_all, rank)
+        self.epoch = 0
+
+    def forward_dev(self, x_ptr: int, m: int) -> int:
+        """x [m, n_in] f32 on the device -> pointer of this rank's [m, n_out] buffer, complete (all
+        ranks' columns) once the enqueued work has run.  A consumer must finish reading the buffer
+        before the next call's stores arrive: call forward_dev again only after that."""
+        if m > self.m_max:
+            raise ValueError("m exceeds m_max")
+        self.pkg.matmul_q8_0_fanout_dev(self.weight, x_ptr, m, self._fan, self.n_out, self.row_begin)
+        self.epoch += 1
+        self.pkg.peer_signal_wait_dev(self.ctx, self._flag_all, self.rank, self.epoch)
+        return self.out_ptr
+
+    def close(self):
+        self.ctx.sync()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group)  # no peer is still storing into a buffer that is about to go
+        for r, (o, f) in enumerate(zip(self._out_all, self._flag_all)):
+            if r != self.rank:
+                self.ctx.ipc_close(o)
+                self.ctx.ipc_close(f)
+        self.ctx.dev_free(self.out_ptr)
+        self.ctx.dev_free(self.flag_ptr)
+        self.weight.free()

@@ -50,3 +50,143 @@ def test_sharded_linear_single_rank(rmi):
     torch.cuda.synchronize()
     assert torch.equal(out_full, out_local)
     ctx.set_semantics(rmi.SEM_AVX2)
+
+
+@pytest.mark.parametrize("sem", ["SEM_NEON", "SEM_AVX2"])
+@pytest.mark.parametrize("m", [1, 2, 16, 130])
+def test_fanout_stores_land_in_every_buffer(rmi, m, sem):
+    """One GPU plays every rank in turn; each rank's matmul stores its column slice into all g
+    'final' buffers (here local allocations).  Every buffer must equal the unsharded matmul."""
+    torch = pytest.importorskip("torch")
+    ctx = rmi.context(0)
+    ctx.set_semantics(getattr(rmi, sem))
+    n, k, g = 1024, 256, 4
+    x = torch.from_numpy(rmi.synth.normal((m, k), seed=4)).cuda()
+    full_w = rmi.QuantizedTensor.from_bytes(rmi.synth.q8_0_weight_rows(n, k, seed=3, row_begin=0, row_end=n),
+                                            rmi.GGML_Q8_0, k, n)
+    ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    rmi.matmul_q8_0_dev(full_w, x.data_ptr(), m, ref.data_ptr())
+    finals = [torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda") for _ in range(g)]
+    torch.cuda.synchronize()
+    for r in range(g):
+        s, e = rmi.sharding.shard_rows(n, g, r)
+        shard = rmi.QuantizedTensor.from_bytes(rmi.synth.q8_0_weight_rows(n, k, seed=3, row_begin=s, row_end=e),
+                                               rmi.GGML_Q8_0, k, e - s)
+        fan = rmi.sharding.rotate_own_first([f.data_ptr() for f in finals], r)
+        rmi.matmul_q8_0_fanout_dev(shard, x.data_ptr(), m, fan, n, s)
+        ctx.sync()
+        shard.free()
+    for f in finals:
+        assert torch.equal(f.view(torch.int32), ref.view(torch.int32))
+    full_w.free()
+    ctx.set_semantics(rmi.SEM_AVX2)
+
+
+def test_fanout_rejects_bad_arguments(rmi):
+    ctx = rmi.context(0)
+    w = rmi.QuantizedTensor.from_bytes(rmi.synth.q8_0_weight_rows(64, 64, seed=1, row_begin=0, row_end=64),
+                                       rmi.GGML_Q8_0, 64, 64)
+    buf = ctx.dev_alloc(64 * 64 * 4)
+    with pytest.raises(rmi.RmiError):
+        rmi.matmul_q8_0_fanout_dev(w, buf, 1, [], 64, 0)                 # no outputs
+    with pytest.raises(rmi.RmiError):
+        rmi.matmul_q8_0_fanout_dev(w, buf, 1, [buf] * 9, 64, 0)          # too many
+    with pytest.raises(rmi.RmiError):
+        rmi.matmul_q8_0_fanout_dev(w, buf, 1, [buf], 64, 32)             # columns past the stride
+    ctx.dev_free(buf)
+    w.free()
+
+
+def test_peer_sharded_linear_single_rank_and_flag_round(rmi):
+    """world = 1: the fan-out is this rank's own buffer and the flag round completes on its own flag."""
+    torch = pytest.importorskip("torch")
+    ctx = rmi.context(0)
+    ctx.set_semantics(rmi.SEM_NEON)
+    n, k, m = 512, 128, 7
+    wb = rmi.synth.q8_0_weight_rows(n, k, seed=8, row_begin=0, row_end=n)
+    lin = rmi.sharding.PeerShardedLinear(rmi, wb, k, n, rank=0, world=1, m_max=8)
+    x = torch.from_numpy(rmi.synth.normal((m, k), seed=9)).cuda()
+    ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    rmi.matmul_q8_0_dev(lin.weight, x.data_ptr(), m, ref.data_ptr())
+    torch.cuda.synchronize()
+    for _ in range(3):
+        ptr = lin.forward_dev(x.data_ptr(), m)
+    ctx.check_status()
+    got = np.empty((m, n), np.float32)
+    ctx.d2h(got, ptr)
+    assert np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
+    assert lin.epoch == 3
+    lin.close()
+    ctx.set_semantics(rmi.SEM_AVX2)
+
+
+def test_ipc_export_gives_a_64_byte_handle(rmi):
+    ctx = rmi.context(0)
+    p = ctx.dev_alloc(4096)
+    h = ctx.ipc_export(p)
+    assert isinstance(h, bytes) and len(h) == 64 and any(h)
+    ctx.dev_free(p)
+
+
+_TWO_RANK_SCRIPT = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["RMI_REPO"])
+from __graft_entry__ import load_package
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo", rank=rank, world_size=world)
+pkg = load_package()
+ctx = pkg.context(rank)
+ctx.set_semantics(pkg.SEM_NEON)
+n, k = 2048, 512
+s, e = pkg.sharding.shard_rows(n, world, rank)
+lin = pkg.sharding.PeerShardedLinear(pkg, pkg.synth.q8_0_weight_rows(n, k, seed=3, row_begin=s, row_end=e), k, n, rank, world, m_max=160)
+full = pkg.QuantizedTensor.from_bytes(pkg.synth.q8_0_weight_rows(n, k, seed=3, row_begin=0, row_end=n), pkg.GGML_Q8_0, k, n)
+ok = True
+for m in (1, 16, 160):
+    x = torch.from_numpy(pkg.synth.normal((m, k), seed=4)).cuda()
+    ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    pkg.matmul_q8_0_dev(full, x.data_ptr(), m, ref.data_ptr())
+    for _ in range(2):
+        ptr = lin.forward_dev(x.data_ptr(), m)
+        ctx.check_status()
+        dist.barrier()          # both ranks have read nothing yet; keeps the rounds apart
+    got = np.empty((m, n), np.float32)
+    ctx.d2h(got, ptr)
+    ok = ok and np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
+    dist.barrier()
+lin.close()
+dist.destroy_process_group()
+print("RANK_OK" if ok else "RANK_MISMATCH", flush=True)
+sys.exit(0 if ok else 1)
+"""
+
+
+def test_two_ranks_on_two_gpus_store_into_each_other(rmi, tmp_path):
+    """Needs two GPUs: the ranks wait on each other's flags, so they must not share a device."""
+    torch = pytest.importorskip("torch")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs (ranks that wait on one another never share one GPU)")
+    import os, subprocess, sys, socket
+    script = tmp_path / "two_ranks.py"
+    script.write_text(_TWO_RANK_SCRIPT)
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   RMI_REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append(out)
+    for p, out in zip(procs, outs):
+        assert p.returncode == 0 and "RANK_OK" in out, out[-2000:]

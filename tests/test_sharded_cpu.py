@@ -80,3 +80,61 @@ def test_sharded_weight_generator_is_shard_consistent(rmi):
     for s, e in ((0, 1024), (1000, 2100), (2999, 3000), (1024, 2048)):
         part = rmi.synth.q8_0_weight_rows(3000, 64, seed=9, row_begin=s, row_end=e)
         assert np.array_equal(part, whole[s * rb:e * rb])
+
+
+def _handle_worker(rank, world, port, q):
+    """The peer-store variant's host logic: handle exchange and pointer tables over gloo, with
+    fake handles and a fake opener (no GPU)."""
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        mine = bytes([rank + 1]) * 64
+        table = pkg.sharding.exchange_handles(mine, rank, world, dist.all_gather_object)
+        ptrs = pkg.sharding.peer_pointer_table(table, rank, own_ptr=1000 + rank, open_handle=lambda h: 2000 + h[0])
+        q.put((rank, table, ptrs, pkg.sharding.rotate_own_first(ptrs, rank)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_exchange_ipc_handles_and_build_pointer_tables():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_handle_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        rank, table, ptrs, fan = q.get(timeout=120)
+        got[rank] = (table, ptrs, fan)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank in range(world):
+        table, ptrs, fan = got[rank]
+        assert table == [bytes([1]) * 64, bytes([2]) * 64]
+        # own allocation for itself, the opener's mapping for the peer
+        assert ptrs[rank] == 1000 + rank and ptrs[1 - rank] == 2000 + (2 - rank)
+        assert fan[0] == ptrs[rank] and sorted(fan) == sorted(ptrs)
+
+
+def test_exchange_handles_rejects_duplicates_and_gaps():
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    pkg = load_package()
+
+    def dup(out, obj):
+        out[0], out[1] = (0, b"a"), (0, b"b")
+
+    def gap(out, obj):
+        out[0], out[1] = (0, b"a"), (1, None)
+
+    with pytest.raises(ValueError):
+        pkg.sharding.exchange_handles(b"a", 0, 2, dup)
+    with pytest.raises(ValueError):
+        pkg.sharding.exchange_handles(b"a", 0, 2, gap)
+    assert pkg.sharding.rotate_own_first([10, 11, 12, 13], 2) == [12, 13, 10, 11]
