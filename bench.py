@@ -375,42 +375,57 @@ def main():
                     "frac_of_bf16_peak": achieved / bf16_peak, "avg_kernel_us": ms_k / n_k * 1e3, "launches": n_k,
                     "down_gemm_avg_us": (ms_d / n_d * 1e3) if n_d else None,
                     "down_gemm_tops": (OPS_DOWN / (ms_d / n_d / 1e3) / 1e12) if n_d else None,
-                    "traffic": None}
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
+                    # the committed ncu capture (profiles/gemm_tc_swiglu_ffn_m512.md); algorithmic bytes 7.65 MB
+                    "traffic": 7703552, "traffic_source": "ncu capture summarised in profiles/gemm_tc_swiglu_ffn_m512.md"}
     else:   # AVX2 semantics keep every M on the CUDA-core kernels
         n_g, ms_g = ctx.prof_read("q8_gemv")
         roofline = {"bound": "tensor", "kernel": "q8_gemv_kernel (CUDA cores; AVX2 semantics)", "achieved": value,
                     "peak": int8_peak, "unit": "TFLOP/s", "frac": value / int8_peak, "traffic": None}
 
-    # end to end through the host-pointer C ABI call: pinned x in, pinned out back, every step
-    e2e_steps = min(args.steps, 300)
-    hx = torch.from_numpy(pkg.synth.normal((M, E), seed=99 + rank)).pin_memory()
-    hout = torch.empty((M, E), dtype=torch.float32).pin_memory()
-    hx_np, hout_np = hx.numpy(), hout.numpy()
+    # end to end through the host-pointer C ABI: every step's x comes from pinned host memory and its result
+    # goes back to pinned host memory.  Headline: the pipelined entry point (copies of neighbouring steps overlap
+    # the arithmetic); the one-call-per-step entry point is reported beside it.
+    e2e_steps = min(args.steps, 304)
+    NBUF_H = 4
+    hxs = [torch.from_numpy(pkg.synth.normal((M, E), seed=99 + rank + 7 * j)).pin_memory() for j in range(NBUF_H)]
+    houts = [torch.empty((M, E), dtype=torch.float32).pin_memory() for _ in range(NBUF_H)]
     lib, C = pkg.lib(), __import__("ctypes")
-    wgu0, wd0 = sets[0][0], sets[0][1]
 
-    def e2e_step(i):
+    def e2e_serial_step(i):
         wgu, wd = sets[i % R][0], sets[i % R][1]
-        st = lib.rmi_ffn_swiglu_q8_0(ctx.handle, wgu._h, wd._h, C.c_void_p(hx_np.ctypes.data), C.c_size_t(M),
-                                     C.c_void_p(hout_np.ctypes.data))
+        st = lib.rmi_ffn_swiglu_q8_0(ctx.handle, wgu._h, wd._h, C.c_void_p(hxs[i % NBUF_H].data_ptr()), C.c_size_t(M),
+                                     C.c_void_p(houts[i % NBUF_H].data_ptr()))
         if st != 0:
             raise RuntimeError(lib.rmi_last_error().decode())
 
+    def e2e_pipelined(n):
+        pkg.ffn_swiglu_q8_0_pipelined([sets[i % R][0] for i in range(n)], [sets[i % R][1] for i in range(n)],
+                                      [hxs[i % NBUF_H].data_ptr() for i in range(n)],
+                                      [houts[i % NBUF_H].data_ptr() for i in range(n)], M)
+
+    def timed(fn):
+        barrier()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) * 1e3], dtype=torch.float64, device="cuda")
+        barrier()
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return float(dt.item())
+
     for i in range(5):
-        e2e_step(i)
-    barrier()
-    e0.record(stream)
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e1.record(stream)
-    barrier()
-    e2e_ms = torch.tensor([max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        e2e_serial_step(i)
+    serial_ms = timed(lambda: [e2e_serial_step(i) for i in range(e2e_steps)])
+    e2e_pipelined(8)
+    e2e_ms_v = timed(lambda: e2e_pipelined(e2e_steps))
+    e2e_ms = torch.tensor([e2e_ms_v], dtype=torch.float64, device="cuda")
     e2e = {"value": world * OPS_STEP * e2e_steps / (float(e2e_ms.item()) / 1e3) / 1e12, "unit": "TOPS",
            "h2d_bytes_per_step": M * E * 4, "d2h_bytes_per_step": M * E * 4, "steps": e2e_steps,
-           "api": "rmi_ffn_swiglu_q8_0 (host pointers, pinned)"}
+           "serial_value": world * OPS_STEP * e2e_steps / (serial_ms / 1e3) / 1e12,
+           "api": "rmi_ffn_swiglu_q8_0_pipelined (host pointers, pinned; copies of neighbouring steps overlap the "
+                  "arithmetic); serial_value = one rmi_ffn_swiglu_q8_0 call per step"}
 
     line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",

@@ -164,6 +164,15 @@ int32_t rmi_ffn_swiglu_q8_0(rmi_ctx* ctx, const rmi_weight* w_gate_up, const rmi
                             const float* x, size_t m, float* out);
 int32_t rmi_ffn_swiglu_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w_gate_up,
                                 const rmi_weight* w_down, const float* x, size_t m, float* out);
+/* A run of n_batches FFN calls (batch i: weights wgu[i]/wd[i], host input x[i] [m, n_embd], host
+ * output out[i] [m, n_embd]; all batches the same m and widths) with the host<->device copies of
+ * neighbouring batches overlapped with the arithmetic on three streams.  Results are those of
+ * n_batches calls of rmi_ffn_swiglu_q8_0.  Pinned host buffers are needed for the overlap;
+ * pageable ones still give correct results.  No counterpart in the reference, whose FFN works
+ * in host memory (src/models/qwen3.rs:968-1052). */
+int32_t rmi_ffn_swiglu_q8_0_pipelined(rmi_ctx* ctx, const rmi_weight* const* w_gate_up,
+                                      const rmi_weight* const* w_down, const float* const* x,
+                                      float* const* out, size_t n_batches, size_t m);
 /* silu_mul_inplace (src/ops/activation/mod.rs:137-151): up[i] *= gate[i]/(1+exp(-gate[i])) */
 int32_t rmi_silu_mul(rmi_ctx* ctx, const float* gate, float* up, size_t n);
 

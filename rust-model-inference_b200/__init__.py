@@ -427,6 +427,21 @@ def ffn_swiglu_q8_0(w_gate_up: QuantizedTensor, w_down: QuantizedTensor, x) -> n
     return out
 
 
+def ffn_swiglu_q8_0_pipelined(w_gate_up, w_down, x_ptrs, out_ptrs, m: int):
+    """A run of FFN calls over host buffers (addresses as integers, pinned for overlap) with the copies of
+    neighbouring batches overlapped with the arithmetic.  w_gate_up / w_down: one QuantizedTensor per batch."""
+    n = len(x_ptrs)
+    if not (len(w_gate_up) == len(w_down) == len(out_ptrs) == n):
+        raise ValueError("one weight pair, one input and one output per batch")
+    if n == 0:
+        return
+    wg = (C.c_void_p * n)(*[w._h for w in w_gate_up])
+    wd = (C.c_void_p * n)(*[w._h for w in w_down])
+    xs = (C.c_void_p * n)(*[C.c_void_p(p) for p in x_ptrs])
+    outs = (C.c_void_p * n)(*[C.c_void_p(p) for p in out_ptrs])
+    _check(lib().rmi_ffn_swiglu_q8_0_pipelined(w_gate_up[0]._ctx.handle, wg, wd, xs, outs, _sz(n), _sz(m)))
+
+
 # Device-pointer variants (stream-ordered, no synchronisation): pointers are integers, e.g.
 # torch.Tensor.data_ptr() or Context.dev_alloc().
 

@@ -170,6 +170,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->prof_on = false;
   c->pdl = false;
   c->fanout = out_fanout{};
+  c->pipe_ready = false;
   for (int i = 0; i < 8; i++) {
     c->scratch[i] = nullptr;
     c->scratch_bytes[i] = 0;
@@ -195,6 +196,15 @@ extern "C" int32_t rmi_destroy(rmi_ctx* ctx) {
     if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
+  if (ctx->pipe_ready) {
+    cudaStreamDestroy(ctx->copy_in);
+    cudaStreamDestroy(ctx->copy_out);
+    for (int i = 0; i < 2; i++) {
+      cudaEventDestroy(ctx->ev_in[i]);
+      cudaEventDestroy(ctx->ev_compute[i]);
+      cudaEventDestroy(ctx->ev_out[i]);
+    }
+  }
   cudaStreamDestroy(ctx->own_stream);
   ctx->magic = 0;
   delete ctx;
@@ -492,7 +502,8 @@ static bool use_tensor_cores(const rmi_ctx* ctx, size_t m) {
   // accumulate.  The AVX2 variant accumulates eight partial sums per block, so it stays on
   // the CUDA-core kernels at every m to remain bit-exact.
   static const bool disabled = getenv("RMI_DISABLE_TC") != nullptr;
-  return m > 32 && ctx->sem != RMI_SEM_AVX2 && !disabled;
+  static const size_t min_m = getenv("RMI_TC_MIN_M") ? (size_t)atoi(getenv("RMI_TC_MIN_M")) : 32;
+  return m > min_m && ctx->sem != RMI_SEM_AVX2 && !disabled;
 }
 
 extern "C" int32_t rmi_quantize_q8_0_dev(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8,
@@ -792,6 +803,65 @@ extern "C" int32_t rmi_ffn_swiglu_q8_0(rmi_ctx* ctx, const rmi_weight* wgu, cons
   if (use_tensor_cores(ctx, m)) return rmi_check_dev_status(ctx, "rmi_ffn_swiglu_q8_0");
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   return RMI_OK;
+}
+
+static int32_t ensure_pipe(rmi_ctx* ctx) {
+  if (ctx->pipe_ready) return RMI_OK;
+  RMI_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+  RMI_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; i++) {
+    RMI_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+    RMI_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->ev_compute[i], cudaEventDisableTiming));
+    RMI_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming));
+  }
+  ctx->pipe_ready = true;
+  return RMI_OK;
+}
+
+// A run of FFN calls with the copies of neighbouring batches overlapped with the arithmetic:
+// batch i is copied in on one stream while batch i-1 is computed on the context's stream and
+// batch i-2 is copied out on a third (two device buffers per direction, events between them).
+extern "C" int32_t rmi_ffn_swiglu_q8_0_pipelined(rmi_ctx* ctx, const rmi_weight* const* wgu,
+                                                 const rmi_weight* const* wd, const float* const* x,
+                                                 float* const* out, size_t n_batches, size_t m) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  if (n_batches == 0 || m == 0) return RMI_OK;
+  RMI_REQUIRE(wgu && wd && x && out, RMI_ERR_BAD_HANDLE, "rmi_ffn_swiglu_q8_0_pipelined: null argument");
+  for (size_t i = 0; i < n_batches; i++) {
+    RMI_TRY(rmi_check_weight(wgu[i], RMI_GGML_Q8_0));
+    RMI_TRY(rmi_check_weight(wd[i], RMI_GGML_Q8_0));
+    RMI_REQUIRE(x[i] && out[i], RMI_ERR_BAD_HANDLE, "rmi_ffn_swiglu_q8_0_pipelined: null buffer in batch %zu", i);
+    RMI_REQUIRE(wgu[i]->n_in == wgu[0]->n_in && wd[i]->n_rows == wd[0]->n_rows, RMI_ERR_BAD_SHAPE,
+                "rmi_ffn_swiglu_q8_0_pipelined: batch %zu has a different width", i);
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  RMI_TRY(ensure_pipe(ctx));
+  const size_t in_bytes = m * wgu[0]->n_in * 4, out_bytes = m * wd[0]->n_rows * 4;
+  const size_t in_slot = (in_bytes + 255) & ~(size_t)255, out_slot = (out_bytes + 255) & ~(size_t)255;
+  uint8_t *dx, *dout;
+  RMI_TRY(rmi_scratch(ctx, 5, 2 * in_slot, (void**)&dx));
+  RMI_TRY(rmi_scratch(ctx, 6, 2 * out_slot, (void**)&dout));
+  // work already queued on the context's stream may still use the scratch buffers
+  RMI_CUDA_CHECK(cudaEventRecord(ctx->ev_compute[0], ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_compute[0], 0));
+  for (size_t i = 0; i < n_batches; i++) {
+    const int b = (int)(i & 1);
+    // dx[b] was read by the arithmetic of batch i-2
+    if (i >= 2) RMI_CUDA_CHECK(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_compute[b], 0));
+    RMI_CUDA_CHECK(cudaMemcpyAsync(dx + b * in_slot, x[i], in_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    RMI_CUDA_CHECK(cudaEventRecord(ctx->ev_in[b], ctx->copy_in));
+    RMI_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[b], 0));
+    // dout[b] was copied out for batch i-2
+    if (i >= 2) RMI_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[b], 0));
+    RMI_TRY(ffn_device(ctx, wgu[i], wd[i], reinterpret_cast<const float*>(dx + b * in_slot), m,
+                       reinterpret_cast<float*>(dout + b * out_slot)));
+    RMI_CUDA_CHECK(cudaEventRecord(ctx->ev_compute[b], ctx->stream));
+    RMI_CUDA_CHECK(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_compute[b], 0));
+    RMI_CUDA_CHECK(cudaMemcpyAsync(out[i], dout + b * out_slot, out_bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+    RMI_CUDA_CHECK(cudaEventRecord(ctx->ev_out[b], ctx->copy_out));
+  }
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->copy_out));
+  return rmi_check_dev_status(ctx, "rmi_ffn_swiglu_q8_0_pipelined");
 }
 
 extern "C" int32_t rmi_silu_mul(rmi_ctx* ctx, const float* gate, float* up, size_t n) {

@@ -94,6 +94,10 @@ struct rmi_ctx {
   bool pdl;
   // set by rmi_matmul_q8_0_fanout_dev for the duration of its launches
   out_fanout fanout;
+  // copy streams and events of the pipelined host entry point (created on first use)
+  cudaStream_t copy_in, copy_out;
+  cudaEvent_t ev_in[2], ev_compute[2], ev_out[2];
+  bool pipe_ready;
 };
 
 // Q8_0 / Q4_K weight resident in HBM.

@@ -103,6 +103,36 @@ def test_ffn_prefill_bit_exact(rmi, ctx, sem, m, e, ff):
         assert rel_err(got[:8], avx) < 2e-2  # different activation rounding; sanity bound only
 
 
+@pytest.mark.parametrize("sem,m", [(orc.SEM_NEON, 130), (orc.SEM_AVX2, 3), (orc.SEM_SCALAR, 40)])
+def test_ffn_pipelined_batches_equal_the_oracle_per_batch(rmi, ctx, sem, m):
+    """Seven batches over two alternating weight sets, copies overlapped with the arithmetic:
+    every batch must carry the oracle's bits (and so those of the one-batch entry point)."""
+    torch = pytest.importorskip("torch")
+    ctx.set_semantics(sem)
+    e, ff, n = 256, 768, 7
+    raw, sets = [], []
+    for k in range(2):
+        g, u, d = (rmi.synth.q8_0_weight(ff, e, seed=10 + k), rmi.synth.q8_0_weight(ff, e, seed=20 + k),
+                   rmi.synth.q8_0_weight(e, ff, seed=30 + k))
+        raw.append((g, u, d))
+        sets.append((rmi.QuantizedTensor.from_bytes(g, rmi.GGML_Q8_0, e, ff).fuse_vstack(
+            rmi.QuantizedTensor.from_bytes(u, rmi.GGML_Q8_0, e, ff)), rmi.QuantizedTensor.from_bytes(d, rmi.GGML_Q8_0, ff, e)))
+    xs = [torch.from_numpy(rmi.synth.normal((m, e), seed=40 + i)).pin_memory() for i in range(n)]
+    outs = [torch.full((m, e), float("nan")).pin_memory() for _ in range(n)]
+    rmi.ffn_swiglu_q8_0_pipelined([sets[i % 2][0] for i in range(n)], [sets[i % 2][1] for i in range(n)],
+                                  [x.data_ptr() for x in xs], [o.data_ptr() for o in outs], m)
+    for i in range(n):
+        g, u, d = raw[i % 2]
+        ref = orc.ffn_swiglu_q8_0(g, u, d, xs[i].numpy(), e, ff, sem, threads=4)
+        assert np.array_equal(bits(outs[i].numpy()), bits(ref)), i
+    # pageable buffers: still correct
+    x_np, o_np = rmi.synth.normal((m, e), seed=77), np.zeros((m, e), np.float32)
+    rmi.ffn_swiglu_q8_0_pipelined([sets[0][0]], [sets[0][1]], [x_np.ctypes.data], [o_np.ctypes.data], m)
+    assert np.array_equal(bits(o_np), bits(rmi.ffn_swiglu_q8_0(sets[0][0], sets[0][1], x_np)))
+    with pytest.raises(ValueError):
+        rmi.ffn_swiglu_q8_0_pipelined([sets[0][0]], [], [x_np.ctypes.data], [o_np.ctypes.data], m)
+
+
 def test_silu_mul_matches_oracle_bits(rmi, ctx):
     g = rmi.synth.normal((3072,), seed=5) * np.float32(3.0)
     u = rmi.synth.normal((3072,), seed=6)
