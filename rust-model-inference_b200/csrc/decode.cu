@@ -98,27 +98,11 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
 
 // Per-head q/k rms_norm, NeoX rope, f16 conversion; K and V appended to the cache.
 // grid (batch, n_head + 2*n_head_kv), one warp per head.
-__global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_head, size_t n_head_kv, size_t hd,
-                                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
-                                       const float* __restrict__ rope, const int* __restrict__ d_step,
-                                       uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
-                                       uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
-                                       size_t capacity) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const size_t b = blockIdx.x, head = blockIdx.y;
-  const int lane = threadIdx.x;
-  const int step = *d_step;
-  const size_t nq = n_head * hd, nk = n_head_kv * hd, half = hd / 2;
-  const float* src = qkv + b * (nq + 2 * nk) + head * hd;
-  const size_t cache_row = ((b * n_layer + layer) * capacity + (size_t)step) * nk;
-  if (head >= n_head + n_head_kv) {  // V: straight f16 conversion
-    const size_t kvh = head - n_head - n_head_kv;
-    for (size_t i = lane; i < hd; i += 32) v_cache[cache_row + kvh * hd + i] = f32_to_f16_bits(src[i]);
-    return;
-  }
-  const bool is_q = head < n_head;
-  const float* nw = is_q ? q_norm : k_norm;
+// One head (hd values at src) by one warp: optional rms norm with weights nw (norm.rs:3-11), NeoX
+// rotation with the (cos, sin) pairs of `tab` (rope.rs:21-37), f16 result (RNE) at dst.
+__device__ __forceinline__ void norm_rope_head_f16(const float* __restrict__ src, const float* __restrict__ nw, float eps,
+                                                   const float* __restrict__ tab, size_t hd, int lane, uint16_t* dst) {
+  const size_t half = hd / 2;
   double part = 0.0;
   for (size_t i = lane; i < hd; i += 32) part += (double)__fmul_rn(src[i], src[i]);
   part = warp_sum_f64(part);
@@ -127,8 +111,6 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
     const float mean_sq = (float)(part / (double)hd);
     sc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
   }
-  const float* tab = rope + (size_t)step * hd;  // [pos][half][2]
-  uint16_t* dst = is_q ? q16 + b * nq + head * hd : k_cache + cache_row + (head - n_head) * hd;
   for (size_t i = lane; i < half; i += 32) {
     float x0 = src[i], x1 = src[i + half];
     if (nw) {
@@ -143,6 +125,30 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
   }
 }
 
+__global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_head, size_t n_head_kv, size_t hd,
+                                       const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                       const float* __restrict__ rope, const int* __restrict__ d_step,
+                                       uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
+                                       uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
+                                       size_t capacity) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t b = blockIdx.x, head = blockIdx.y;
+  const int lane = threadIdx.x;
+  const int step = *d_step;
+  const size_t nq = n_head * hd, nk = n_head_kv * hd;
+  const float* src = qkv + b * (nq + 2 * nk) + head * hd;
+  const size_t cache_row = ((b * n_layer + layer) * capacity + (size_t)step) * nk;
+  if (head >= n_head + n_head_kv) {  // V: straight f16 conversion
+    const size_t kvh = head - n_head - n_head_kv;
+    for (size_t i = lane; i < hd; i += 32) v_cache[cache_row + kvh * hd + i] = f32_to_f16_bits(src[i]);
+    return;
+  }
+  const bool is_q = head < n_head;
+  uint16_t* dst = is_q ? q16 + b * nq + head * hd : k_cache + cache_row + (head - n_head) * hd;
+  norm_rope_head_f16(src, is_q ? q_norm : k_norm, eps, rope + (size_t)step * hd, hd, lane, dst);
+}
+
 // Attention for one (sequence, kv head) by a thread-block cluster of CL CTAs; the `group`
 // query heads that share the kv head are processed together.  CTA r owns the time steps
 // [r*chunk, (r+1)*chunk): it stages its K and V rows in shared memory (cp.async, V overlapped
@@ -152,12 +158,26 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
 // reference's sequential f32 sum, divide, f16), forms the f64 partial of P.V over its own
 // steps and sends it to CTA 0, which adds the partials in rank order, re-quantizes the
 // group*hd outputs to Q8_0 for the Wo projection and writes them.
-template <int SEM>
+//
+// With fq.qkv set the kernel also does the step's q/k norm + rotation and cache write itself
+// (qwen3.rs:851-870): every CTA derives the group's f16 query heads from the f32 projection, and
+// the CTA that owns the current time step derives the new K and V rows, keeps them in its staged
+// tiles and stores them into the caches.
+struct attn_fused_qk {
+  const float* qkv;     // [batch][nq + 2 nk] f32 projections of this step, or null
+  const float* q_norm;  // may be null
+  const float* k_norm;  // may be null
+  const float* rope;    // [pos][hd/2][2]
+  float eps;
+};
+
+template <int SEM, bool FQ>
 __global__ void __launch_bounds__(256)
-    attention_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
-                     const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
+    attention_kernel(const uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
+                     uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
                      size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity, size_t chunk,
-                     float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+                     float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales,
+                     const attn_fused_qk fq) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned CL = cluster.num_blocks(), rank = cluster.block_rank();
@@ -188,14 +208,46 @@ __global__ void __launch_bounds__(256)
 
   // stage q, K (group 0) and V (group 1) with 16-byte async copies
   const size_t row16 = hd / 8;  // 16-byte pieces per row
-  for (size_t i = tid; i < group * row16; i += blockDim.x)
-    cp_async16(qs + i * 8, q16 + b * nq + kvh * group * hd + i * 8);
-  for (size_t i = tid; i < (size_t)n_t * row16; i += blockDim.x)
+  constexpr bool fused = FQ;
+  const bool owner = fused && n_t > 0 && t0 + n_t == T;  // this CTA holds the current time step
+  const int n_ld = owner ? n_t - 1 : n_t;                 // rows that already sit in the caches
+  if (!fused)
+    for (size_t i = tid; i < group * row16; i += blockDim.x)
+      cp_async16(qs + i * 8, q16 + b * nq + kvh * group * hd + i * 8);
+  for (size_t i = tid; i < (size_t)n_ld * row16; i += blockDim.x)
     cp_async16(kbuf + (i / row16) * kstride + (i % row16) * 16, kbase + (i / row16) * nk + (i % row16) * 8);
   cp_async_commit();
-  for (size_t i = tid; i < (size_t)n_t * row16; i += blockDim.x)
+  for (size_t i = tid; i < (size_t)n_ld * row16; i += blockDim.x)
     cp_async16(vbuf + i * 16, vbase + (i / row16) * nk + (i % row16) * 8);
   cp_async_commit();
+  if (fused) {
+    const float* proj = fq.qkv + b * (nq + 2 * nk);
+    const float* tab = fq.rope + (size_t)(T - 1) * hd;
+    for (size_t unit = warp; unit < group + 2; unit += nwarp) {
+      if (unit < group) {
+        norm_rope_head_f16(proj + (kvh * group + unit) * hd, fq.q_norm, fq.eps, tab, hd, lane, qs + unit * hd);
+      } else if (owner) {
+        const size_t tl = (size_t)n_t - 1;
+        const size_t cache_off = (size_t)tl * nk;  // relative to kbase / vbase
+        if (unit == group) {
+          uint16_t* krow = reinterpret_cast<uint16_t*>(kbuf + tl * kstride);
+          norm_rope_head_f16(proj + nq + kvh * hd, fq.k_norm, fq.eps, tab, hd, lane, krow);
+          __syncwarp();
+          uint16_t* kg = k_cache + ((b * n_layer + layer) * capacity + t0) * nk + kvh * hd + cache_off;
+          for (size_t i = lane; i < hd; i += 32) kg[i] = krow[i];
+        } else {
+          uint16_t* vrow = reinterpret_cast<uint16_t*>(vbuf) + tl * hd;
+          uint16_t* vg = v_cache + ((b * n_layer + layer) * capacity + t0) * nk + kvh * hd + cache_off;
+          const float* vsrc = proj + nq + nk + kvh * hd;
+          for (size_t i = lane; i < hd; i += 32) {
+            const uint16_t h = f32_to_f16_bits(vsrc[i]);
+            vrow[i] = h;
+            vg[i] = h;
+          }
+        }
+      }
+    }
+  }
   cp_async_wait<1>();
   __syncthreads();
 
@@ -435,18 +487,23 @@ size_t attention_smem_bytes(const decode_dims& d) {
   return b + 32;
 }
 
-int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
-                         const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
-                         float* scales) {
+int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, uint16_t* k_cache,
+                         uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                         float* scales, const float* qkv, const float* q_norm, const float* k_norm,
+                         const float* rope) {
   RMI_REQUIRE(d.hd % 8 == 0 && (d.n_head / d.n_head_kv) * d.hd % 32 == 0, RMI_ERR_UNSUPPORTED,
               "attention needs head_dim %% 8 == 0 and group*head_dim %% 32 == 0");
   const size_t smem = attention_smem_bytes(d);
   const unsigned cl = attention_cluster(d);
   const size_t chunk = (d.capacity + cl - 1) / cl;
-  void (*kern)(const uint16_t*, const uint16_t*, const uint16_t*, const int*, size_t, size_t, size_t, size_t, size_t,
-               size_t, size_t, float*, uint8_t*, float*) =
-      ctx->sem == RMI_SEM_AVX2 ? attention_kernel<RMI_SEM_AVX2>
-                               : (ctx->sem == RMI_SEM_NEON ? attention_kernel<RMI_SEM_NEON> : attention_kernel<RMI_SEM_SCALAR>);
+  void (*kern)(const uint16_t*, uint16_t*, uint16_t*, const int*, size_t, size_t, size_t, size_t, size_t,
+               size_t, size_t, float*, uint8_t*, float*, const attn_fused_qk) =
+      qkv ? (ctx->sem == RMI_SEM_AVX2 ? attention_kernel<RMI_SEM_AVX2, true>
+                                      : (ctx->sem == RMI_SEM_NEON ? attention_kernel<RMI_SEM_NEON, true>
+                                                                  : attention_kernel<RMI_SEM_SCALAR, true>))
+          : (ctx->sem == RMI_SEM_AVX2 ? attention_kernel<RMI_SEM_AVX2, false>
+                                      : (ctx->sem == RMI_SEM_NEON ? attention_kernel<RMI_SEM_NEON, false>
+                                                                  : attention_kernel<RMI_SEM_SCALAR, false>));
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     rmi_set_error("attention needs %zu B of shared memory", smem);
@@ -467,7 +524,8 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
   cfg.attrs = attr;
   cfg.numAttrs = ctx->pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, q16, k_cache, v_cache, d_step, d.n_head, d.n_head_kv, d.hd, layer,
-                                     d.n_layer, d.capacity, chunk, attn_out, q8, scales);
+                                     d.n_layer, d.capacity, chunk, attn_out, q8, scales,
+                                     attn_fused_qk{qkv, q_norm, k_norm, rope, d.eps});
   if (e != cudaSuccess) {
     rmi_set_error("attention launch failed: %s", cudaGetErrorString(e));
     return RMI_ERR_CUDA;

@@ -45,6 +45,7 @@ struct rmi_session {
   uint16_t *k_cache, *v_cache;
   float *x, *x2, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;  // x2: second residual buffer of the fused-norm path
   bool fused_norm;
+  bool fused_qk;  // q/k norm + rotation + cache write inside the attention kernel
   uint16_t* q16;
   uint8_t* q8;
   float* xs;
@@ -340,8 +341,10 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
-  for (const auto& l : model->layers)
+  s->fused_qk = batch <= 4 && getenv("RMI_NO_FUSED_QK") == nullptr;  // measured: a loss at batch 32
+  for (const auto& l : model->layers) {
     s->fused_norm = s->fused_norm && q8_gemv_fused_norm_eligible(ctx, l.wqkv, batch) && q8_gemv_fused_norm_eligible(ctx, l.wgu, batch);
+  }
   cudaMemset(s->k_cache, 0, kv);
   cudaMemset(s->v_cache, 0, kv);
   // rope_neox (src/ops/rope.rs:21-37): theta_0 = pos, theta_{i+1} = theta_i * base^(-2/d) in f32,
@@ -387,9 +390,15 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
       RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
       RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
     }
-    RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
-                                   s->v_cache, l));
-    RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+    if (s->fused_qk) {
+      // q/k norm, rotation and the cache write happen inside the attention kernel
+      RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs, s->qkv,
+                               w.q_norm, w.k_norm, s->rope));
+    } else {
+      RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
+                                     s->v_cache, l));
+      RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+    }
     RMI_TRY(launch_q8_gemv(ctx, w.wo, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
     if (s->fused_norm) {
       RMI_TRY(launch_q8_gemv_fused_norm(ctx, w.wgu, xc, s->proj, w.ffn_norm, d.eps, xn, B, s->gu, 2 * d.n_ff));
@@ -502,7 +511,8 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
       passes++;
       rem %= p2;
     }
-  const uint64_t launches_per_body = 3 + d.n_layer * (s->fused_norm ? 7 : 5 + 4 * passes), launches_full = launches_per_body + passes + 2;
+  const uint64_t per_layer = 4 * passes + 1 + (s->fused_norm ? 0 : 2) + (s->fused_qk ? 0 : 1) + 1;
+  const uint64_t launches_per_body = 3 + d.n_layer * per_layer, launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;
   for (size_t st = 0; st < steps && ce == cudaSuccess; st++) {
