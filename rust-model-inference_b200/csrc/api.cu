@@ -497,6 +497,10 @@ int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* cw, bool gate_up_inte
 
 // ---------------------------------------------------------------- Q8_0 entry points
 
+// Up to this many activation rows the GEMM runs with swapped operands (32 activation rows per tile column
+// block instead of a 128-row tile that is mostly padding).
+constexpr size_t SWAP_AB_MAX_M = 96;
+
 static bool use_tensor_cores(const rmi_ctx* ctx, size_t m) {
   // The tcgen05 path produces whole-block sums, which is how the NEON and scalar variants
   // accumulate.  The AVX2 variant accumulates eight partial sums per block, so it stays on
@@ -504,6 +508,13 @@ static bool use_tensor_cores(const rmi_ctx* ctx, size_t m) {
   static const bool disabled = getenv("RMI_DISABLE_TC") != nullptr;
   static const size_t min_m = getenv("RMI_TC_MIN_M") ? (size_t)atoi(getenv("RMI_TC_MIN_M")) : 32;
   return m > min_m && ctx->sem != RMI_SEM_AVX2 && !disabled;
+}
+
+// Plain matmuls (no fused epilogue) also take the tensor cores for 8 < m <= 32, with swapped operands.
+static bool matmul_on_tensor_cores(const rmi_ctx* ctx, size_t m) {
+  static const bool disabled = getenv("RMI_DISABLE_TC") != nullptr || getenv("RMI_DISABLE_SWAP_AB") != nullptr;
+  if (use_tensor_cores(ctx, m)) return true;
+  return m > 8 && m <= SWAP_AB_MAX_M && ctx->sem != RMI_SEM_AVX2 && !disabled;
 }
 
 extern "C" int32_t rmi_quantize_q8_0_dev(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8,
@@ -580,7 +591,7 @@ static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float
                                   size_t out_stride = 0) {
   const size_t blocks = w->n_in / 32;
   if (out_stride == 0) out_stride = w->n_rows;
-  if (use_tensor_cores(ctx, m)) {
+  if (matmul_on_tensor_cores(ctx, m)) {
     RMI_TRY(ensure_umma_layout(ctx, w));
     const size_t m_tiles = (m + 127) / 128, n_slabs = (w->n_in + 127) / 128;
     uint8_t* a_img;
@@ -602,6 +613,7 @@ static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float
     g.epilogue = GEMM_EPI_F32;
     g.out = dout;
     g.out_stride = out_stride;
+    g.swap_ab = m <= SWAP_AB_MAX_M;
     return launch_gemm_tc(ctx, g);
   }
   uint8_t* dq;
@@ -655,7 +667,7 @@ extern "C" int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const floa
   RMI_CUDA_CHECK(cudaMemcpyAsync(dx, x, m * w->n_in * 4, cudaMemcpyHostToDevice, ctx->stream));
   RMI_TRY(matmul_q8_0_device(ctx, w, dx, m, dout));
   RMI_CUDA_CHECK(cudaMemcpyAsync(output, dout, m * w->n_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
-  if (use_tensor_cores(ctx, m)) return rmi_check_dev_status(ctx, "rmi_matmul_q8_0");
+  if (matmul_on_tensor_cores(ctx, m)) return rmi_check_dev_status(ctx, "rmi_matmul_q8_0");
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   return RMI_OK;
 }

@@ -56,6 +56,7 @@ struct gemm_params {
   size_t act_slabs, act_blocks;
   rmi_dev_status* status;
   out_fanout fo;  // extra copies of the f32 output (GEMM_EPI_F32)
+  int transpose;  // GEMM_EPI_F32: store element (row, n) at out[n * out_stride + row]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -478,7 +479,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     }
 
     if (EPI == GEMM_EPI_F32 && ok) {
-      if (row < p.m) {
+      if (row < p.m && p.transpose) {
+        // operands swapped: `row` is a weight row, the tile's columns are activation rows; consecutive
+        // lanes store consecutive addresses
+        const size_t n0 = wrow_tile + col0;
+        float v[CPW];
+#pragma unroll
+        for (int c = 0; c < CPW / 2; c++) unpack2(acc[c], &v[2 * c], &v[2 * c + 1]);
+#pragma unroll
+        for (int c = 0; c < CPW; c++)
+          if (n0 + c < p.col_end) store_fanout(p.out + (n0 + c) * p.out_stride + row, v[c], p.fo);
+      } else if (row < p.m) {
         const size_t n0 = wrow_tile + col0;
         float* o = p.out + row * p.out_stride + n0;
         float v[CPW];
@@ -581,6 +592,34 @@ int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
               "tcgen05 weight layout was not built");
   RMI_REQUIRE(ctx->sem != RMI_SEM_AVX2 || a.epilogue == GEMM_EPI_BLOCK_SUMS, RMI_ERR_UNSUPPORTED,
               "the tcgen05 GEMM accumulates whole-block sums (NEON or SCALAR semantics)");
+  if (a.swap_ab) {
+    // small batches: the weight is the 128-row operand, the activation rows are the tile columns, so no
+    // tensor-core or epilogue work is spent on padding rows; the result is stored transposed
+    RMI_REQUIRE(a.epilogue == GEMM_EPI_F32 && a.col_begin == 0 && a.col_end == w->n_rows, RMI_ERR_UNSUPPORTED,
+                "swapped-operand GEMM: f32 output of all weight rows only");
+    RMI_REQUIRE(w->d_umma_q != nullptr, RMI_ERR_BAD_HANDLE, "tcgen05 weight layout was not built");
+    RMI_REQUIRE(ctx->sem != RMI_SEM_AVX2, RMI_ERR_UNSUPPORTED,
+                "the tcgen05 GEMM accumulates whole-block sums (NEON or SCALAR semantics)");
+    if (a.m == 0 || w->n_rows == 0) return RMI_OK;
+    gemm_params p = {};
+    p.a_img = w->d_umma_q;
+    p.a_scales = w->d_umma_s;
+    p.b_img = a.a_img;
+    p.b_scales = a.a_scales;
+    p.m = w->n_rows;
+    p.n_rows_w = a.m;
+    p.blocks = w->n_in / 32;
+    p.n_slabs = (w->n_in + 127) / 128;
+    p.col_begin = 0;
+    p.col_end = a.m;
+    p.out = a.out;
+    p.out_stride = a.out_stride;
+    p.status = ctx->d_status;
+    p.fo = ctx->fanout;
+    p.transpose = 1;
+    p.n_tiles_n = (a.m + 31) / 32;
+    return launch_nt<32, GEMM_EPI_F32>(ctx, p, (w->n_rows + 127) / 128);
+  }
   gemm_params p = {};
   p.a_img = a.a_img;
   p.a_scales = a.a_scales;

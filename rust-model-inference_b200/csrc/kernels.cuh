@@ -35,6 +35,7 @@ struct gemm_tc_args {
   float* act_scales;
   float* act_f32;
   int32_t* sums;         // BLOCK_SUMS: [m][n_rows][blocks]
+  bool swap_ab;          // F32, all rows: weight as the 128-row operand, activation rows as tile columns
 };
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
 int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w, bool gate_up_interleaved = false);

@@ -65,6 +65,23 @@ def test_gemm_avx2_semantics_stays_bit_exact_and_tc_is_within_tolerance(rmi, ctx
     w.free()
 
 
+@pytest.mark.parametrize("sem", [orc.SEM_NEON, orc.SEM_SCALAR])
+@pytest.mark.parametrize("m,n,k", [(9, 128, 128), (16, 1000, 96), (32, 384, 1024), (33, 130, 160), (40, 256, 3072),
+                                   (96, 200, 64), (16, 4096, 1024)])
+def test_small_batch_gemm_with_swapped_operands_is_bit_exact(rmi, ctx, sem, m, n, k):
+    """8 < m <= 96: the weight is the 128-row MMA operand and the activation rows are tile columns
+    (transposed store); ragged n (rows of the last weight tile) and ragged m (columns of the last block)."""
+    ctx.set_semantics(sem)
+    wb = rmi.synth.q8_0_weight(n, k, seed=n + 7 * k)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q8_0, k, n)
+    x = rmi.synth.normal((m, k), seed=m + 11)
+    got = rmi.matmul_q8_0(w, x)
+    ref = orc.q8_forward_batched(wb, x, k, n, sem, threads=8)
+    assert np.array_equal(bits(got), bits(ref))
+    assert np.array_equal(bits(rmi.matmul_q8_0(w, x)), bits(got))   # run twice: same bits
+    w.free()
+
+
 @pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
 @pytest.mark.parametrize("m", [1, 5, 32])
 def test_ffn_decode_shapes_bit_exact(rmi, ctx, sem, m):
