@@ -232,14 +232,14 @@ struct __align__(128) smem_layout_hdr {
   int abort_flag;
 };
 
-// Per-stage shared memory: A image (16 KiB) | B image (NT*128 B) | weight scales [4][NT] f32 |
+// Per-stage shared memory: A image (16 KiB) | B image (NT*128 B) | weight scales [4][128] f32 |
 // activation scales [4][128] f32.
 template <int NT>
 struct stage_layout {
   static constexpr int A = 0;
   static constexpr int B = SLAB_BYTES_A;
   static constexpr int WS = B + NT * 128;
-  static constexpr int XS = WS + 4 * NT * 4;
+  static constexpr int XS = WS + 4 * 128 * 4;  // the weight tile's scales of all 128 rows: one contiguous copy
   static constexpr int BYTES = XS + 4 * 128 * 4;
 };
 
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
       const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
       const uint8_t* bsrc0 = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
-      const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 + (wrow_tile % 128) : nullptr;
+      const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 : nullptr;
       const float* xs0 = kScales ? p.a_scales + (size_t)tile_m * p.blocks * 128 : nullptr;
       const uint8_t* asrc0 = p.a_img + (size_t)tile_m * p.n_slabs * SLAB_BYTES_A;
       for (int s = 0; s < n_slabs; s++, gs++) {
@@ -355,13 +355,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         }
         uint8_t* sb = stages + st * SL::BYTES;
         const uint32_t kb_n = (uint32_t)(blocks - s * 4 < 4 ? blocks - s * 4 : 4);
-        const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (NT * 4 + 512) : 0);
+        const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (512 + 512) : 0);
         mbar_expect_tx(&hdr->full[st], tx);
         bulk_g2s(sb + SL::A, asrc0 + (size_t)s * SLAB_BYTES_A, SLAB_BYTES_A, &hdr->full[st]);
         bulk_g2s(sb + SL::B, bsrc0 + (size_t)s * SLAB_BYTES_A, NT * 128, &hdr->full[st]);
         if (kScales) {
-          for (uint32_t kb = 0; kb < kb_n; kb++)
-            bulk_g2s(sb + SL::WS + kb * NT * 4, ws0 + (size_t)(s * 4 + kb) * 128, NT * 4, &hdr->full[st]);
+          bulk_g2s(sb + SL::WS, ws0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
           bulk_g2s(sb + SL::XS, xs0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
         }
       }
@@ -403,6 +402,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
     const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
     const size_t row = (size_t)tile_m * 128 + r_tile;
+    const int ws_col = (int)(wrow_tile % 128) + col0;  // this thread's first column inside the 128-row weight tile
     uint64_t acc[CPW / 2];
 #pragma unroll
     for (int c = 0; c < CPW / 2; c++) acc[c] = 0ull;
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
               }
             } else {
               const float xs = reinterpret_cast<const float*>(sb + SL::XS)[kb * 128 + r_tile];
-              const uint64_t* wsp = reinterpret_cast<const uint64_t*>(sb + SL::WS + (kb * NT + col0) * 4);
+              const uint64_t* wsp = reinterpret_cast<const uint64_t*>(sb + SL::WS + (kb * 128 + ws_col) * 4);
               const uint64_t xs2 = pack2(xs, xs);
 #pragma unroll
               for (int c = 0; c < CPW / 2; c++) {
