@@ -298,7 +298,13 @@ template <int NT, int EPI, int SEM>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p) {
   using SL = stage_layout<NT>;
   constexpr int CPW = NT / 4;  // columns per epilogue warp
-  constexpr uint32_t TMEM_COLS = 8 * NT;
+  // tensor-memory slab buffers (four K blocks each): as many as fit in 512 columns, so that more MMA groups
+  // are in flight while a finished one waits for the epilogue
+#ifndef RMI_TMEM_BUFS32
+#define RMI_TMEM_BUFS32 4
+#endif
+  constexpr int NB = NT == 32 ? RMI_TMEM_BUFS32 : 2;
+  constexpr uint32_t TMEM_COLS = NB * 4 * NT;
   static_assert(TMEM_COLS <= 512 && CPW >= 8, "tile width must be 32 or 64");
   extern __shared__ __align__(128) uint8_t smem_raw[];
   smem_layout_hdr* hdr = reinterpret_cast<smem_layout_hdr*>(smem_raw);
@@ -318,7 +324,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       mbar_init(&hdr->full[i], 1);
       mbar_init(&hdr->empty[i], 1 + EPI_WARPS);
     }
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < NB; i++) {
       mbar_init(&hdr->tfull[i], 1);
       mbar_init(&hdr->tempty[i], EPI_WARPS);
     }
@@ -373,9 +379,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
       int gs = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x)
       for (int s = 0; s < n_slabs; s++, gs++) {
-        const int st = gs % STAGES, tb = gs & 1;
+        const int st = gs % STAGES, tb = gs % NB;
         if (!mbar_wait_a(full_a + 8 * st, (gs / STAGES) & 1, abort_flag, p.status, 2, s) ||
-            (gs >= 2 && !mbar_wait_a(tempty_a + 8 * tb, ((gs >> 1) & 1) ^ 1, abort_flag, p.status, 3, s))) {
+            (gs >= NB && !mbar_wait_a(tempty_a + 8 * tb, ((gs / NB) & 1) ^ 1, abort_flag, p.status, 3, s))) {
           tile = n_tiles;
           break;
         }
@@ -408,7 +414,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
     for (int c = 0; c < CPW / 2; c++) acc[c] = 0ull;
 
     for (int s = 0; s < n_slabs; s++, gs++) {
-      const int st = gs % STAGES, tb = gs & 1;
+      const int st = gs % STAGES, tb = gs % NB;
       const uint8_t* sb = stages + st * SL::BYTES;
       const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
       // tfull[tb] completes after the MMAs of slab s, which were issued after full[st] completed;
@@ -417,7 +423,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         ok = false;
         break;
       }
-      if (!mbar_wait_a(tfull_a + 8 * tb, (gs >> 1) & 1, abort_flag, p.status, 4, s)) {
+      if (!mbar_wait_a(tfull_a + 8 * tb, (gs / NB) & 1, abort_flag, p.status, 4, s)) {
         ok = false;
         break;
       }
