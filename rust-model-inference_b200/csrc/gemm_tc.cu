@@ -148,6 +148,28 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
       : "memory");
 }
 
+// The four MMAs of one K slab (blocks 0..3: operand start addresses 256 B apart, accumulators NT columns apart).
+template <int NT>
+__device__ __forceinline__ void umma_i8_x4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b32 z, d1, d2, d3;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "mov.b32 z, 0;\n\t"
+      "setp.ne.b32 p, z, 0;\n\t"
+      "add.u32 d1, %0, %4;\n\tadd.u32 d2, d1, %4;\n\tadd.u32 d3, d2, %4;\n\t"
+      "add.u64 a1, %1, 16;\n\tadd.u64 a2, %1, 32;\n\tadd.u64 a3, %1, 48;\n\t"
+      "add.u64 b1, %2, 16;\n\tadd.u64 b2, %2, 32;\n\tadd.u64 b3, %2, 48;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {z, z, z, z}, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [d1], a1, b1, %3, {z, z, z, z}, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [d2], a2, b2, %3, {z, z, z, z}, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [d3], a3, b3, %3, {z, z, z, z}, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)NT)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_a(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -344,38 +366,50 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    // Lanes 0..3 each own one of the stage's four bulk copies (A image, B image, weight scales, activation
+    // scales), so a slab costs one short instruction stream for the whole warp: the roles that run on a single
+    // warp set the pace of the pipeline and compete with sixteen epilogue warps for issue slots.
+    if (lane < (kScales ? 4 : 2)) {
       int gs = 0;  // slabs issued so far (all tiles)
+      const uint32_t dst_off = lane == 0 ? SL::A : (lane == 1 ? SL::B : (lane == 2 ? SL::WS : SL::XS));
+      const uint32_t full_bytes = lane == 0 ? SLAB_BYTES_A : (lane == 1 ? NT * 128 : 4 * 512);
+      const size_t stride = lane < 2 ? (size_t)SLAB_BYTES_A : (size_t)4 * 512;  // bytes from one slab's source to the next
+      const int last_kb = blocks - (n_slabs - 1) * 4;                           // blocks in the last slab (1..4)
+      const uint32_t last_bytes = lane < 2 ? full_bytes : (uint32_t)last_kb * 512;
+      const uint32_t tx_full = SLAB_BYTES_A + NT * 128 + (kScales ? 4 * 1024 : 0);
+      const uint32_t tx_last = SLAB_BYTES_A + NT * 128 + (kScales ? (uint32_t)last_kb * 1024 : 0);
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
-      const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
-      const uint8_t* bsrc0 = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
-      const float* ws0 = kScales ? p.b_scales + (wrow_tile / 128) * p.blocks * 128 : nullptr;
-      const float* xs0 = kScales ? p.a_scales + (size_t)tile_m * p.blocks * 128 : nullptr;
-      const uint8_t* asrc0 = p.a_img + (size_t)tile_m * p.n_slabs * SLAB_BYTES_A;
-      for (int s = 0; s < n_slabs; s++, gs++) {
-        const int st = gs % STAGES;
-        if (gs >= STAGES && !mbar_wait_a(empty_a + 8 * st, ((gs / STAGES) & 1) ^ 1, abort_flag, p.status, 1, s)) {
-          tile = n_tiles;
-          break;
+        const int tile_n = tile % n_tiles_n, tile_m = tile / n_tiles_n;
+        const size_t wrow_tile = p.col_begin + (size_t)tile_n * NT;
+        const uint8_t* src;
+        if (lane == 0) src = p.a_img + (size_t)tile_m * p.n_slabs * SLAB_BYTES_A;
+        else if (lane == 1) src = p.b_img + (wrow_tile / 128) * p.n_slabs * SLAB_BYTES_A + ((wrow_tile % 128) / 8) * 1024;
+        else if (lane == 2) src = reinterpret_cast<const uint8_t*>(p.b_scales + (wrow_tile / 128) * p.blocks * 128);
+        else src = reinterpret_cast<const uint8_t*>(p.a_scales + (size_t)tile_m * p.blocks * 128);
+        for (int s = 0; s < n_slabs; s++, gs++, src += stride) {
+          const int st = gs % STAGES;
+          if (gs >= STAGES && !mbar_wait_a(empty_a + 8 * st, ((gs / STAGES) & 1) ^ 1, abort_flag, p.status, 1, s)) {
+            tile = n_tiles;
+            break;
+          }
+          const bool last = s + 1 == n_slabs;
+          const uint32_t bar = full_a + 8 * st;
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(last ? tx_last : tx_full)
+                         : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           stages_a + (uint32_t)(st * SL::BYTES) + dst_off),
+                       "l"(src), "r"(last ? last_bytes : full_bytes), "r"(bar)
+                       : "memory");
         }
-        uint8_t* sb = stages + st * SL::BYTES;
-        const uint32_t kb_n = (uint32_t)(blocks - s * 4 < 4 ? blocks - s * 4 : 4);
-        const uint32_t tx = SLAB_BYTES_A + NT * 128 + (kScales ? kb_n * (512 + 512) : 0);
-        mbar_expect_tx(&hdr->full[st], tx);
-        bulk_g2s(sb + SL::A, asrc0 + (size_t)s * SLAB_BYTES_A, SLAB_BYTES_A, &hdr->full[st]);
-        bulk_g2s(sb + SL::B, bsrc0 + (size_t)s * SLAB_BYTES_A, NT * 128, &hdr->full[st]);
-        if (kScales) {
-          bulk_g2s(sb + SL::WS, ws0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
-          bulk_g2s(sb + SL::XS, xs0 + (size_t)s * 4 * 128, kb_n * 512, &hdr->full[st]);
-        }
-      }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8<NT>();
+      // descriptors differ from stage to stage and block to block only in the 14-bit start address field
+      const uint64_t adesc0 = umma_desc(stages_a + SL::A), bdesc0 = umma_desc(stages_a + SL::B);
       int gs = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x)
       for (int s = 0; s < n_slabs; s++, gs++) {
@@ -386,13 +420,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
           break;
         }
         tc_fence_after();
-        const uint32_t a0 = stages_a + st * SL::BYTES + SL::A, b0 = stages_a + st * SL::BYTES + SL::B;
-        const int kb_n = blocks - s * 4 < 4 ? blocks - s * 4 : 4;
-        for (int kb = 0; kb < kb_n; kb++)
-          umma_i8(tmem_base + (uint32_t)((tb * 4 + kb) * NT), umma_desc(a0 + (uint32_t)kb * 256u),
-                  umma_desc(b0 + (uint32_t)kb * 256u), idesc);
-        umma_commit(&hdr->tfull[tb]);  // the slab's accumulators are complete
-        umma_commit(&hdr->empty[st]);  // A/B of this stage have been read
+        const uint64_t so = (uint64_t)((st * SL::BYTES) >> 4);
+        const uint32_t d0 = tmem_base + (uint32_t)(tb * 4 * NT);
+        if (s + 1 < n_slabs || (blocks & 3) == 0) {
+          umma_i8_x4<NT>(d0, adesc0 + so, bdesc0 + so, idesc);
+        } else {
+          const int kb_n = blocks - s * 4;
+          for (int kb = 0; kb < kb_n; kb++)
+            umma_i8(d0 + (uint32_t)(kb * NT), adesc0 + so + (uint64_t)(kb * 16), bdesc0 + so + (uint64_t)(kb * 16), idesc);
+        }
+        umma_commit_a(tfull_a + 8 * tb);  // the slab's accumulators are complete
+        umma_commit_a(empty_a + 8 * st);  // A/B of this stage have been read
       }
     }
   } else {
