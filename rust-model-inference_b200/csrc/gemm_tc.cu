@@ -268,7 +268,9 @@ struct stage_layout {
 // Out-of-line slow path of a wait: keeps polling with the time limit, records the failure.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
                                             rmi_dev_status* status, int site, int detail) {
-  const uint64_t t0 = global_ns();
+  // The common case is a phase that completes during the first suspended tries: the global timer (a slow
+  // read) and the abort flag are only consulted after every eighth failed try.
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
     uint32_t ok;
     asm volatile(
@@ -279,8 +281,12 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t parity, 
         : "r"(bar_addr), "r"(parity), "r"(20000u)
         : "memory");
     if (ok) return true;
-    if (*abort_flag) return false;
-    if (global_ns() - t0 > WAIT_NS) break;
+    if ((i & 7) == 7) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_NS) break;
+    }
   }
   *abort_flag = 1;
   if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
