@@ -275,6 +275,28 @@ def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16
                           "results": results}), flush=True)
 
 
+def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
+    """The HBM-bound decode GEMVs on their own (configs[0] shape, the logits shape, the config-5 M=1 shape):
+    one JSON line, `roofline` for the logits GEMV."""
+    ctx.set_stream(stream.cuda_stream)
+    iters = max(3, min(args.steps, 10))
+    res = {}
+    for name, (n, k, copies) in {"c1_3072x1024": (3072, 1024, 160), "logits_151936x1024": (151936, 1024, 4),
+                                 "c5_m1_32768x8192": (32768, 8192, 3)}.items():
+        for sem_name, sem in (("avx2", pkg.SEM_AVX2), ("neon", pkg.SEM_NEON)):
+            r = gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem)
+            r["frac_of_hbm_peak"] = r["gbs"] / hbm_peak
+            res[f"{name}_{sem_name}"] = r
+    top = res["logits_151936x1024_avx2"]
+    print(json.dumps({"metric": "Q8_0 decode GEMV achieved HBM bandwidth (logits shape 151936x1024, M=1)",
+                      "value": top["gbs"], "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8",
+                      "data": "synthetic", "config": {"workload": "decode GEMVs, pre-quantized x, distinct weight copies > L2"},
+                      "roofline": {"bound": "hbm", "kernel": "q8_gemv_kernel<AVX2,16,1>", "achieved": top["gbs"],
+                                   "peak": hbm_peak, "unit": "GB/s", "frac": top["gbs"] / hbm_peak,
+                                   "peak_source": f"copy bandwidth, of {peak_kind}", "traffic": None},
+                      "results": res}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,7 +306,7 @@ def main():
     ap.add_argument("--threads", type=int, default=0, help="CPU threads of the reference arm / cpu baseline (0 = all)")
     ap.add_argument("--semantics", default="neon", choices=["neon", "scalar", "avx2"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary figures (GEMV, decode)")
-    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded"],
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv"],
                     help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -310,6 +332,12 @@ def main():
     ctx.set_stream(stream.cuda_stream)
     hbm_peak, bf16_peak, bf16_sus, peak_kind = measured_peaks()
     sm_count, l2_bytes, _ = ctx.device_info()
+    if args.workload == "gemv":
+        if rank == 0:
+            run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "sharded":
         run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak)
         if world > 1:

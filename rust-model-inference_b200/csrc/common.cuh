@@ -176,7 +176,11 @@ static inline cudaError_t rmi_launch(const rmi_ctx* ctx, void (*kern)(KArgs...),
 // One f32 result to the primary output and to every extra copy.
 __device__ __forceinline__ void store_fanout(float* o, float v, const out_fanout& fo) {
   *o = v;
-  for (int i = 0; i < fo.n; i++) *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + fo.delta[i]) = v;
+  if (fo.n == 0) return;
+  // static indices: a dynamically indexed by-value struct would be copied to local memory in every thread
+#pragma unroll
+  for (int i = 0; i < RMI_MAX_FANOUT - 1; i++)
+    if (i < fo.n) *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + fo.delta[i]) = v;
 }
 
 // IEEE f16 -> f32 (exact)

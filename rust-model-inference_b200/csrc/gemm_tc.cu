@@ -545,7 +545,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
         float v[CPW];
 #pragma unroll
         for (int c = 0; c < CPW / 2; c++) unpack2(acc[c], &v[2 * c], &v[2 * c + 1]);
-        for (int copy = 0; copy <= p.fo.n; copy++) {
+#pragma unroll
+        for (int copy = 0; copy < RMI_MAX_FANOUT; copy++) {
+          if (copy > p.fo.n) break;
           if (copy > 0) o = reinterpret_cast<float*>(reinterpret_cast<char*>(p.out + row * p.out_stride + n0) + p.fo.delta[copy - 1]);
           if (n0 + CPW <= p.col_end && ((p.out_stride | n0) & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
