@@ -279,7 +279,7 @@ def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
     """The HBM-bound decode GEMVs on their own (configs[0] shape, the logits shape, the config-5 M=1 shape):
     one JSON line, `roofline` for the logits GEMV."""
     ctx.set_stream(stream.cuda_stream)
-    iters = max(3, min(args.steps, 10))
+    iters = max(10, min(args.steps, 50))
     res = {}
     for name, (n, k, copies) in {"c1_3072x1024": (3072, 1024, 160), "logits_151936x1024": (151936, 1024, 4),
                                  "c5_m1_32768x8192": (32768, 8192, 3)}.items():

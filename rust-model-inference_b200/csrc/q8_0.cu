@@ -198,8 +198,11 @@ __device__ __forceinline__ void gemv_consume_batch(const gemv_batch<LB>& t, size
 // 16-row tile of 8..16 load batches, so the plain "load a batch, consume it" loop with eight warps per CTA
 // (one activation staging per 128 rows) streams better than the double-buffered kernel below
 // (measured 87 % against 75 % of the copy bandwidth at 151936 x 1024).
+#ifndef RMI_GEMV_SHORT_MINB
+#define RMI_GEMV_SHORT_MINB 1
+#endif
 template <int SEM, int LB, int MP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, RMI_GEMV_SHORT_MINB)
     q8_gemv_short_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
                    const float* __restrict__ xs, float* __restrict__ out, size_t out_stride,
                    size_t row_begin, size_t row_end, size_t first_tile, const out_fanout fo) {
