@@ -291,9 +291,11 @@ def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
     print(json.dumps({"metric": "Q8_0 decode GEMV achieved HBM bandwidth (logits shape 151936x1024, M=1)",
                       "value": top["gbs"], "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8",
                       "data": "synthetic", "config": {"workload": "decode GEMVs, pre-quantized x, distinct weight copies > L2"},
-                      "roofline": {"bound": "hbm", "kernel": "q8_gemv_kernel<AVX2,16,1>", "achieved": top["gbs"],
+                      "roofline": {"bound": "hbm", "kernel": "q8_gemv_short_kernel<AVX2,16,1>", "achieved": top["gbs"],
                                    "peak": hbm_peak, "unit": "GB/s", "frac": top["gbs"] / hbm_peak,
-                                   "peak_source": f"copy bandwidth, of {peak_kind}", "traffic": None},
+                                   "peak_source": f"copy bandwidth, of {peak_kind}",
+                                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch (profiles/q8_gemv_short_logits.md)
+                                   "traffic": 169306000},
                       "results": res}), flush=True)
 
 
