@@ -187,6 +187,46 @@ def gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem):
             "distinct_weight_copies": copies, "launch": mode}
 
 
+def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10):
+    """BASELINE config 3: W [4096, 4096] Q4_K, M in {1, 8, 256}; both reference paths (dequantize-and-matmul,
+    Q4_K x Q8_K).  16 distinct weight copies (151 MB > L2) rotate inside one CUDA graph."""
+    n = k = 4096
+    ctx.set_semantics(pkg.SEM_AVX2)
+    ctx.set_stream(stream.cuda_stream)
+    wb = pkg.synth.q4_k_weight(n, k, seed=0)
+    ws = [pkg.QuantizedTensor.from_bytes(wb, pkg.GGML_Q4_K, k, n) for _ in range(16)]
+    res = {}
+    for m in (1, 8, 256):
+        x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
+        out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        for name, fn in (("dequant", pkg.matmul_q4_k_dequant_dev), ("q8k", pkg.matmul_q4_k_q8k_dev)):
+            def burst():
+                for w in ws:
+                    fn(w, x.data_ptr(), m, out.data_ptr())
+            for _ in range(2):
+                burst()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                burst()
+            graph.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                e0.record(stream)
+                for _ in range(iters):
+                    graph.replay()
+                e1.record(stream)
+            stream.synchronize()
+            per = e0.elapsed_time(e1) / 1e3 / (iters * len(ws))
+            algo = n * (k // 256) * 144 + m * k * 4 + m * n * 4
+            res[f"{name}_m{m}"] = {"us": per * 1e6, "gbs": algo / per / 1e9, "frac_of_hbm_peak": algo / per / 1e9 / hbm_peak,
+                                   "tflops": 2.0 * m * n * k / per / 1e12, "algorithmic_bytes": algo}
+    for w in ws:
+        w.free()
+    return res
+
+
 def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem):
     ctx.set_semantics(sem)
     model = pkg.Qwen3Model.from_file(path)
@@ -484,6 +524,10 @@ def main():
                 also["hbm_peak_gbs"] = hbm_peak
             except Exception as ex:   # secondary figures never break the headline line
                 also["gemv_error"] = repr(ex)
+            try:
+                also["q4_k_4096x4096"] = q4k_bench(pkg, ctx, torch, stream, hbm_peak)
+            except Exception as ex:
+                also["q4k_error"] = repr(ex)
             try:
                 ctx.set_stream(None)
                 cfg = dict(pkg.synth.QWEN3_0_6B)

@@ -187,6 +187,10 @@ int32_t rmi_matmul_q4_k_q8k(rmi_ctx* ctx, const rmi_weight* w, const float* x, s
                             float* output, size_t row_begin, size_t row_end);
 /* QuantizedLinear::forward_dequant / Layer::forward (src/core/model.rs:65-93): dequantized
  * f32 weights times the f32 input.  No 64 MiB scratch: weights are decoded in registers. */
+/* Device-pointer variant of rmi_matmul_q4_k_q8k over all rows: x [m, n_in] f32 and output [m, n_rows] f32 on the
+ * device; quantizes to Q8_K and multiplies, stream-ordered, no synchronisation. */
+int32_t rmi_matmul_q4_k_q8k_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                                float* output);
 int32_t rmi_matmul_q4_k_dequant(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
                                 float* output);
 int32_t rmi_matmul_q4_k_dequant_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,

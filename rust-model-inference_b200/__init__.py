@@ -473,6 +473,10 @@ def quantize_q8_0_dev(ctx: Context, x_ptr: int, m: int, n: int, q8_ptr: int, sca
                                        C.c_void_p(scales_ptr)))
 
 
+def matmul_q4_k_q8k_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    _check(lib().rmi_matmul_q4_k_q8k_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m), C.c_void_p(out_ptr)))
+
+
 def matmul_q4_k_dequant_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
     _check(lib().rmi_matmul_q4_k_dequant_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m),
                                              C.c_void_p(out_ptr)))

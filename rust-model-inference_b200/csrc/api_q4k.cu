@@ -55,6 +55,24 @@ extern "C" int32_t rmi_matmul_q4_k_q8k(rmi_ctx* ctx, const rmi_weight* w, const 
   return RMI_OK;
 }
 
+extern "C" int32_t rmi_matmul_q4_k_q8k_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q4_K));
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  RMI_REQUIRE(x && output, RMI_ERR_BAD_HANDLE, "rmi_matmul_q4_k_q8k_dev: null buffer");
+  RMI_REQUIRE(ctx->sem != RMI_SEM_NEON, RMI_ERR_UNSUPPORTED, "the reference has no NEON Q4_K x Q8_K kernel; use AVX2 or SCALAR");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n = w->n_in, nb = m * n / 256;
+  float* dd;
+  int8_t* dq;
+  int16_t* db;
+  RMI_TRY(rmi_scratch(ctx, 0, m * n, (void**)&dq));
+  RMI_TRY(rmi_scratch(ctx, 1, nb * 4, (void**)&dd));
+  RMI_TRY(rmi_scratch(ctx, 4, nb * 32, (void**)&db));
+  RMI_TRY(launch_q8k_quantize(ctx, x, m, n, dd, dq, db));
+  return launch_q4k_q8k_matmul(ctx, w, dd, dq, db, m, output, 0, w->n_rows);
+}
+
 extern "C" int32_t rmi_matmul_q4_k_dequant_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
                                                float* output) {
   RMI_TRY(rmi_check_ctx(ctx));

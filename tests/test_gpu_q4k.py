@@ -121,3 +121,43 @@ def test_config3_q4_k_dequant_matmul(rmi, ctx, m):
         assert rel_err(out[t], ref64) < 1e-4
         if ref_seq is not None:
             assert rel_err(out[t], ref_seq) < 1e-4   # the reference's sequential f32 order
+
+
+@pytest.mark.parametrize("m,n,k", [(37, 200, 512), (64, 128, 256), (130, 260, 1024)])
+def test_q4_k_dequant_gemm_ragged_tiles(rmi, ctx, m, n, k):
+    """m >= 32 runs the tiled f32 GEMM with on-the-fly decode: ragged weight rows and activation rows,
+    every output against the f64 product of the dequantized weight (1e-4 relative)."""
+    wb = rmi.synth.q4_k_weight(n, k, seed=5)
+    lin = rmi.QuantizedLinear.from_weight_slice(wb, None, k, n, "ragged")
+    x = rmi.synth.normal((m, k), seed=6)
+    out = np.full((m, n), np.nan, np.float32)
+    lin.forward_dequant(x, out)
+    deq = orc.dequantize_q4_k_weight(wb, n, k)
+    ref = (x.astype(np.float64) @ deq.astype(np.float64).T).astype(np.float32)
+    assert np.isfinite(out).all()
+    assert rel_err(out, ref) < 1e-4
+    # the small-batch kernel gives the same values within the same tolerance
+    out8 = np.zeros((8, n), np.float32)
+    lin.forward_dequant(x[:8], out8)
+    assert rel_err(out8, ref[:8]) < 1e-4
+
+
+@pytest.mark.parametrize("sem", ["SEM_AVX2", "SEM_SCALAR"])
+@pytest.mark.parametrize("m", [1, 4, 7, 9])
+def test_q4_k_q8k_device_entry_point_matches_host_entry_point(rmi, ctx, sem, m):
+    """rmi_matmul_q4_k_q8k_dev (groups of four activation rows per pass + remainder) == rmi_matmul_q4_k_q8k bits."""
+    torch = pytest.importorskip("torch")
+    ctx.set_semantics(getattr(rmi, sem))
+    n, k = 96, 512
+    wb = rmi.synth.q4_k_weight(n, k, seed=9)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q4_K, k, n)
+    x = rmi.synth.normal((m, k), seed=10)
+    xd = torch.from_numpy(x).cuda()
+    od = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    rmi.matmul_q4_k_q8k_dev(w, xd.data_ptr(), m, od.data_ptr())
+    ctx.sync()
+    ref = np.stack([orc.q4k_forward_prepared(wb, x[t], k, n, sem=getattr(orc, sem)) for t in range(m)])
+    assert np.array_equal(bits(od.cpu().numpy()), bits(ref))
+    w.free()
+    ctx.set_semantics(rmi.SEM_AVX2)
