@@ -517,6 +517,28 @@ def dequantize_q4_k_weight(weight: QuantizedTensor) -> np.ndarray:
     return out
 
 
+class Qwen35Ffn:
+    """The multi-token FFN of the reference's Qwen3.5 forward (`forward_ffn_parallel`,
+    src/models/qwen35.rs:762-782) for Q8_0 weights: per token gate and up matmuls on the Q8_0-quantized
+    hidden row, `silu_mul_inplace` over all tokens, per token down matmul on the re-quantized product.
+    Here one fused call for all tokens: v-stacked gate|up weight, SiLU*up and the re-quantization in the
+    GEMM epilogue (tcgen05 for more than 32 tokens under NEON/SCALAR semantics)."""
+
+    def __init__(self, ffn_gate: "QuantizedTensor", ffn_up: "QuantizedTensor", ffn_down: "QuantizedTensor"):
+        if ffn_gate.ggml_type != GGML_Q8_0 or ffn_up.ggml_type != GGML_Q8_0 or ffn_down.ggml_type != GGML_Q8_0:
+            raise RmiError(5, "Qwen35Ffn: Q8_0 weights only")
+        self.n_embd, self.n_ff = ffn_gate.n_in, ffn_gate.n_out
+        self.gate_up = ffn_gate.fuse_vstack(ffn_up)
+        self.down = ffn_down
+
+    def forward_ffn_parallel(self, hidden, n_tokens: int) -> np.ndarray:
+        hidden = np.ascontiguousarray(hidden, np.float32).reshape(n_tokens, self.n_embd)
+        return ffn_swiglu_q8_0(self.gate_up, self.down, hidden)
+
+    def free(self):
+        self.gate_up.free()
+
+
 class QuantizedLinear:
     """QuantizedLinear<'a> (src/core/model.rs:12-104): Q4_K dequantize-and-matmul Layer."""
 

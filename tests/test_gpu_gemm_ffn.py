@@ -162,3 +162,25 @@ def test_silu_mul_matches_oracle_bits(rmi, ctx):
     pin_u = np.array([0x3ddf57e5], np.uint32).view(np.float32).copy()
     rmi.silu_mul_inplace(pin_g, pin_u)
     assert bits(pin_u)[0] == 0xbcd98667
+
+
+@pytest.mark.parametrize("sem,n_tokens", [(orc.SEM_NEON, 70), (orc.SEM_AVX2, 6)])
+def test_qwen35_forward_ffn_parallel_matches_the_per_token_reference(rmi, ctx, sem, n_tokens):
+    """src/models/qwen35.rs:762-782: gate/up per token, silu_mul over all tokens, down per token."""
+    ctx.set_semantics(sem)
+    e, ff = 256, 512
+    g, u, d = (rmi.synth.q8_0_weight(ff, e, seed=61), rmi.synth.q8_0_weight(ff, e, seed=62),
+               rmi.synth.q8_0_weight(e, ff, seed=63))
+    ffn = rmi.Qwen35Ffn(rmi.QuantizedTensor.from_bytes(g, rmi.GGML_Q8_0, e, ff),
+                        rmi.QuantizedTensor.from_bytes(u, rmi.GGML_Q8_0, e, ff),
+                        rmi.QuantizedTensor.from_bytes(d, rmi.GGML_Q8_0, ff, e))
+    hidden = rmi.synth.normal((n_tokens, e), seed=64)
+    got = ffn.forward_ffn_parallel(hidden.reshape(-1), n_tokens)
+    # the reference order, step by step, with the oracle's single-token kernels
+    gate = orc.q8_forward_batched(g, hidden, e, ff, sem)
+    up = orc.q8_forward_batched(u, hidden, e, ff, sem)
+    act = np.ascontiguousarray(up.reshape(-1))
+    orc.silu_mul_inplace(gate.reshape(-1), act)       # up[i] *= silu(gate[i]) over all tokens at once
+    ref = orc.q8_forward_batched(d, act.reshape(n_tokens, ff), ff, e, sem)
+    assert np.array_equal(bits(got), bits(ref))
+    ffn.free()
