@@ -348,7 +348,10 @@ def main():
     ap.add_argument("--threads", type=int, default=0, help="CPU threads of the reference arm / cpu baseline (0 = all)")
     ap.add_argument("--semantics", default="neon", choices=["neon", "scalar", "avx2"])
     ap.add_argument("--no-also", action="store_true", help="skip the secondary figures (GEMV, decode)")
-    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv"],
+    ap.add_argument("--decode-batch", type=int, default=1)
+    ap.add_argument("--decode-prompt", type=int, default=512)
+    ap.add_argument("--decode-gen", type=int, default=128)
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv", "decode"],
                     help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -374,6 +377,28 @@ def main():
     ctx.set_stream(stream.cuda_stream)
     hbm_peak, bf16_peak, bf16_sus, peak_kind = measured_peaks()
     sm_count, l2_bytes, _ = ctx.device_info()
+    if args.workload == "decode":
+        # BASELINE config 4 on its own: Qwen3-0.6B-architecture greedy decode (synthetic GGUF, seed 0)
+        if rank == 0:
+            ctx.set_stream(None)
+            cfg = dict(pkg.synth.QWEN3_0_6B)
+            path = os.path.join(tempfile.gettempdir(), "rmi_qwen3_0_6b_seed0.gguf")
+            if not os.path.exists(path):
+                pkg.synth.write_qwen3_gguf(path, cfg, pkg.synth.qwen3_tensors(cfg, 0))
+            res, _ = decode_bench(pkg, ctx, cfg, path, args.decode_batch, args.decode_prompt, args.decode_gen, sem)
+            kv = 28 * (args.decode_prompt + args.decode_gen // 2) * 1024 * 2 * 2
+            roof = hbm_peak * 1e9 / (633233408 + args.decode_batch * kv) * args.decode_batch
+            print(json.dumps({"metric": "Qwen3-0.6B-architecture greedy decode throughput", "value": res["tok_s"],
+                              "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+                              "config": {"workload": "configs[3]: decode", "batch": args.decode_batch,
+                                         "prompt": args.decode_prompt, "gen": args.decode_gen, "semantics": args.semantics},
+                              "roofline": {"bound": "hbm", "achieved": res["tok_s"], "peak": roof, "unit": "tok/s",
+                                           "frac": res["tok_s"] / roof,
+                                           "peak_source": f"copy bandwidth ({peak_kind}) / bytes per step (weights once + KV per sequence)"},
+                              "result": res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "gemv":
         if rank == 0:
             run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind)
