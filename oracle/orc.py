@@ -246,6 +246,44 @@ def q4k_forward_prequantized(w, q8, scales, n_in, n_out, ith=0, nth=1, output=No
     return out
 
 
+def dequantize_row_q6_k(w, n):
+    w = _u8(w)
+    out = np.zeros(n, np.float32)
+    lib().orc_dequantize_row_q6_k(_p(w), C.c_size_t(w.size), _p(out), C.c_size_t(n))
+    return out
+
+
+def vec_dot_q6k_q8k(q6k, blocks, sem=SEM_AVX2):
+    q6k = _u8(q6k)
+    fn = lib().orc_vec_dot_q6k_q8k
+    fn.restype = C.c_float
+    return float(fn(_p(q6k), C.c_size_t(q6k.size), blocks, C.c_size_t(len(blocks)), C.c_int(sem)))
+
+
+def q6k_q8k_block_lanes(q6k_block, block):
+    q6k_block = _u8(q6k_block)
+    lanes = (C.c_int32 * 8)()
+    lib().orc_q6k_q8k_block_lanes(_p(q6k_block), C.byref(block), lanes)
+    return np.array(list(lanes), np.int32)
+
+
+def q6k_forward_prepared(w, x, n_in, n_out, ith=0, nth=1, sem=SEM_AVX2, output=None):
+    w, x = _u8(w), _f32(x)
+    out = np.zeros(n_out, np.float32) if output is None else output
+    lib().orc_q6k_forward_prepared(_p(w), C.c_size_t(w.size), _p(x), _p(out), C.c_size_t(n_in),
+                                   C.c_size_t(n_out), C.c_size_t(ith), C.c_size_t(nth), C.c_int(sem))
+    return out
+
+
+def q6k_forward_prequantized(w, q8, scales, n_in, n_out, ith=0, nth=1, output=None):
+    w, q8, scales = _u8(w), _u8(q8), _f32(scales)
+    out = np.zeros(n_out, np.float32) if output is None else output
+    lib().orc_q6k_forward_prequantized(_p(w), C.c_size_t(w.size), _p(q8), _p(scales), _p(out),
+                                       C.c_size_t(n_in), C.c_size_t(n_out), C.c_size_t(ith),
+                                       C.c_size_t(nth))
+    return out
+
+
 def rms_norm(x, w, eps):
     x, w = _f32(x), _f32(w)
     out = np.zeros_like(x)

@@ -826,6 +826,132 @@ void orc_q4k_forward_prequantized(const uint8_t* weight, size_t weight_len, cons
   free(row);
 }
 
+/* ------------------------------------------------------------------ Q6_K */
+
+/* the 6-bit value (0..63) at position e (0..255) of a super-block: mod.rs:542-555 */
+static inline int q6k_value(const uint8_t* blk, int e) {
+  const int j = e / 128, r = e % 128, k = r / 32, l = r % 32;
+  const uint8_t* ql = blk + j * 64;
+  const uint8_t qh = blk[128 + j * 32 + l];
+  int lo, hi;
+  switch (k) {
+    case 0: lo = ql[l] & 0xF; hi = qh & 3; break;
+    case 1: lo = ql[l + 32] & 0xF; hi = (qh >> 2) & 3; break;
+    case 2: lo = ql[l] >> 4; hi = (qh >> 4) & 3; break;
+    default: lo = ql[l + 32] >> 4; hi = (qh >> 6) & 3; break;
+  }
+  return lo | (hi << 4);
+}
+
+void orc_dequantize_row_q6_k(const uint8_t* bytes, size_t bytes_len, float* output, size_t n) {
+  size_t nb = n / 256;
+  for (size_t b = 0; b < nb; b++) {
+    if ((b + 1) * 210 > bytes_len) break;
+    const uint8_t* blk = bytes + b * 210;
+    float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8)));
+    for (int e = 0; e < 256; e++) {
+      /* scale index: j128*8 + is + {0,2,4,6} with is = l/16  ==  e/16 */
+      float sc = (float)(int8_t)blk[192 + e / 16];
+      int q = q6k_value(blk, e) - 32;
+      float ds = d * sc;
+      output[b * 256 + e] = ds * (float)q;
+    }
+  }
+}
+
+void orc_q6k_q8k_block_lanes(const uint8_t* blk, const orc_block_q8k* q8k, int32_t lanes[8]) {
+  /* mod.rs:998-1062.  Vector (j, k) covers positions 128j + 32k .. +31; int32 lane L of the madd result
+   * covers its bytes 4L..4L+3, bytes 0..15 scaled by scales[8j+2k], bytes 16..31 by scales[8j+2k+1]. */
+  const int8_t* sc = (const int8_t*)(blk + 192);
+  for (int L = 0; L < 8; L++) {
+    int32_t s = 0;
+    for (int v = 0; v < 8; v++) {
+      int base = 32 * v + 4 * L;
+      int32_t p = 0;
+      for (int t = 0; t < 4; t++) p += q6k_value(blk, base + t) * (int32_t)q8k->qs[base + t];
+      s += (int32_t)sc[2 * v + (L >= 4)] * p;
+    }
+    int32_t sub = ((int32_t)q8k->bsums[2 * L] * sc[2 * L] + (int32_t)q8k->bsums[2 * L + 1] * sc[2 * L + 1]) * 32;
+    lanes[L] = s - sub;
+  }
+}
+
+float orc_vec_dot_q6k_q8k(const uint8_t* q6k, size_t q6k_len, const orc_block_q8k* q8k, size_t nb, int sem) {
+  if (sem == ORC_SEM_SCALAR) {
+    /* mod.rs:640-692 */
+    float sums[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (size_t i = 0; i < nb; i++) {
+      if ((i + 1) * 210 > q6k_len) break;
+      const uint8_t* blk = q6k + i * 210;
+      int32_t aux32[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int g = 0; g < 16; g++) {
+        int32_t scale = (int8_t)blk[192 + g];
+        for (int t = 0; t < 16; t++) {
+          int e = 16 * g + t;
+          aux32[t % 8] += scale * (int32_t)q8k[i].qs[e] * (q6k_value(blk, e) - 32);
+        }
+      }
+      float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8))) * q8k[i].d;
+      for (int l = 0; l < 8; l++) {
+        float t = d * (float)aux32[l];
+        sums[l] = sums[l] + t;
+      }
+    }
+    float sumf = 0.0f;
+    for (int l = 0; l < 8; l++) sumf = sumf + sums[l];
+    return sumf;
+  }
+  /* AVX2, mod.rs:964-1064: eight f32 lanes, one FMA per super-block, hsum_ps at the end */
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (size_t i = 0; i < nb; i++) {
+    if ((i + 1) * 210 > q6k_len) break;
+    const uint8_t* blk = q6k + i * 210;
+    float d = orc_f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8))) * q8k[i].d;
+    int32_t lanes[8];
+    orc_q6k_q8k_block_lanes(blk, &q8k[i], lanes);
+    for (int L = 0; L < 8; L++) acc[L] = fmaf(d, (float)lanes[L], acc[L]);
+  }
+  return hsum8(acc);
+}
+
+void orc_q6k_forward_prepared(const uint8_t* weight, size_t weight_len, const float* input_f32, float* output,
+                              size_t n_in, size_t n_out, size_t ith, size_t nth, int sem) {
+  size_t per = (n_out + nth - 1) / nth;
+  size_t s = ith * per, e = s + per < n_out ? s + per : n_out;
+  if (s >= e) return;
+  size_t nb = n_in / 256;
+  orc_block_q8k* q = (orc_block_q8k*)malloc(sizeof(orc_block_q8k) * nb);
+  orc_quantize_row_q8_k(input_f32, n_in, q, sem);
+  size_t row_bytes = nb * 210;
+  (void)weight_len;
+  for (size_t r = s; r < e; r++) output[r] = orc_vec_dot_q6k_q8k(weight + r * row_bytes, row_bytes, q, nb, sem);
+  free(q);
+}
+
+void orc_q6k_forward_prequantized(const uint8_t* weight, size_t weight_len, const uint8_t* input_q8,
+                                  const float* input_scales, float* output, size_t n_in, size_t n_out,
+                                  size_t ith, size_t nth) {
+  size_t per = (n_out + nth - 1) / nth;
+  size_t s = ith * per, e = s + per < n_out ? s + per : n_out;
+  if (s >= e) return;
+  float* in = (float*)malloc(sizeof(float) * n_in);
+  float* row = (float*)malloc(sizeof(float) * n_in);
+  for (size_t i = 0; i < n_in; i++) in[i] = (float)(int8_t)input_q8[i] * input_scales[i / 32];
+  size_t row_bytes = n_in / 256 * 210;
+  (void)weight_len;
+  for (size_t r = s; r < e; r++) {
+    orc_dequantize_row_q6_k(weight + r * row_bytes, row_bytes, row, n_in);
+    float sum = 0.0f;
+    for (size_t i = 0; i < n_in; i++) {
+      float t = row[i] * in[i];
+      sum = sum + t;
+    }
+    output[r] = sum;
+  }
+  free(in);
+  free(row);
+}
+
 /* ------------------------------------------------------------------ element-wise ops */
 
 /* src/ops/norm.rs:3-11 */

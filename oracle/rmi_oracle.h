@@ -119,6 +119,21 @@ void orc_q4k_q8k_block_ints(const uint8_t* q4k_block, const orc_block_q8k* q8k,
 void orc_dequantize_row_q4_k(const uint8_t* bytes, size_t bytes_len, float* output, size_t n);
 void orc_dequantize_q4_k_weight(const uint8_t* bytes, size_t bytes_len, size_t n_rows,
                                 size_t n_cols, float* output);
+/* ---- Q6_K (210-byte super-blocks: ql[128] | qh[64] | scales i8[16] | f16 d) ----
+ * src/ops/quant/mod.rs:530-569: w = (d * sc) * q, q in [-32, 31]. */
+void orc_dequantize_row_q6_k(const uint8_t* bytes, size_t bytes_len, float* output, size_t n);
+/* src/ops/quant/mod.rs:640-692 (scalar), :964-1064 (AVX2). nb super-blocks. */
+float orc_vec_dot_q6k_q8k(const uint8_t* q6k, size_t q6k_len, const orc_block_q8k* q8k, size_t nb, int sem);
+/* the eight exact int32 lane sums of one super-block as the AVX2 kernel forms them (after the -32 offset term) */
+void orc_q6k_q8k_block_lanes(const uint8_t* q6k_block, const orc_block_q8k* q8k, int32_t lanes[8]);
+/* src/ops/kernel/q6_k.rs:44-80 (Q8_K activation, vec_dot per row, (ith, nth) partition) */
+void orc_q6k_forward_prepared(const uint8_t* weight, size_t weight_len, const float* input_f32, float* output,
+                              size_t n_in, size_t n_out, size_t ith, size_t nth, int sem);
+/* src/ops/kernel/q6_k.rs:83-115 (Q8_0 activation dequantized, row dequantized, sequential f32 dot) */
+void orc_q6k_forward_prequantized(const uint8_t* weight, size_t weight_len, const uint8_t* input_q8,
+                                  const float* input_scales, float* output, size_t n_in, size_t n_out,
+                                  size_t ith, size_t nth);
+
 /* src/core/model.rs:65-85: dequantize the whole matrix, then sequential f32 dot per row. */
 void orc_q4k_forward_dequant(const uint8_t* weight, size_t weight_len, size_t out_features,
                              size_t in_features, const float* input, float* output,

@@ -65,13 +65,27 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
   const size_t blocks = n / 32;
   float* xr = x + b * n;
   double part = 0.0;
-  for (size_t blk = warp; blk < blocks; blk += 8) {
-    float v = xr[blk * 32 + lane];
-    if (add) {
-      v = __fadd_rn(v, add[b * n + blk * 32 + lane]);
-      xr[blk * 32 + lane] = v;
+  constexpr int NB = 4;  // blocks per batch: all loads of a batch are issued before the first use
+  for (size_t b0 = warp; b0 < blocks; b0 += 8 * NB) {
+    float v[NB], a2[NB];
+#pragma unroll
+    for (int u = 0; u < NB; u++) {
+      const size_t blk = b0 + 8 * u;
+      v[u] = blk < blocks ? xr[blk * 32 + lane] : 0.0f;
+      a2[u] = (add && blk < blocks) ? add[b * n + blk * 32 + lane] : 0.0f;
     }
-    part += (double)__fmul_rn(v, v);
+#pragma unroll
+    for (int u = 0; u < NB; u++) {
+      const size_t blk = b0 + 8 * u;
+      if (blk < blocks) {
+        float val = v[u];
+        if (add) {
+          val = __fadd_rn(val, a2[u]);
+          xr[blk * 32 + lane] = val;
+        }
+        part += (double)__fmul_rn(val, val);
+      }
+    }
   }
   part = warp_sum_f64(part);
   if (lane == 0) s_part[warp] = part;
@@ -103,6 +117,35 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
 __device__ __forceinline__ void norm_rope_head_f16(const float* __restrict__ src, const float* __restrict__ nw, float eps,
                                                    const float* __restrict__ tab, size_t hd, int lane, uint16_t* dst) {
   const size_t half = hd / 2;
+  if (hd == 128) {
+    // the usual head size: every global load (values, norm weights, cos/sin) is issued before the first use
+    float xv[4], wv[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      xv[u] = src[lane + 32 * u];
+      wv[u] = nw ? nw[lane + 32 * u] : 1.0f;
+    }
+    const float2 cs0 = *reinterpret_cast<const float2*>(tab + 2 * lane);
+    const float2 cs1 = *reinterpret_cast<const float2*>(tab + 2 * (lane + 32));
+    double part = 0.0;
+#pragma unroll
+    for (int u = 0; u < 4; u++) part += (double)__fmul_rn(xv[u], xv[u]);
+    part = warp_sum_f64(part);
+    if (nw) {
+      const float mean_sq = (float)(part / 128.0);
+      const float sc = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, eps)));
+#pragma unroll
+      for (int u = 0; u < 4; u++) xv[u] = __fmul_rn(__fmul_rn(xv[u], sc), wv[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; u++) {  // pairs (i, i + 64), i = lane + 32 u
+      const float x0 = xv[u], x1 = xv[u + 2];
+      const float c = u == 0 ? cs0.x : cs1.x, sn = u == 0 ? cs0.y : cs1.y;
+      dst[lane + 32 * u] = f32_to_f16_bits(__fmaf_rn(x0, c, __fmul_rn(x1, -sn)));
+      dst[lane + 32 * u + 64] = f32_to_f16_bits(__fmaf_rn(x0, sn, __fmul_rn(x1, c)));
+    }
+    return;
+  }
   double part = 0.0;
   for (size_t i = lane; i < hd; i += 32) part += (double)__fmul_rn(src[i], src[i]);
   part = warp_sum_f64(part);

@@ -480,17 +480,32 @@ __global__ void __launch_bounds__(128)
     __shared__ float s_scale[MP];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t seq0 = (size_t)blockIdx.y * MP;
+    // Warp w owns the 32-blocks w, w+4, ...; they are handled NB at a time with every global load of a batch
+    // (input, residual, norm weight) issued before the first use: loads inside a rolled loop would be serialised.
+    constexpr int NB = 8;
 #pragma unroll
     for (int m = 0; m < MP; m++) {
       const float* xi = na.x_in + (seq0 + m) * K;
       const float* ad = na.add ? na.add + (seq0 + m) * K : nullptr;
       double part = 0.0;
-      for (size_t blk = warp; blk < blocks; blk += 4) {
-        float v = __ldg(xi + blk * 32 + lane);
-        if (ad) v = __fadd_rn(v, __ldg(ad + blk * 32 + lane));
-        xf[m * K + blk * 32 + lane] = v;
-        if (na.x_out && blockIdx.x == 0) na.x_out[(seq0 + m) * K + blk * 32 + lane] = v;
-        part += (double)__fmul_rn(v, v);
+      for (size_t b0 = warp; b0 < blocks; b0 += 4 * NB) {
+        float v[NB], a2[NB];
+#pragma unroll
+        for (int u = 0; u < NB; u++) {
+          const size_t blk = b0 + 4 * u;
+          v[u] = blk < blocks ? __ldg(xi + blk * 32 + lane) : 0.0f;
+          a2[u] = (ad && blk < blocks) ? __ldg(ad + blk * 32 + lane) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < NB; u++) {
+          const size_t blk = b0 + 4 * u;
+          if (blk < blocks) {
+            const float val = ad ? __fadd_rn(v[u], a2[u]) : v[u];
+            xf[m * K + blk * 32 + lane] = val;
+            if (na.x_out && blockIdx.x == 0) na.x_out[(seq0 + m) * K + blk * 32 + lane] = val;
+            part += (double)__fmul_rn(val, val);
+          }
+        }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
@@ -503,18 +518,27 @@ __global__ void __launch_bounds__(128)
       s_scale[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, na.eps)));
     }
     __syncthreads();
+    for (size_t b0 = warp; b0 < blocks; b0 += 4 * NB) {
+      float nw[NB];
 #pragma unroll
-    for (int m = 0; m < MP; m++) {
-      const float sc = s_scale[m];
-      for (size_t blk = warp; blk < blocks; blk += 4) {
-        const float v = __fmul_rn(__fmul_rn(xf[m * K + blk * 32 + lane], sc), __ldg(na.norm_w + blk * 32 + lane));
-        float a = fabsf(v);
+      for (int u = 0; u < NB; u++) nw[u] = b0 + 4 * u < blocks ? __ldg(na.norm_w + (b0 + 4 * u) * 32 + lane) : 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-        float d, inv;
-        q8_scale_pair<SEM>(a, &d, &inv);
-        xq_s[m * K + blk * 32 + lane] = (int8_t)q8_quant_value<SEM>(v, inv);
-        if (lane == 0) xs_s[m * blocks + blk] = f16_round_trip(d);
+      for (int m = 0; m < MP; m++) {
+        const float sc = s_scale[m];
+#pragma unroll
+        for (int u = 0; u < NB; u++) {
+          const size_t blk = b0 + 4 * u;
+          if (blk < blocks) {
+            const float v = __fmul_rn(__fmul_rn(xf[m * K + blk * 32 + lane], sc), nw[u]);
+            float a = fabsf(v);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            float d, inv;
+            q8_scale_pair<SEM>(a, &d, &inv);
+            xq_s[m * K + blk * 32 + lane] = (int8_t)q8_quant_value<SEM>(v, inv);
+            if (lane == 0) xs_s[m * blocks + blk] = f16_round_trip(d);
+          }
+        }
       }
     }
   }

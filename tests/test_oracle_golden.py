@@ -440,3 +440,99 @@ def test_session_sizing_steps_and_token_count():
     prompt = np.array([1, 2, 3], np.uint32)
     toks, trace = m.generate(prompt, 4, want_trace=True)
     assert len(toks) == 4 and trace.shape[0] == 3 + 4 - 1
+
+
+# ---------------------------------------------------------------- Q6_K (src/ops/quant/mod.rs)
+
+def _q6k_block(ql, qh, scales, d):
+    """make_q6k_block, src/ops/quant/mod.rs:1097-1111"""
+    v = np.zeros(210, np.uint8)
+    v[:128], v[128:192] = ql, qh
+    v[192:208] = np.asarray(scales, np.int8).view(np.uint8)
+    v[208:210] = np.array([d], np.float16).view(np.uint8)
+    return v
+
+
+def _q8k_test_blocks(values):
+    """block_q8k of the reference's test module (mod.rs:1070-1087): d = amax/127, q = round-half-away(v*127/amax)."""
+    values = np.asarray(values, np.float32)
+    blocks = (orc.BlockQ8K * (values.size // 256))()
+    for b, chunk in enumerate(values.reshape(-1, 256)):
+        amax = np.float32(np.abs(chunk).max())
+        idv = np.float32(0) if amax == 0 else np.float32(127.0) / amax
+        blocks[b].d = float(np.float32(0) if amax == 0 else amax / np.float32(127.0))
+        t = (chunk * idv).astype(np.float32)
+        q = np.clip(np.where(t >= 0, np.floor(t + np.float32(0.5)), np.ceil(t - np.float32(0.5))), -127, 127).astype(np.int8)
+        for i in range(256):
+            blocks[b].qs[i] = int(q[i])
+        for g in range(16):
+            blocks[b].bsums[g] = int(q[16 * g:16 * g + 16].astype(np.int32).sum())
+    return blocks
+
+
+def test_q6k_reference_fixture_one_block_avx2_vs_scalar():
+    # q6k_avx2_matches_scalar_one_block, src/ops/quant/mod.rs:1165-1184
+    ql = np.array([i % 4 for i in range(128)], np.uint8)
+    qh = np.array([i * 5 % 4 for i in range(64)], np.uint8)
+    w = _q6k_block(ql, qh, [i - 4 for i in range(16)], 0.5)
+    x = np.array([(i - 128.0) * 0.01 for i in range(256)], np.float32)
+    q8k = _q8k_test_blocks(x)
+    avx2, scalar = orc.vec_dot_q6k_q8k(w, q8k, orc.SEM_AVX2), orc.vec_dot_q6k_q8k(w, q8k, orc.SEM_SCALAR)
+    rel = abs(avx2 - scalar) / abs(scalar) if abs(scalar) > 1e-3 else abs(avx2 - scalar)
+    assert rel < 1e-3
+    # both equal the dot of the dequantized row with the dequantized activation to f32 accuracy
+    deq = orc.dequantize_row_q6_k(w, 256).astype(np.float64)
+    d8, qs, _ = orc.q8k_to_numpy(q8k)
+    ref = float((deq * (qs[0].astype(np.float64) * float(d8[0]))).sum())
+    assert abs(avx2 - ref) <= 1e-5 * max(1.0, abs(ref)) and abs(scalar - ref) <= 1e-5 * max(1.0, abs(ref))
+
+
+def test_q6k_reference_fixture_four_blocks_avx2_vs_scalar():
+    # q6k_avx2_matches_scalar_multi_block, src/ops/quant/mod.rs:1187-1211
+    w = np.concatenate([_q6k_block(np.array([(i * 11 + j * 3) % 4 for j in range(128)], np.uint8),
+                                   np.array([(i + j * 7) % 4 for j in range(64)], np.uint8),
+                                   [(i * 5 + k) - 6 for k in range(16)], 0.01 + i * 0.1) for i in range(4)])
+    x = np.array([(i - 512.0) * 0.01 for i in range(1024)], np.float32)
+    q8k = _q8k_test_blocks(x)
+    avx2, scalar = orc.vec_dot_q6k_q8k(w, q8k, orc.SEM_AVX2), orc.vec_dot_q6k_q8k(w, q8k, orc.SEM_SCALAR)
+    rel = abs(avx2 - scalar) / abs(scalar) if abs(scalar) > 1e-3 else abs(avx2 - scalar)
+    assert rel < 1e-3
+
+
+def test_q6k_lane_sums_equal_the_scalar_integer_sums():
+    """The eight AVX2 int32 lanes (with the -32 offset folded through bsums) sum to the scalar kernel's
+    Σ scale·q8·(q6-32) exactly, on random bytes."""
+    rng = np.random.default_rng(11)
+    blk = rng.integers(0, 256, 210, dtype=np.uint8)
+    x = rng.standard_normal(256).astype(np.float32)
+    q8k = orc.quantize_row_q8_k(x, orc.SEM_AVX2)
+    lanes = orc.q6k_q8k_block_lanes(blk, q8k[0])
+    _, qs, _ = orc.q8k_to_numpy(q8k)
+    sc = blk[192:208].view(np.int8).astype(np.int64)
+    deq_int = np.array([0] * 256, np.int64)
+    row = orc.dequantize_row_q6_k(np.concatenate([blk[:208], np.array([1.0], np.float16).view(np.uint8)]), 256)
+    # with d = 1 the dequantized value is sc * (q - 32) exactly
+    total = int((row.astype(np.int64) * qs[0].astype(np.int64)).sum())
+    assert int(lanes.astype(np.int64).sum()) == total
+    del deq_int, sc
+
+
+def test_q6k_forward_partition_and_prequantized_path():
+    rng = np.random.default_rng(12)
+    n_in, n_out = 512, 24
+    w = rng.integers(0, 256, n_out * (n_in // 256) * 210, dtype=np.uint8)
+    for r in range(n_out * (n_in // 256)):   # sane f16 scales
+        w[r * 210 + 208:r * 210 + 210] = np.array([0.01 + 0.001 * (r % 7)], np.float16).view(np.uint8)
+    x = rng.standard_normal(n_in).astype(np.float32)
+    for sem in (orc.SEM_AVX2, orc.SEM_SCALAR):
+        whole = orc.q6k_forward_prepared(w, x, n_in, n_out, sem=sem)
+        parts = np.zeros(n_out, np.float32)
+        for ith in range(5):
+            orc.q6k_forward_prepared(w, x, n_in, n_out, ith, 5, sem=sem, output=parts)
+        assert np.array_equal(whole.view(np.uint32), parts.view(np.uint32))
+    q8, sc = orc.quantize_q8_0(x, orc.SEM_AVX2)
+    pre = orc.q6k_forward_prequantized(w, q8, sc, n_in, n_out)
+    deq = np.stack([orc.dequantize_row_q6_k(w[r * 420:(r + 1) * 420], n_in) for r in range(n_out)]).astype(np.float64)
+    xin = q8.reshape(-1).view(np.int8).astype(np.float64) * np.repeat(sc.reshape(-1).astype(np.float64), 32)
+    ref = deq @ xin
+    assert np.abs(pre - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
