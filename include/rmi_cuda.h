@@ -48,7 +48,7 @@ typedef enum {
 } rmi_status;
 
 /* ggml type ids as in src/core/tensor.rs:15-35 */
-enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12 };
+enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12, RMI_GGML_Q6_K = 14 };
 
 /* The reference has three instruction-set variants of this path whose f32 results are not
  * bit-identical to each other (docs/OPTIMIZATION.md:330-332).  The device reproduces the
@@ -197,6 +197,21 @@ int32_t rmi_matmul_q4_k_dequant_dev(rmi_ctx* ctx, const rmi_weight* w, const flo
                                     float* output);
 /* dequantize_q4_k_weight (src/ops/quant/mod.rs:492-508) */
 int32_t rmi_dequantize_q4_k(rmi_ctx* ctx, const rmi_weight* w, float* output);
+
+/* ---- Q6_K (rmi_weight_upload with ggml type 14; 210-byte super-blocks) ------------------------
+ * Q6_KKernel::forward_prepared (src/ops/kernel/q6_k.rs:44-80): Q8_K-quantize every row of x, then
+ * vec_dot_q6k_q8k per weight row (src/ops/quant/mod.rs:640-692 scalar, :964-1064 AVX2), rows
+ * [row_begin, row_end) of output [m, n_rows].  Bit-exact under AVX2 and SCALAR semantics. */
+int32_t rmi_matmul_q6_k_q8k(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
+                            float* output, size_t row_begin, size_t row_end);
+/* Q6_KKernel::forward_prequantized = matmul_q6_k_scalar_range (src/ops/kernel/q6_k.rs:83-115): the
+ * Q8_0 activation (q8 [m, n_in], scales [m, n_in/32]) dequantized, times the dequantized row
+ * (src/ops/quant/mod.rs:530-569); f32 within 1e-4 of the reference's sequential sum. */
+int32_t rmi_matmul_q6_k_prequantized(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8,
+                                     const float* scales, size_t m, float* output,
+                                     size_t row_begin, size_t row_end);
+/* dequant_q6k_weight (src/ops/quant/mod.rs:571-583): all rows to f32 [n_rows, n_in], bit-exact. */
+int32_t rmi_dequantize_q6_k(rmi_ctx* ctx, const rmi_weight* w, float* output);
 
 /* ---- GGUF -------------------------------------------------------------------------------
  * GGUFLoader::from_file / tensor_info / tensor_slice / metadata (src/core/loader.rs:211-395):

@@ -29,7 +29,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "librmi_cuda.so")
 
 SEM_AVX2, SEM_NEON, SEM_SCALAR = 0, 1, 2
-GGML_F32, GGML_Q8_0, GGML_Q4_K = 0, 8, 12
+GGML_F32, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 8, 12, 14
 STATUS = {0: "RMI_OK", 1: "RMI_ERR_BAD_HANDLE", 2: "RMI_ERR_BAD_SHAPE", 3: "RMI_ERR_OOM", 4: "RMI_ERR_CUDA",
           5: "RMI_ERR_TIMEOUT", 6: "RMI_ERR_UNSUPPORTED", 7: "RMI_ERR_IO", 8: "RMI_ERR_FORMAT",
           9: "RMI_ERR_NONFINITE"}
@@ -219,6 +219,8 @@ class QuantizedTensor:
             return Q8Kernel(self)
         if self.ggml_type == GGML_Q4_K:
             return Q4_KKernel(self)
+        if self.ggml_type == GGML_Q6_K:
+            return Q6_KKernel(self)
         raise RmiError(6, f"ggml type {self.ggml_type} has no kernel on this path")
 
     def device_bytes(self) -> int:
@@ -327,6 +329,42 @@ class Q4_KKernel(Kernel):
         full = np.zeros(n_out, np.float32)
         _check(lib().rmi_matmul_q4_k_dequant(self._ctx.handle, self.weight._h, _p(x), _sz(1), _p(full)))
         output.reshape(-1)[s:e] = full[s:e]
+
+
+class Q6_KKernel(Kernel):
+    """Q6_KKernel (src/ops/kernel/q6_k.rs:7-80)."""
+
+    @classmethod
+    def new(cls, data, n_in: int, n_out: int, ctx: Context | None = None) -> "Q6_KKernel":
+        return cls(QuantizedTensor.from_bytes(data, GGML_Q6_K, n_in, n_out, ctx=ctx))
+
+    def forward_prepared(self, input_f32, input_q8, input_scales, q8_k, output, n_in, n_out, ith, nth):
+        # q6_k.rs:44-80; a caller-prepared Q8_K is recomputed on the device from input_f32 (deterministic)
+        input_f32 = np.ascontiguousarray(input_f32, np.float32).reshape(-1, n_in)
+        per = (n_out + nth - 1) // nth
+        s, e = ith * per, min(ith * per + per, n_out)
+        if s >= e:
+            return
+        _check(lib().rmi_matmul_q6_k_q8k(self._ctx.handle, self.weight._h, _p(input_f32), _sz(input_f32.shape[0]),
+                                         _p(output), _sz(s), _sz(e)))
+
+    def forward_prequantized(self, input_q8, input_scales, output, n_in, n_out, ith, nth):
+        # q6_k.rs:22-42 -> matmul_q6_k_scalar_range (q6_k.rs:83-115)
+        q8 = np.ascontiguousarray(input_q8, np.uint8).reshape(-1)[:n_in]
+        sc = np.ascontiguousarray(input_scales, np.float32).reshape(-1)[: n_in // 32]
+        per = (n_out + nth - 1) // nth
+        s, e = ith * per, min(ith * per + per, n_out)
+        if s >= e:
+            return
+        _check(lib().rmi_matmul_q6_k_prequantized(self._ctx.handle, self.weight._h, _p(q8), _p(sc), _sz(1), _p(output),
+                                                  _sz(s), _sz(e)))
+
+
+def dequantize_q6_k(weight: "QuantizedTensor") -> np.ndarray:
+    """dequant_q6k_weight (src/ops/quant/mod.rs:571-583)"""
+    out = np.zeros((weight.n_out, weight.n_in), np.float32)
+    _check(lib().rmi_dequantize_q6_k(weight._ctx.handle, weight._h, _p(out)))
+    return out
 
 
 # ------------------------------------------------------------------------------ free functions

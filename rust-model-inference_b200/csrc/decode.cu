@@ -98,15 +98,28 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
   }
   __syncthreads();
   const float sc = s_scale;
-  for (size_t blk = warp; blk < blocks; blk += 8) {
-    const float v = __fmul_rn(__fmul_rn(xr[blk * 32 + lane], sc), weight[blk * 32 + lane]);
-    float a = fabsf(v);
+  for (size_t b0 = warp; b0 < blocks; b0 += 8 * NB) {
+    float xv[NB], wv[NB];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    float d, inv;
-    q8_scale_pair<SEM>(a, &d, &inv);
-    q8[b * n + blk * 32 + lane] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
-    if (lane == 0) scales[b * blocks + blk] = f16_round_trip(d);
+    for (int u = 0; u < NB; u++) {
+      const size_t blk = b0 + 8 * u;
+      xv[u] = blk < blocks ? xr[blk * 32 + lane] : 0.0f;
+      wv[u] = blk < blocks ? weight[blk * 32 + lane] : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < NB; u++) {
+      const size_t blk = b0 + 8 * u;
+      if (blk < blocks) {
+        const float v = __fmul_rn(__fmul_rn(xv[u], sc), wv[u]);
+        float a = fabsf(v);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        float d, inv;
+        q8_scale_pair<SEM>(a, &d, &inv);
+        q8[b * n + blk * 32 + lane] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
+        if (lane == 0) scales[b * blocks + blk] = f16_round_trip(d);
+      }
+    }
   }
 }
 
@@ -282,10 +295,19 @@ __global__ void __launch_bounds__(256)
           uint16_t* vrow = reinterpret_cast<uint16_t*>(vbuf) + tl * hd;
           uint16_t* vg = v_cache + ((b * n_layer + layer) * capacity + t0) * nk + kvh * hd + cache_off;
           const float* vsrc = proj + nq + nk + kvh * hd;
-          for (size_t i = lane; i < hd; i += 32) {
-            const uint16_t h = f32_to_f16_bits(vsrc[i]);
-            vrow[i] = h;
-            vg[i] = h;
+          for (size_t i0 = lane; i0 < hd; i0 += 128) {  // four loads in flight per lane
+            float vv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) vv[u] = i0 + 32 * u < hd ? vsrc[i0 + 32 * u] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              const size_t i = i0 + 32 * u;
+              if (i < hd) {
+                const uint16_t h = f32_to_f16_bits(vv[u]);
+                vrow[i] = h;
+                vg[i] = h;
+              }
+            }
           }
         }
       }

@@ -83,6 +83,17 @@ def q4_k_weight(n: int, k: int, seed: int) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q6_k_weight(n: int, k: int, seed: int) -> np.ndarray:
+    """A valid Q6_K super-block stream [n, k/256, 210]: uniform random ql/qh bytes and int8 scales, f16 d sized so
+    that decoded weights have roughly N(0,0.02) spread.  Parity is defined on decoding these bytes."""
+    rng = np.random.default_rng(seed)
+    nb = k // 256
+    out = rng.integers(0, 256, size=(n, nb, 210), dtype=np.uint8)
+    d = (rng.uniform(0.5, 1.5, size=(n, nb)) * (0.02 / 64.0 / 20.0)).astype(np.float16).view(np.uint16)
+    out[:, :, 208], out[:, :, 209] = d & 0xff, d >> 8
+    return out.reshape(-1)
+
+
 def prompt_tokens(vocab: int, n: int, seed: int) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, vocab, size=n, dtype=np.uint32)
 
