@@ -48,7 +48,7 @@ typedef enum {
 } rmi_status;
 
 /* ggml type ids as in src/core/tensor.rs:15-35 */
-enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12, RMI_GGML_Q6_K = 14 };
+enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q4_0 = 2, RMI_GGML_Q8_0 = 8, RMI_GGML_Q4_K = 12, RMI_GGML_Q6_K = 14 };
 
 /* The reference has three instruction-set variants of this path whose f32 results are not
  * bit-identical to each other (docs/OPTIMIZATION.md:330-332).  The device reproduces the
@@ -197,6 +197,17 @@ int32_t rmi_matmul_q4_k_dequant_dev(rmi_ctx* ctx, const rmi_weight* w, const flo
                                     float* output);
 /* dequantize_q4_k_weight (src/ops/quant/mod.rs:492-508) */
 int32_t rmi_dequantize_q4_k(rmi_ctx* ctx, const rmi_weight* w, float* output);
+
+/* ---- Q4_0 (rmi_weight_upload with ggml type 2; 18-byte blocks) -------------------------------
+ * Q4_0Kernel::forward_prequantized (src/ops/kernel/q4_0/mod.rs:29-80, scalar.rs:13-53; the AVX2 kernel is
+ * bit-identical by contract): exact block dots with the Q8_0 activation (q8 [m, n_in], scales [m, n_in/32]),
+ * sum += (f32(dot) * d) * scale in block order; rows [row_begin, row_end) of output [m, n_rows].  Bit-exact. */
+int32_t rmi_matmul_q4_0_prequantized(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8,
+                                     const float* scales, size_t m, float* output,
+                                     size_t row_begin, size_t row_end);
+/* Kernel::forward for Q4_0 (src/ops/kernel/trait_.rs:57-76): quantize x to Q8_0 with the context's
+ * semantics, then the call above over all rows. */
+int32_t rmi_matmul_q4_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
 
 /* ---- Q6_K (rmi_weight_upload with ggml type 14; 210-byte super-blocks) ------------------------
  * Q6_KKernel::forward_prepared (src/ops/kernel/q6_k.rs:44-80): Q8_K-quantize every row of x, then

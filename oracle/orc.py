@@ -246,6 +246,14 @@ def q4k_forward_prequantized(w, q8, scales, n_in, n_out, ith=0, nth=1, output=No
     return out
 
 
+def q4_0_forward_prequantized(w, q8, scales, n_in, n_out, ith=0, nth=1, output=None):
+    w, q8, scales = _u8(w), _u8(q8), _f32(scales)
+    out = np.zeros(n_out, np.float32) if output is None else output
+    lib().orc_q4_0_forward_prequantized(_p(w), _p(q8), _p(scales), _p(out), C.c_size_t(n_in), C.c_size_t(n_out),
+                                        C.c_size_t(ith), C.c_size_t(nth))
+    return out
+
+
 def dequantize_row_q6_k(w, n):
     w = _u8(w)
     out = np.zeros(n, np.float32)

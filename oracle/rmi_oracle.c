@@ -826,6 +826,32 @@ void orc_q4k_forward_prequantized(const uint8_t* weight, size_t weight_len, cons
   free(row);
 }
 
+/* ------------------------------------------------------------------ Q4_0 */
+
+void orc_q4_0_forward_prequantized(const uint8_t* weight, const uint8_t* input_q8, const float* input_scales,
+                                   float* output, size_t n_in, size_t n_out, size_t ith, size_t nth) {
+  size_t n_blocks = n_in / 32, row_stride = n_blocks * 18;
+  size_t per = (n_out + nth - 1) / nth;
+  size_t s = ith * per, e = s + per < n_out ? s + per : n_out;
+  if (s >= e) return;
+  for (size_t r = s; r < e; r++) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < n_blocks; b++) {
+      const uint8_t* blk = weight + r * row_stride + b * 18;
+      float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+      int32_t dot = 0;
+      for (int l = 0; l < 16; l++) {
+        int x0 = (blk[2 + l] & 0x0F) - 8, x1 = (blk[2 + l] >> 4) - 8;
+        dot += x0 * (int32_t)(int8_t)input_q8[b * 32 + l] + x1 * (int32_t)(int8_t)input_q8[b * 32 + 16 + l];
+      }
+      float t = (float)dot * d;
+      t = t * input_scales[b];
+      sum = sum + t;
+    }
+    output[r] = sum;
+  }
+}
+
 /* ------------------------------------------------------------------ Q6_K */
 
 /* the 6-bit value (0..63) at position e (0..255) of a super-block: mod.rs:542-555 */

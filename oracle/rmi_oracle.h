@@ -119,6 +119,12 @@ void orc_q4k_q8k_block_ints(const uint8_t* q4k_block, const orc_block_q8k* q8k,
 void orc_dequantize_row_q4_k(const uint8_t* bytes, size_t bytes_len, float* output, size_t n);
 void orc_dequantize_q4_k_weight(const uint8_t* bytes, size_t bytes_len, size_t n_rows,
                                 size_t n_cols, float* output);
+/* ---- Q4_0 (18-byte blocks: f16 d | 16 nibble bytes; value l = low nibble of byte l, value 16+l = high nibble)
+ * src/ops/kernel/q4_0/scalar.rs:13-53; the AVX2 kernel (q4_0/avx2.rs:25-108) is bit-identical by contract:
+ * exact int32 block dot of (nibble - 8) with the Q8_0 activation, sum += (f32(dot) * d) * scale in block order. */
+void orc_q4_0_forward_prequantized(const uint8_t* weight, const uint8_t* input_q8, const float* input_scales,
+                                   float* output, size_t n_in, size_t n_out, size_t ith, size_t nth);
+
 /* ---- Q6_K (210-byte super-blocks: ql[128] | qh[64] | scales i8[16] | f16 d) ----
  * src/ops/quant/mod.rs:530-569: w = (d * sc) * q, q in [-32, 31]. */
 void orc_dequantize_row_q6_k(const uint8_t* bytes, size_t bytes_len, float* output, size_t n);

@@ -29,7 +29,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "librmi_cuda.so")
 
 SEM_AVX2, SEM_NEON, SEM_SCALAR = 0, 1, 2
-GGML_F32, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 8, 12, 14
+GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
 STATUS = {0: "RMI_OK", 1: "RMI_ERR_BAD_HANDLE", 2: "RMI_ERR_BAD_SHAPE", 3: "RMI_ERR_OOM", 4: "RMI_ERR_CUDA",
           5: "RMI_ERR_TIMEOUT", 6: "RMI_ERR_UNSUPPORTED", 7: "RMI_ERR_IO", 8: "RMI_ERR_FORMAT",
           9: "RMI_ERR_NONFINITE"}
@@ -221,6 +221,8 @@ class QuantizedTensor:
             return Q4_KKernel(self)
         if self.ggml_type == GGML_Q6_K:
             return Q6_KKernel(self)
+        if self.ggml_type == GGML_Q4_0:
+            return Q4_0Kernel(self)
         raise RmiError(6, f"ggml type {self.ggml_type} has no kernel on this path")
 
     def device_bytes(self) -> int:
@@ -358,6 +360,32 @@ class Q6_KKernel(Kernel):
             return
         _check(lib().rmi_matmul_q6_k_prequantized(self._ctx.handle, self.weight._h, _p(q8), _p(sc), _sz(1), _p(output),
                                                   _sz(s), _sz(e)))
+
+
+class Q4_0Kernel(Kernel):
+    """Q4_0Kernel (src/ops/kernel/q4_0/mod.rs:14-80)."""
+
+    @classmethod
+    def new(cls, data, n_in: int, n_out: int, ctx: Context | None = None) -> "Q4_0Kernel":
+        return cls(QuantizedTensor.from_bytes(data, GGML_Q4_0, n_in, n_out, ctx=ctx))
+
+    def forward_prequantized(self, input_q8, input_scales, output, n_in, n_out, ith, nth):
+        q8 = np.ascontiguousarray(input_q8, np.uint8).reshape(-1)[:n_in]
+        sc = np.ascontiguousarray(input_scales, np.float32).reshape(-1)[: n_in // 32]
+        per = (n_out + nth - 1) // nth
+        s, e = ith * per, min(ith * per + per, n_out)
+        if s >= e:
+            return
+        _check(lib().rmi_matmul_q4_0_prequantized(self._ctx.handle, self.weight._h, _p(q8), _p(sc), _sz(1), _p(output),
+                                                  _sz(s), _sz(e)))
+
+
+def matmul_q4_0(weight: "QuantizedTensor", x) -> np.ndarray:
+    """Kernel::forward for every row of x (quantize to Q8_0, then Q4_0 x Q8_0)."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, weight.n_in)
+    out = np.zeros((x.shape[0], weight.n_out), np.float32)
+    _check(lib().rmi_matmul_q4_0(weight._ctx.handle, weight._h, _p(x), _sz(x.shape[0]), _p(out)))
+    return out
 
 
 def dequantize_q6_k(weight: "QuantizedTensor") -> np.ndarray:

@@ -342,10 +342,12 @@ extern "C" int32_t rmi_weight_upload(rmi_ctx* ctx, int32_t ggml_type, const void
   RMI_TRY(rmi_check_ctx(ctx));
   RMI_REQUIRE(out != nullptr && bytes != nullptr, RMI_ERR_BAD_HANDLE, "rmi_weight_upload: null argument");
   *out = nullptr;
-  RMI_REQUIRE(ggml_type == RMI_GGML_Q8_0 || ggml_type == RMI_GGML_Q4_K || ggml_type == RMI_GGML_Q6_K, RMI_ERR_UNSUPPORTED,
-              "ggml type %d is not handled by this path (Q8_0 = 8, Q4_K = 12 and Q6_K = 14 are)", ggml_type);
-  const size_t be = ggml_type == RMI_GGML_Q8_0 ? 32 : 256;
-  const size_t bb = ggml_type == RMI_GGML_Q8_0 ? 34 : (ggml_type == RMI_GGML_Q4_K ? 144 : 210);
+  RMI_REQUIRE(ggml_type == RMI_GGML_Q8_0 || ggml_type == RMI_GGML_Q4_K || ggml_type == RMI_GGML_Q6_K ||
+                  ggml_type == RMI_GGML_Q4_0,
+              RMI_ERR_UNSUPPORTED,
+              "ggml type %d is not handled by this path (Q4_0 = 2, Q8_0 = 8, Q4_K = 12 and Q6_K = 14 are)", ggml_type);
+  const size_t be = (ggml_type == RMI_GGML_Q8_0 || ggml_type == RMI_GGML_Q4_0) ? 32 : 256;
+  const size_t bb = ggml_type == RMI_GGML_Q8_0 ? 34 : (ggml_type == RMI_GGML_Q4_0 ? 18 : (ggml_type == RMI_GGML_Q4_K ? 144 : 210));
   RMI_REQUIRE(n_in > 0 && n_in % be == 0, RMI_ERR_BAD_SHAPE, "n_in=%zu is not a multiple of %zu", n_in, be);
   RMI_REQUIRE(row_begin <= row_end && row_end <= n_out, RMI_ERR_BAD_SHAPE,
               "row range [%zu,%zu) outside [0,%zu)", row_begin, row_end, n_out);
@@ -358,12 +360,20 @@ extern "C" int32_t rmi_weight_upload(rmi_ctx* ctx, int32_t ggml_type, const void
   RMI_REQUIRE(w != nullptr, RMI_ERR_OOM, "host allocation failed");
   const uint8_t* src = (const uint8_t*)bytes + row_begin * row_bytes;
   int32_t st = RMI_OK;
-  if (ggml_type == RMI_GGML_Q6_K) {
-    // 210-byte super-blocks padded to an aligned device stride
-    const size_t nsb = n_rows * (n_in / 256), stride = q6k_device_block_bytes();
+  if (ggml_type == RMI_GGML_Q6_K || ggml_type == RMI_GGML_Q4_0) {
+    // 210-byte super-blocks / 18-byte blocks padded to an aligned device stride
+    const bool q6 = ggml_type == RMI_GGML_Q6_K;
+    const size_t nsb = n_rows * (n_in / be), stride = q6 ? q6k_device_block_bytes() : q4_0_device_block_bytes();
     w->raw_bytes = nsb * stride;
     std::vector<uint8_t> staged(w->raw_bytes ? w->raw_bytes : 1, 0);
-    for (size_t i = 0; i < nsb; i++) memcpy(staged.data() + i * stride, src + i * 210, 210);
+    for (size_t i = 0; i < nsb; i++) {
+      if (q6) {
+        memcpy(staged.data() + i * stride, src + i * 210, 210);
+      } else {  // f16 d | pad | nibbles
+        memcpy(staged.data() + i * stride, src + i * 18, 2);
+        memcpy(staged.data() + i * stride + 4, src + i * 18 + 2, 16);
+      }
+    }
     st = dev_malloc((void**)&w->d_raw, w->raw_bytes);
     if (st == RMI_OK && w->raw_bytes) {
       cudaError_t e = cudaMemcpyAsync(w->d_raw, staged.data(), w->raw_bytes, cudaMemcpyHostToDevice, ctx->stream);
@@ -446,7 +456,7 @@ extern "C" int32_t rmi_weight_fuse_vstack(rmi_ctx* ctx, const rmi_weight* a, con
   RMI_REQUIRE(w != nullptr, RMI_ERR_OOM, "host allocation failed");
   w->n_rows_a = a->n_rows;
   int32_t st = RMI_OK;
-  if (a->ggml_type == RMI_GGML_Q4_K || a->ggml_type == RMI_GGML_Q6_K) {
+  if (a->ggml_type != RMI_GGML_Q8_0) {
     w->raw_bytes = a->raw_bytes + b->raw_bytes;
     st = dev_malloc((void**)&w->d_raw, w->raw_bytes);
     if (st == RMI_OK) {

@@ -178,3 +178,50 @@ extern "C" int32_t rmi_dequantize_q6_k(rmi_ctx* ctx, const rmi_weight* w, float*
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   return RMI_OK;
 }
+
+// ---------------------------------------------------------------- Q4_0
+
+extern "C" int32_t rmi_matmul_q4_0_prequantized(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8, const float* scales,
+                                                size_t m, float* output, size_t row_begin, size_t row_end) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q4_0));
+  RMI_REQUIRE(row_begin <= row_end && row_end <= w->n_rows, RMI_ERR_BAD_SHAPE, "row range [%zu,%zu) outside [0,%zu)",
+              row_begin, row_end, w->n_rows);
+  if (m == 0 || row_begin == row_end) return RMI_OK;
+  RMI_REQUIRE(q8 && scales && output, RMI_ERR_BAD_HANDLE, "rmi_matmul_q4_0_prequantized: null buffer");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n = w->n_in, nr = row_end - row_begin;
+  uint8_t* dq;
+  float *ds, *dout;
+  RMI_TRY(rmi_scratch(ctx, 0, m * n, (void**)&dq));
+  RMI_TRY(rmi_scratch(ctx, 1, m * (n / 32) * 4, (void**)&ds));
+  RMI_TRY(rmi_scratch(ctx, 6, m * w->n_rows * 4, (void**)&dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(dq, q8, m * n, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(ds, scales, m * (n / 32) * 4, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_TRY(launch_q4_0_matmul(ctx, w, dq, ds, m, dout, row_begin, row_end));
+  RMI_CUDA_CHECK(cudaMemcpy2DAsync(output + row_begin, w->n_rows * 4, dout + row_begin, w->n_rows * 4, nr * 4, m,
+                                   cudaMemcpyDeviceToHost, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_matmul_q4_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q4_0));
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  RMI_REQUIRE(x && output, RMI_ERR_BAD_HANDLE, "rmi_matmul_q4_0: null buffer");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n = w->n_in;
+  uint8_t* dq;
+  float *dx, *ds, *dout;
+  RMI_TRY(rmi_scratch(ctx, 5, m * n * 4, (void**)&dx));
+  RMI_TRY(rmi_scratch(ctx, 0, m * n, (void**)&dq));
+  RMI_TRY(rmi_scratch(ctx, 1, m * (n / 32) * 4, (void**)&ds));
+  RMI_TRY(rmi_scratch(ctx, 6, m * w->n_rows * 4, (void**)&dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(dx, x, m * n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_TRY(launch_q8_quantize(ctx, dx, m, n, dq, ds, 0));
+  RMI_TRY(launch_q4_0_matmul(ctx, w, dq, ds, m, dout, 0, w->n_rows));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(output, dout, m * w->n_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  return RMI_OK;
+}

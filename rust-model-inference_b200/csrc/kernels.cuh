@@ -40,6 +40,11 @@ struct gemm_tc_args {
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
 int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w, bool gate_up_interleaved = false);
 
+// q4_0.cu
+size_t q4_0_device_block_bytes();
+int32_t launch_q4_0_matmul(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m, float* out,
+                           size_t row_begin, size_t row_end);
+
 // q6k.cu
 size_t q6k_device_block_bytes();
 int32_t launch_q6k_q8k_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* d8, const int8_t* qs, const int16_t* bsums,

@@ -83,6 +83,15 @@ def q4_k_weight(n: int, k: int, seed: int) -> np.ndarray:
     return out.reshape(-1)
 
 
+def q4_0_weight(n: int, k: int, seed: int) -> np.ndarray:
+    """A valid Q4_0 block stream [n, k/32, 18]: random nibbles, f16 d sized for roughly N(0,0.02) weights."""
+    rng = np.random.default_rng(seed)
+    out = rng.integers(0, 256, size=(n, k // 32, 18), dtype=np.uint8)
+    d = (rng.uniform(0.5, 1.5, size=(n, k // 32)) * (0.02 / 4.0)).astype(np.float16).view(np.uint16)
+    out[:, :, 0], out[:, :, 1] = d & 0xff, d >> 8
+    return out.reshape(-1)
+
+
 def q6_k_weight(n: int, k: int, seed: int) -> np.ndarray:
     """A valid Q6_K super-block stream [n, k/256, 210]: uniform random ql/qh bytes and int8 scales, f16 d sized so
     that decoded weights have roughly N(0,0.02) spread.  Parity is defined on decoding these bytes."""

@@ -536,3 +536,45 @@ def test_q6k_forward_partition_and_prequantized_path():
     xin = q8.reshape(-1).view(np.int8).astype(np.float64) * np.repeat(sc.reshape(-1).astype(np.float64), 32)
     ref = deq @ xin
     assert np.abs(pre - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+
+
+# ---------------------------------------------------------------- Q4_0 (src/ops/kernel/q4_0)
+
+def _q4_0_block(scale, lo, hi=None):
+    hi = lo if hi is None else hi
+    return np.concatenate([np.array([scale], np.float16).view(np.uint8), np.full(16, lo | (hi << 4), np.uint8)])
+
+
+def test_q4_0_reference_known_answers():
+    # q4_0/mod.rs:99-123: nibble 8 -> 0.0; nibble 9 with q8 = 1, scale 1 -> 32.0
+    q8, sc = np.full(32, 1, np.int8).view(np.uint8), np.ones(1, np.float32)
+    assert orc.q4_0_forward_prequantized(_q4_0_block(1.0, 8), q8, sc, 32, 1)[0] == 0.0
+    assert orc.q4_0_forward_prequantized(_q4_0_block(1.0, 9), q8, sc, 32, 1)[0] == 32.0
+
+
+def test_q4_0_reference_edge_blocks():
+    # the inputs of q4_0/avx2.rs:247-330 (zero / max / min activations, zero / max nibbles, linspace, alternating
+    # signs): the exact integer dot times d times scale
+    cases = [(0, np.zeros(32, np.int8)), (15, np.zeros(32, np.int8)), (0, np.full(32, 127, np.int8)),
+             (0, np.full(32, -128, np.int8)), (15, np.full(32, 127, np.int8)),
+             (5, np.linspace(-127, 127, 32).astype(np.int8)), (11, np.array([127 if i % 2 else -127 for i in range(32)], np.int8))]
+    for nib, q in cases:
+        w = _q4_0_block(0.5, nib, 15 - nib)
+        got = orc.q4_0_forward_prequantized(w, q.view(np.uint8), np.array([0.25], np.float32), 32, 1)[0]
+        dot = int(((nib - 8) * q[:16].astype(np.int64)).sum() + ((15 - nib - 8) * q[16:].astype(np.int64)).sum())
+        assert got == np.float32(np.float32(np.float32(dot) * np.float32(0.5)) * np.float32(0.25))
+
+
+def test_q4_0_partition_equals_whole():
+    rng = np.random.default_rng(5)
+    n_in, n_out = 256, 19
+    w = rng.integers(0, 256, n_out * (n_in // 32) * 18, dtype=np.uint8)
+    for r in range(n_out * (n_in // 32)):
+        w[r * 18:r * 18 + 2] = np.array([0.01 + 0.002 * (r % 5)], np.float16).view(np.uint8)
+    x = rng.standard_normal(n_in).astype(np.float32)
+    q8, sc = orc.quantize_q8_0(x, orc.SEM_AVX2)
+    whole = orc.q4_0_forward_prequantized(w, q8, sc, n_in, n_out)
+    parts = np.zeros(n_out, np.float32)
+    for ith in range(4):
+        orc.q4_0_forward_prequantized(w, q8, sc, n_in, n_out, ith, 4, output=parts)
+    assert np.array_equal(whole.view(np.uint32), parts.view(np.uint32))
