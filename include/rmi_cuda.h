@@ -224,6 +224,13 @@ int32_t rmi_matmul_q6_k_prequantized(rmi_ctx* ctx, const rmi_weight* w, const ui
 /* dequant_q6k_weight (src/ops/quant/mod.rs:571-583): all rows to f32 [n_rows, n_in], bit-exact. */
 int32_t rmi_dequantize_q6_k(rmi_ctx* ctx, const rmi_weight* w, float* output);
 
+/* ---- embedding lookup --------------------------------------------------------------------
+ * embedding_lookup (src/ops/embedding.rs:3-47) for a Q8_0, Q4_0 or Q6_K table uploaded with
+ * rmi_weight_upload: rows token_ids[0..m) dequantized to output [m, n_in], bit-exact.  Ids outside the
+ * table are rejected (RMI_ERR_BAD_SHAPE) instead of panicking on the slice as the reference does. */
+int32_t rmi_embedding_lookup(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* token_ids, size_t m,
+                             float* output);
+
 /* ---- GGUF -------------------------------------------------------------------------------
  * GGUFLoader::from_file / tensor_info / tensor_slice / metadata (src/core/loader.rs:211-395):
  * mmap + header, KV and tensor-table parse with the same range checks. */
@@ -251,6 +258,14 @@ int32_t rmi_qwen3_config(const rmi_qwen3* model, size_t* n_embd, size_t* n_layer
 int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size_t batch, size_t capacity,
                            rmi_session** out);
 int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s);
+/* Which of the reference's copies of the Qwen3 forward the session reproduces (both with the F16 KV cache):
+ * RMI_FORWARD_QWEN3_SESSION (default) = Qwen3Session::generate_inner (src/models/qwen3.rs:581-1158): f16 query,
+ *   scores buffer + softmax, first maximal index as the greedy token;
+ * RMI_FORWARD_APP_TEXT = the CLI's loop (src/app/text.rs:257-648): f32 query against the f16 keys
+ *   (dot_f16_f32), online soft-max with a running maximum starting at 0, vec_mad_f16_f32 / vec_scale_f32 on
+ *   the output row, and the last maximal index as the greedy token (:664-670). */
+enum { RMI_FORWARD_QWEN3_SESSION = 0, RMI_FORWARD_APP_TEXT = 1 };
+int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward);
 /* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): feeds the prompts one
  * position at a time, then generates n_gen tokens per sequence; the whole step runs on the
  * device.  prompts [batch, n_prompt] u32, out_tokens [batch, n_gen] u32.  EOS handling is

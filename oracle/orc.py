@@ -326,6 +326,15 @@ def dot_f16(a, b):
     return np.float32(lib().orc_dot_f16(_p(a), _p(b), C.c_size_t(a.size)))
 
 
+def embedding_lookup(w, token, n_embd, ggml_type):
+    """src/ops/embedding.rs:3-10 dispatch: 8 = Q8_0, 2 = Q4_0, 14 = Q6_K"""
+    w = _u8(w)
+    out = np.zeros(n_embd, np.float32)
+    fn = {8: lib().orc_embedding_lookup_q8_0, 2: lib().orc_embedding_lookup_q4_0, 14: lib().orc_embedding_lookup_q6_k}[ggml_type]
+    fn(_p(w), C.c_uint32(token), C.c_size_t(n_embd), _p(out))
+    return out
+
+
 def embedding_lookup_q8_0(w, token, n_embd):
     w = _u8(w)
     out = np.zeros(n_embd, np.float32)
@@ -377,15 +386,17 @@ class Qwen3:
         m.output = ptr("output.weight", np.uint8) if "output.weight" in tensors else m.token_embd
         self._m = m
 
-    def generate(self, prompt, n_gen, sem=SEM_AVX2, threads=1, want_trace=False, want_logits=False):
+    def generate(self, prompt, n_gen, sem=SEM_AVX2, threads=1, want_trace=False, want_logits=False, cli=False):
+        """cli=False: Qwen3Session (src/models/qwen3.rs); cli=True: the CLI's forward (src/app/text.rs:257-648)."""
         prompt = np.ascontiguousarray(prompt, np.uint32)
         out = np.zeros(max(n_gen, 1), np.uint32)
         steps = prompt.size + n_gen - 1
         trace = np.zeros((steps, self.cfg["n_embd"]), np.float32) if want_trace else None
         logits = np.zeros(self.cfg["vocab"], np.float32) if want_logits else None
-        n = lib().orc_qwen3_generate(C.byref(self._m), _p(prompt), C.c_size_t(prompt.size),
-                                     C.c_size_t(n_gen), _p(out), C.c_int(sem), C.c_int(threads),
-                                     _p(trace), _p(logits))
+        fn = lib().orc_qwen3_generate_cli if cli else lib().orc_qwen3_generate
+        fn.restype = C.c_int64
+        n = fn(C.byref(self._m), _p(prompt), C.c_size_t(prompt.size), C.c_size_t(n_gen), _p(out), C.c_int(sem),
+               C.c_int(threads), _p(trace), _p(logits))
         if n < 0:
             raise RuntimeError("Cannot sample non-finite logits")
         res = [out[:n].copy()]

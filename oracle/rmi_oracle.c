@@ -852,6 +852,20 @@ void orc_q4_0_forward_prequantized(const uint8_t* weight, const uint8_t* input_q
   }
 }
 
+void orc_embedding_lookup_q4_0(const uint8_t* weight, uint32_t token, size_t n_embd, float* out) {
+  size_t bpr = n_embd / 32;
+  const uint8_t* row = weight + (size_t)token * bpr * 18;
+  for (size_t b = 0; b < bpr; b++) {
+    const uint8_t* blk = row + b * 18;
+    float d = orc_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    for (int j = 0; j < 16; j++) {
+      float a = (float)(blk[2 + j] & 0x0F) - 8.0f, h = (float)(blk[2 + j] >> 4) - 8.0f;
+      out[b * 32 + j] = a * d;
+      out[b * 32 + j + 16] = h * d;
+    }
+  }
+}
+
 /* ------------------------------------------------------------------ Q6_K */
 
 /* the 6-bit value (0..63) at position e (0..255) of a super-block: mod.rs:542-555 */
@@ -1087,6 +1101,7 @@ typedef struct {
   uint16_t *k_cache, *v_cache;
   float* scores;       /* [nth][2*score_stride] (second half reused as f16 scratch) */
   size_t score_stride;
+  int sem;
 } attn_job;
 
 static void attn_job_fn(void* p, size_t ith, size_t nth) {
@@ -1123,6 +1138,95 @@ static void attn_job_fn(void* p, size_t ith, size_t nth) {
   }
 }
 
+/* src/ops/dot.rs:79-97, :241-276: f32 x f16 dot in the order of the selected instruction set */
+float orc_dot_f16_f32(const float* a, const uint16_t* b, size_t n, int sem) {
+  if (sem == ORC_SEM_AVX2) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8)
+      for (int l = 0; l < 8; l++) acc[l] = fmaf(a[i + l], orc_f16_to_f32(b[i + l]), acc[l]);
+    float sum = hsum8(acc);
+    for (; i < n; i++) {
+      float t = a[i] * orc_f16_to_f32(b[i]);
+      sum = sum + t;
+    }
+    return sum;
+  }
+  if (sem == ORC_SEM_NEON) {
+    float acc[4] = {0, 0, 0, 0};
+    size_t i = 0;
+    for (; i + 4 <= n; i += 4)
+      for (int l = 0; l < 4; l++) acc[l] = fmaf(a[i + l], orc_f16_to_f32(b[i + l]), acc[l]);
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]); /* vaddvq_f32 */
+    for (; i < n; i++) {
+      float t = a[i] * orc_f16_to_f32(b[i]);
+      sum = sum + t;
+    }
+    return sum;
+  }
+  float s = 0.0f;
+  for (size_t i = 0; i < n; i++) {
+    float t = a[i] * orc_f16_to_f32(b[i]);
+    s = s + t;
+  }
+  return s;
+}
+
+/* src/ops/dot.rs:278-345: y += v * f16(x): fused on AVX2 and NEON, separate multiply and add in the scalar path */
+void orc_vec_mad_f16_f32(float* y, const uint16_t* x, float v, size_t n, int sem) {
+  for (size_t i = 0; i < n; i++) {
+    if (sem == ORC_SEM_SCALAR) {
+      float t = v * orc_f16_to_f32(x[i]);
+      y[i] = y[i] + t;
+    } else {
+      y[i] = fmaf(v, orc_f16_to_f32(x[i]), y[i]);
+    }
+  }
+}
+
+static void attn_cli_job_fn(void* p, size_t ith, size_t nth) {
+  /* src/app/text.rs:414-453: online soft-max over the cached positions, f32 query, F16 cache */
+  attn_job* j = (attn_job*)p;
+  const orc_qwen3_config* c = &j->m->cfg;
+  size_t hd = c->head_dim, kv_stride = c->n_head_kv * hd;
+  size_t group = c->n_head / c->n_head_kv;
+  float kq_scale = 1.0f / sqrtf((float)hd);
+  size_t h0 = ith * c->n_head / nth, h1 = (ith + 1) * c->n_head / nth;
+  size_t layer_base = j->layer * j->capacity * kv_stride;
+  for (size_t head = h0; head < h1; head++) {
+    size_t kvh = head / group;
+    float* out = j->attn_out + head * hd;
+    float ms = 0.0f, s_sum = 0.0f;
+    for (size_t d = 0; d < hd; d++) out[d] = 0.0f;
+    for (size_t t = 0; t <= j->step; t++) {
+      const uint16_t* key = j->k_cache + layer_base + t * kv_stride + kvh * hd;
+      float score = orc_dot_f16_f32(j->q + head * hd, key, hd, j->sem) * kq_scale;
+      if (score > ms) {
+        float rescale = orc_expf(ms - score);
+        for (size_t d = 0; d < hd; d++) out[d] = out[d] * rescale;
+        s_sum = s_sum * rescale;
+        ms = score;
+      }
+      float vs = orc_expf(score - ms);
+      orc_vec_mad_f16_f32(out, j->v_cache + layer_base + t * kv_stride + kvh * hd, vs, hd, j->sem);
+      s_sum = s_sum + vs;
+    }
+    float inv_sum = 1.0f / s_sum;
+    for (size_t d = 0; d < hd; d++) out[d] = out[d] * inv_sum;
+  }
+}
+
+/* Iterator::max_by(partial_cmp): the last maximal index (src/app/text.rs:664-670); -1 on NaN (the reference panics) */
+int64_t orc_greedy_token_last(const float* logits, size_t n) {
+  if (n == 0) return 0;
+  size_t best = 0;
+  for (size_t i = 0; i < n; i++) {
+    if (isnan(logits[i])) return -1;
+    if (i > 0 && logits[i] >= logits[best]) best = i;
+  }
+  return (int64_t)best;
+}
+
 typedef struct {
   const orc_qwen3_layer* w;
   const uint8_t* q8;
@@ -1139,9 +1243,25 @@ static void qkv_job_fn(void* p, size_t ith, size_t nth) {
   gemv_rows(j->w->wv, j->q8, j->xs, j->v, j->n_embd, j->nk, ith, nth, j->sem);
 }
 
+static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                                      size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                                      float* logits_last, int cli);
+
 int64_t orc_qwen3_generate(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
                            size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
                            float* logits_last) {
+  return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last, 0);
+}
+
+int64_t orc_qwen3_generate_cli(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                               size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                               float* logits_last) {
+  return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last, 1);
+}
+
+static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                                      size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                                      float* logits_last, int cli) {
   /* src/models/qwen3.rs:440-550 (session buffers), :581-1158 (step loop) */
   const orc_qwen3_config* c = &model->cfg;
   size_t hd = c->head_dim, nq = c->n_head * hd, nk = c->n_head_kv * hd, n_attn = nq;
@@ -1190,8 +1310,8 @@ int64_t orc_qwen3_generate(const orc_qwen3_model* model, const uint32_t* prompt,
       size_t row = layer * capacity * kv_stride + step * kv_stride;
       orc_f32_slice_to_f16(k, k_cache + row, nk);
       orc_f32_slice_to_f16(v, v_cache + row, nk);
-      attn_job aj = {model, layer, step, capacity, q, attn_out, k_cache, v_cache, scores, score_stride};
-      orc_compute(threads, attn_job_fn, &aj);
+      attn_job aj = {model, layer, step, capacity, q, attn_out, k_cache, v_cache, scores, score_stride, sem};
+      orc_compute(threads, cli ? attn_cli_job_fn : attn_job_fn, &aj);
       quantize_any(attn_out, n_attn, q8, xs, sem);
       pooled_gemv(w->wo, q8, xs, proj, n_attn, c->n_embd, sem, threads);
       for (size_t i = 0; i < c->n_embd; i++) x[i] = x[i] + proj[i];
@@ -1210,7 +1330,7 @@ int64_t orc_qwen3_generate(const orc_qwen3_model* model, const uint32_t* prompt,
     quantize_any(normed, c->n_embd, q8, xs, sem);
     pooled_gemv(model->output, q8, xs, logits, c->n_embd, c->vocab, sem, threads);
     if (step + 1 < n_prompt) continue;
-    int64_t t = orc_greedy_token(logits, c->vocab);
+    int64_t t = cli ? orc_greedy_token_last(logits, c->vocab) : orc_greedy_token(logits, c->vocab);
     if (t < 0) {
       failed = 1;
       break;
@@ -1222,4 +1342,9 @@ int64_t orc_qwen3_generate(const orc_qwen3_model* model, const uint32_t* prompt,
   free(k_cache); free(v_cache); free(x); free(normed); free(q); free(k); free(v);
   free(attn_out); free(proj); free(gate); free(up); free(logits); free(q8); free(xs); free(scores);
   return failed ? -1 : n_out;
+}
+
+void orc_embedding_lookup_q6_k(const uint8_t* weight, uint32_t token, size_t n_embd, float* out) {
+  size_t row_bytes = n_embd / 256 * 210;
+  orc_dequantize_row_q6_k(weight + (size_t)token * row_bytes, row_bytes, out, n_embd);
 }

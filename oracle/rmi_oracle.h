@@ -167,6 +167,10 @@ void orc_softmax(float* x, size_t n);
 float orc_dot_f16(const uint16_t* a, const uint16_t* b, size_t n);
 /* src/ops/embedding.rs:12-22 */
 void orc_embedding_lookup_q8_0(const uint8_t* weight, uint32_t token, size_t n_embd, float* out);
+/* src/ops/embedding.rs:24-38: ((nibble as f32) - 8.0) * d */
+void orc_embedding_lookup_q4_0(const uint8_t* weight, uint32_t token, size_t n_embd, float* out);
+/* src/ops/embedding.rs:40-47: dequantize_row_q6_k of the token's row */
+void orc_embedding_lookup_q6_k(const uint8_t* weight, uint32_t token, size_t n_embd, float* out);
 /* src/models/qwen3.rs:172-191: first maximal index; returns -1 on empty or non-finite. */
 int64_t orc_greedy_token(const float* logits, size_t n);
 
@@ -205,6 +209,16 @@ typedef struct {
 int64_t orc_qwen3_generate(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
                            size_t n_gen, uint32_t* out_tokens, int sem, int threads,
                            float* trace, float* logits_last);
+
+/* The CLI's copy of the same forward (src/app/text.rs:257-648, F16 KV cache): f32 query against the f16 keys
+ * (dot_f16_f32), online soft-max with a running maximum that starts at 0, vec_mad_f16_f32 / vec_scale_f32 on
+ * the output row, and the last maximal index as the greedy token (:664-670).  Same arguments as above. */
+int64_t orc_qwen3_generate_cli(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                               size_t n_gen, uint32_t* out_tokens, int sem, int threads,
+                               float* trace, float* logits_last);
+float orc_dot_f16_f32(const float* a, const uint16_t* b, size_t n, int sem);
+void orc_vec_mad_f16_f32(float* y, const uint16_t* x, float v, size_t n, int sem);
+int64_t orc_greedy_token_last(const float* logits, size_t n);
 
 #ifdef __cplusplus
 }

@@ -30,6 +30,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "librmi_cuda.so")
 
 SEM_AVX2, SEM_NEON, SEM_SCALAR = 0, 1, 2
 GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+FORWARD_QWEN3_SESSION, FORWARD_APP_TEXT = 0, 1
 STATUS = {0: "RMI_OK", 1: "RMI_ERR_BAD_HANDLE", 2: "RMI_ERR_BAD_SHAPE", 3: "RMI_ERR_OOM", 4: "RMI_ERR_CUDA",
           5: "RMI_ERR_TIMEOUT", 6: "RMI_ERR_UNSUPPORTED", 7: "RMI_ERR_IO", 8: "RMI_ERR_FORMAT",
           9: "RMI_ERR_NONFINITE"}
@@ -388,6 +389,14 @@ def matmul_q4_0(weight: "QuantizedTensor", x) -> np.ndarray:
     return out
 
 
+def embedding_lookup(weight: "QuantizedTensor", token_ids) -> np.ndarray:
+    """embedding_lookup (src/ops/embedding.rs:3-47) for Q8_0 / Q4_0 / Q6_K tables: [len(token_ids), n_embd]."""
+    ids = np.ascontiguousarray(token_ids, np.uint32).reshape(-1)
+    out = np.zeros((ids.size, weight.n_in), np.float32)
+    _check(lib().rmi_embedding_lookup(weight._ctx.handle, weight._h, _p(ids), _sz(ids.size), _p(out)))
+    return out
+
+
 def dequantize_q6_k(weight: "QuantizedTensor") -> np.ndarray:
     """dequant_q6k_weight (src/ops/quant/mod.rs:571-583)"""
     out = np.zeros((weight.n_out, weight.n_in), np.float32)
@@ -729,11 +738,17 @@ class Qwen3Model:
 class Qwen3Session:
     """Qwen3Session (src/models/qwen3.rs:238-243, :440-550): F16 KV cache + scratch in HBM."""
 
-    def __init__(self, model: Qwen3Model, capacity: int, batch: int = 1):
+    def __init__(self, model: Qwen3Model, capacity: int, batch: int = 1, forward: int = 0):
         self.model, self._ctx, self.batch, self.capacity = model, model._ctx, batch, capacity
         self._h = C.c_void_p()
         _check(lib().rmi_session_create(self._ctx.handle, model._h, _sz(batch), _sz(capacity), C.byref(self._h)))
         self.prefill_ms = self.gen_ms = 0.0
+        if forward != FORWARD_QWEN3_SESSION:
+            self.set_forward(forward)
+
+    def set_forward(self, forward: int):
+        """FORWARD_QWEN3_SESSION (src/models/qwen3.rs) or FORWARD_APP_TEXT (the CLI's loop, src/app/text.rs:257-648)."""
+        _check(lib().rmi_session_set_forward(self._ctx.handle, self._h, C.c_int32(forward)))
 
     def generate(self, prompts, max_new_tokens: int) -> np.ndarray:
         prompts = np.ascontiguousarray(prompts, np.uint32).reshape(self.batch, -1)

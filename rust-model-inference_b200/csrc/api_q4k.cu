@@ -225,3 +225,30 @@ extern "C" int32_t rmi_matmul_q4_0(rmi_ctx* ctx, const rmi_weight* w, const floa
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   return RMI_OK;
 }
+
+// ---------------------------------------------------------------- embedding lookup
+
+extern "C" int32_t rmi_embedding_lookup(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* token_ids, size_t m,
+                                        float* output) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, -1));
+  RMI_REQUIRE(w->ggml_type == RMI_GGML_Q8_0 || w->ggml_type == RMI_GGML_Q4_0 || w->ggml_type == RMI_GGML_Q6_K,
+              RMI_ERR_UNSUPPORTED, "unsupported embedding type %d (Q8_0, Q4_0 and Q6_K are handled)", w->ggml_type);
+  if (m == 0 || w->n_in == 0) return RMI_OK;
+  RMI_REQUIRE(token_ids && output, RMI_ERR_BAD_HANDLE, "rmi_embedding_lookup: null buffer");
+  for (size_t i = 0; i < m; i++)
+    RMI_REQUIRE(token_ids[i] < w->n_rows, RMI_ERR_BAD_SHAPE, "token id %u at position %zu is outside the table of %zu rows",
+                token_ids[i], i, w->n_rows);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  uint32_t* dids;
+  float* dout;
+  RMI_TRY(rmi_scratch(ctx, 0, m * 4, (void**)&dids));
+  RMI_TRY(rmi_scratch(ctx, 6, m * w->n_in * 4, (void**)&dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(dids, token_ids, m * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (w->ggml_type == RMI_GGML_Q8_0) RMI_TRY(launch_q8_embedding(ctx, w, dids, m, dout));
+  else if (w->ggml_type == RMI_GGML_Q4_0) RMI_TRY(launch_q4_0_embedding(ctx, w, dids, m, dout));
+  else RMI_TRY(launch_q6k_embedding(ctx, w, dids, m, dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(output, dout, m * w->n_in * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  return RMI_OK;
+}

@@ -128,8 +128,27 @@ __global__ void rmsnorm_quant_kernel(float* __restrict__ x, const float* __restr
 // One head (hd values at src) by one warp: optional rms norm with weights nw (norm.rs:3-11), NeoX
 // rotation with the (cos, sin) pairs of `tab` (rope.rs:21-37), f16 result (RNE) at dst.
 __device__ __forceinline__ void norm_rope_head_f16(const float* __restrict__ src, const float* __restrict__ nw, float eps,
-                                                   const float* __restrict__ tab, size_t hd, int lane, uint16_t* dst) {
+                                                   const float* __restrict__ tab, size_t hd, int lane, uint16_t* dst,
+                                                   float* dst32 = nullptr) {
   const size_t half = hd / 2;
+  if (dst32) {  // f32 result (the CLI forward keeps the query in f32): plain loops
+    double part32 = 0.0;
+    for (size_t i = lane; i < hd; i += 32) part32 += (double)__fmul_rn(src[i], src[i]);
+    part32 = warp_sum_f64(part32);
+    float sc32 = 1.0f;
+    if (nw) sc32 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(part32 / (double)hd), eps)));
+    for (size_t i = lane; i < half; i += 32) {
+      float x0 = src[i], x1 = src[i + half];
+      if (nw) {
+        x0 = __fmul_rn(__fmul_rn(x0, sc32), nw[i]);
+        x1 = __fmul_rn(__fmul_rn(x1, sc32), nw[i + half]);
+      }
+      const float c = tab[2 * i], sn = tab[2 * i + 1];
+      dst32[i] = __fmaf_rn(x0, c, __fmul_rn(x1, -sn));
+      dst32[i + half] = __fmaf_rn(x0, sn, __fmul_rn(x1, c));
+    }
+    return;
+  }
   if (hd == 128) {
     // the usual head size: every global load (values, norm weights, cos/sin) is issued before the first use
     float xv[4], wv[4];
@@ -186,7 +205,7 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
                                        const float* __restrict__ rope, const int* __restrict__ d_step,
                                        uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
-                                       size_t capacity) {
+                                       size_t capacity, float* __restrict__ q32) {
   pdl_wait();
   pdl_launch_dependents();
   const size_t b = blockIdx.x, head = blockIdx.y;
@@ -202,7 +221,8 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
   }
   const bool is_q = head < n_head;
   uint16_t* dst = is_q ? q16 + b * nq + head * hd : k_cache + cache_row + (head - n_head) * hd;
-  norm_rope_head_f16(src, is_q ? q_norm : k_norm, eps, rope + (size_t)step * hd, hd, lane, dst);
+  norm_rope_head_f16(src, is_q ? q_norm : k_norm, eps, rope + (size_t)step * hd, hd, lane, dst,
+                     (is_q && q32) ? q32 + b * nq + head * hd : nullptr);
 }
 
 // Attention for one (sequence, kv head) by a thread-block cluster of CL CTAs; the `group`
@@ -401,25 +421,141 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The CLI forward's attention (src/app/text.rs:414-453) for one (sequence, head) per CTA: f32 query against the
+// f16 keys in the lane order of the selected instruction set (dot.rs:79-97, :241-276), an online soft-max whose
+// running maximum starts at 0, vec_mad_f16_f32 / vec_scale_f32 on the output row.  The recurrence over the
+// cached positions is evaluated exactly but in three parallel steps:
+//   scores (all t in parallel)  ->  running maximum, rescale factors exp(ms_{t-1} - s_t) (1 where the maximum
+//   does not move: multiplying by 1 is the identity) and weights exp(s_t - ms_t)  ->  per output element the
+//   sequential chain over t (out = out * r_t; out = fma(w_t, v_t, out)), 128 chains side by side.
+template <int SEM>
+__global__ void __launch_bounds__(256)
+    attention_online_kernel(const float* __restrict__ q32, const uint16_t* __restrict__ k_cache,
+                            const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
+                            size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                            float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  constexpr int LN = SEM == RMI_SEM_AVX2 ? 8 : (SEM == RMI_SEM_NEON ? 4 : 1);
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t head = blockIdx.x, b = blockIdx.y, kvh = head / (n_head / n_head_kv);
+  const size_t nq = n_head * hd, nk = n_head_kv * hd;
+  const int T = *d_step + 1;
+  float* sc = reinterpret_cast<float*>(smem);  // [capacity] scores, then weights
+  float* rs = sc + capacity;                   // [capacity] rescale factors
+  float* qs = rs + capacity;                   // [hd]
+  float* seg = qs + hd;                        // [256] segment maxima
+  const int tid = threadIdx.x, lane = tid & 31;
+  const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  for (size_t i = tid; i < hd; i += blockDim.x) qs[i] = q32[b * nq + head * hd + i];
+  __syncthreads();
+  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+
+  // scores: a group of LN threads per position, thread l takes elements l, l + LN, ... (one SIMD lane)
+  {
+    const int l = tid % LN, grp = tid / LN, n_grp = 256 / LN;
+    for (int t = grp; t < ((T + n_grp - 1) / n_grp) * n_grp; t += n_grp) {  // whole groups stay converged for the shuffles
+      float acc = 0.0f;
+      if (t < T) {
+        const uint16_t* kr = kbase + (size_t)t * nk;
+        for (size_t i = l; i < hd; i += LN) {
+          const float kv = f16_bits_to_f32(kr[i]);
+          acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qs[i], kv)) : __fmaf_rn(qs[i], kv, acc);
+        }
+      }
+      if (SEM == RMI_SEM_AVX2) {  // hsum_ps (dot.rs:447-456)
+        acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+      } else if (SEM == RMI_SEM_NEON) {  // vaddvq_f32
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+      }
+      if (l == 0 && t < T) sc[t] = __fmul_rn(acc, kq_scale);
+    }
+  }
+  __syncthreads();
+
+  // running maximum (starts at 0): thread i owns the positions [i*S, (i+1)*S)
+  const int S = (T + 255) / 256;
+  const int t_lo = tid * S, t_hi = min(T, t_lo + S);
+  float mx = 0.0f;
+  for (int t = t_lo; t < t_hi; t++) mx = fmaxf(mx, sc[t]);
+  seg[tid] = mx;
+  __syncthreads();
+  float ms = 0.0f;  // maximum over all earlier segments
+  for (int i = 0; i < tid; i++) ms = fmaxf(ms, seg[i]);
+  for (int t = t_lo; t < t_hi; t++) {
+    const float s = sc[t];
+    float r = 1.0f;
+    if (s > ms) {
+      r = exp_cr(__fsub_rn(ms, s));
+      ms = s;
+    }
+    rs[t] = r;
+    sc[t] = exp_cr(__fsub_rn(s, ms));
+  }
+  __syncthreads();
+
+  // the chains over t, one per output element; every thread also carries s_sum
+  if ((size_t)tid < hd) {
+    float out = 0.0f, s_sum = 0.0f;
+    const uint16_t* vp = vbase + tid;
+    for (int t0 = 0; t0 < T; t0 += 8) {
+      uint16_t vv[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) vv[u] = t0 + u < T ? vp[(size_t)(t0 + u) * nk] : (uint16_t)0;
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        if (t0 + u < T) {
+          const float r = rs[t0 + u], wgt = sc[t0 + u], vf = f16_bits_to_f32(vv[u]);
+          out = __fmul_rn(out, r);
+          s_sum = __fmul_rn(s_sum, r);
+          out = SEM == RMI_SEM_SCALAR ? __fadd_rn(out, __fmul_rn(wgt, vf)) : __fmaf_rn(wgt, vf, out);
+          s_sum = __fadd_rn(s_sum, wgt);
+        }
+      }
+    }
+    out = __fmul_rn(out, __fdiv_rn(1.0f, s_sum));
+    // this head's output, f32 (debug) and Q8_0 (one block per warp) for the Wo projection
+    const size_t o = b * nq + head * hd + tid;
+    if (attn_out) attn_out[o] = out;
+    float a = fabsf(out);
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sft));
+    float dsc, inv;
+    q8_scale_pair<SEM>(a, &dsc, &inv);
+    q8[o] = (uint8_t)(int8_t)q8_quant_value<SEM>(out, inv);
+    if (lane == 0) scales[o / 32] = f16_round_trip(dsc);
+  }
+}
+
 // Greedy token in two stages: ARGMAX_SLICES CTAs per sequence each reduce a slice of the logits to
 // (value, first index), then one CTA per sequence combines the slices.  Larger value wins, equal
 // values keep the lower index (first maximum); a non-finite logit raises *flag.
 constexpr int ARGMAX_SLICES = 64;
 
+// LAST = false: equal values keep the lower index (Qwen3Session, qwen3.rs:172-191); LAST = true: the higher
+// index (Iterator::max_by in the CLI forward, src/app/text.rs:664-670).  0xffffffff marks "no candidate yet".
+template <bool LAST>
 __device__ __forceinline__ void argmax_combine(float& best, uint32_t& bi, float ov, uint32_t oi) {
-  if (ov > best || (ov == best && oi < bi)) {
+  if (oi == 0xffffffffu) return;
+  const bool tie_wins = LAST ? oi > bi : oi < bi;
+  if (bi == 0xffffffffu || ov > best || (ov == best && tie_wins)) {
     best = ov;
     bi = oi;
   }
 }
 
+template <bool LAST>
 __device__ __forceinline__ void argmax_block_reduce(float& best, uint32_t& bi, float* s_v, uint32_t* s_i) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    argmax_combine(best, bi, ov, oi);
+    argmax_combine<LAST>(best, bi, ov, oi);
   }
   if (lane == 0) {
     s_v[warp] = best;
@@ -427,9 +563,10 @@ __device__ __forceinline__ void argmax_block_reduce(float& best, uint32_t& bi, f
   }
   __syncthreads();
   if (threadIdx.x == 0)
-    for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_combine(best, bi, s_v[w], s_i[w]);
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_combine<LAST>(best, bi, s_v[w], s_i[w]);
 }
 
+template <bool LAST>
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, size_t vocab, float* __restrict__ part_v,
                                       uint32_t* __restrict__ part_i, int* __restrict__ flag) {
   __shared__ float s_v[32];
@@ -446,16 +583,17 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, size_t v
   for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = l[i];
     if (!isfinite(v)) bad = true;
-    argmax_combine(best, bi, v, (uint32_t)i);
+    argmax_combine<LAST>(best, bi, v, (uint32_t)i);
   }
   if (bad) atomicExch(flag, 1);
-  argmax_block_reduce(best, bi, s_v, s_i);
+  argmax_block_reduce<LAST>(best, bi, s_v, s_i);
   if (threadIdx.x == 0) {
     part_v[b * ARGMAX_SLICES + slice] = best;
     part_i[b * ARGMAX_SLICES + slice] = bi;
   }
 }
 
+template <bool LAST>
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const uint32_t* __restrict__ part_i,
                                     const int* __restrict__ d_step, size_t n_prompt, uint32_t* __restrict__ gen,
                                     size_t n_gen) {
@@ -470,7 +608,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_v, const uint
     best = part_v[b * ARGMAX_SLICES + threadIdx.x];
     bi = part_i[b * ARGMAX_SLICES + threadIdx.x];
   }
-  argmax_block_reduce(best, bi, s_v, s_i);
+  argmax_block_reduce<LAST>(best, bi, s_v, s_i);
   if (threadIdx.x == 0) {
     const int step = *d_step;
     const size_t gi = (size_t)step + 1 - n_prompt;  // step >= n_prompt-1 when this kernel runs
@@ -525,10 +663,10 @@ int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const flo
 
 int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
                                const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
-                               uint16_t* k_cache, uint16_t* v_cache, size_t layer) {
+                               uint16_t* k_cache, uint16_t* v_cache, size_t layer, float* q32) {
   dim3 grid((unsigned)d.batch, (unsigned)(d.n_head + 2 * d.n_head_kv));
   if (rmi_launch(ctx, qk_norm_rope_kv_kernel, grid, dim3(32), 0, qkv, d.n_head, d.n_head_kv, d.hd, q_norm, k_norm, d.eps,
-                 rope, d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity) != cudaSuccess) {
+                 rope, d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity, q32) != cudaSuccess) {
     rmi_set_error("launch of qk_norm_rope_kv failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }
@@ -598,14 +736,38 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
   return rmi_post_launch(ctx, "attention");
 }
 
+// The CLI forward's attention: one CTA per (head, sequence).
+int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
+                                const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                                float* scales) {
+  RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "online attention needs head_dim %% 32 == 0 and <= 256");
+  const size_t smem = (2 * d.capacity + d.hd + 256) * 4;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_online_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? attention_online_kernel<RMI_SEM_NEON>
+                                                                   : attention_online_kernel<RMI_SEM_SCALAR>);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rmi_set_error("online attention needs %zu B of shared memory", smem);
+    return RMI_ERR_UNSUPPORTED;
+  }
+  if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head, (unsigned)d.batch), dim3(256), smem, q32, k_cache, v_cache, d_step,
+                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales) != cudaSuccess) {
+    rmi_set_error("launch of attention_online failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
+  return rmi_post_launch(ctx, "attention_online");
+}
+
 size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }
 
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
-                      size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i) {
+                      size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i, bool last_index) {
   dim3 grid(ARGMAX_SLICES, (unsigned)batch);
-  if (rmi_launch(ctx, argmax_partial_kernel, grid, dim3(256), 0, logits, vocab, part_v, part_i, flag) != cudaSuccess ||
-      rmi_launch(ctx, argmax_final_kernel, dim3((unsigned)batch), dim3(64), 0, part_v, part_i, d_step, n_prompt, gen,
-                 n_gen) != cudaSuccess) {
+  auto k1 = last_index ? argmax_partial_kernel<true> : argmax_partial_kernel<false>;
+  auto k2 = last_index ? argmax_final_kernel<true> : argmax_final_kernel<false>;
+  if (rmi_launch(ctx, k1, grid, dim3(256), 0, logits, vocab, part_v, part_i, flag) != cudaSuccess ||
+      rmi_launch(ctx, k2, dim3((unsigned)batch), dim3(64), 0, part_v, part_i, d_step, n_prompt, gen, n_gen) !=
+          cudaSuccess) {
     rmi_set_error("launch of argmax failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }

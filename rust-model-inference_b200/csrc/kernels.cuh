@@ -40,6 +40,11 @@ struct gemm_tc_args {
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
 int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w, bool gate_up_interleaved = false);
 
+// embedding lookups (q8_0.cu, q4_0.cu, q6k.cu): ids and out on the device
+int32_t launch_q8_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out);
+int32_t launch_q4_0_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out);
+int32_t launch_q6k_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out);
+
 // q4_0.cu
 size_t q4_0_device_block_bytes();
 int32_t launch_q4_0_matmul(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, size_t m, float* out,

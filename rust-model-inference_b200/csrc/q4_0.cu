@@ -54,7 +54,27 @@ __global__ void q4_0_matmul_kernel(const uint8_t* __restrict__ w, size_t blocks,
   if (lane == 0) out[t * n_rows + row] = sum;
 }
 
+// embedding_lookup_q4_0 (src/ops/embedding.rs:24-38): one CTA per requested row, ((nibble as f32) - 8) * d
+__global__ void q4_0_embedding_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint32_t* __restrict__ ids,
+                                      float* __restrict__ out) {
+  const uint8_t* row = w + (size_t)ids[blockIdx.x] * blocks * Q4_0_DEV_BYTES;
+  for (size_t i = threadIdx.x; i < blocks * 16; i += blockDim.x) {
+    const uint8_t* blk = row + (i / 16) * Q4_0_DEV_BYTES;
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk));
+    const uint8_t q = blk[4 + (i % 16)];
+    float* o = out + (size_t)blockIdx.x * blocks * 32 + (i / 16) * 32 + (i % 16);
+    o[0] = __fmul_rn(__fsub_rn((float)(q & 0x0F), 8.0f), d);
+    o[16] = __fmul_rn(__fsub_rn((float)(q >> 4), 8.0f), d);
+  }
+}
+
 }  // namespace
+
+int32_t launch_q4_0_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out) {
+  if (m == 0) return RMI_OK;
+  q4_0_embedding_kernel<<<(unsigned)m, 256, 0, ctx->stream>>>(w->d_raw, w->n_in / 32, ids, out);
+  return rmi_post_launch(ctx, "q4_0_embedding");
+}
 
 size_t q4_0_device_block_bytes() { return Q4_0_DEV_BYTES; }
 

@@ -158,6 +158,20 @@ __global__ void q6k_dequantize_kernel(const uint8_t* __restrict__ w, size_t n_su
   out[sb * 256 + e] = __fmul_rn(__fmul_rn(d, sc), (float)q);
 }
 
+// embedding_lookup_q6_k (src/ops/embedding.rs:40-47): dequantize_row_q6_k of the requested rows;
+// grid (super-blocks per row, rows), 256 threads = one value each
+__global__ void q6k_embedding_kernel(const uint8_t* __restrict__ w, size_t nb, const uint32_t* __restrict__ ids,
+                                     float* __restrict__ out) {
+  const uint8_t* blk = w + ((size_t)ids[blockIdx.y] * nb + blockIdx.x) * Q6K_DEV_BYTES;
+  const int e = threadIdx.x;
+  const int j = e / 128, r = e % 128, k = r / 32, l = r % 32;
+  const uint8_t qlb = blk[64 * j + 32 * (k & 1) + l], qhb = blk[128 + 32 * j + l];
+  const int q = (int)(((qlb >> (4 * (k >> 1))) & 0xF) | (((qhb >> (2 * k)) & 3) << 4)) - 32;
+  const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(blk + 208));
+  const float sc = (float)(int)(int8_t)blk[192 + e / 16];
+  out[((size_t)blockIdx.y * nb + blockIdx.x) * 256 + e] = __fmul_rn(__fmul_rn(d, sc), (float)q);
+}
+
 template <int MP>
 void q6k_q8k_launch(rmi_ctx* ctx, const rmi_weight* w, const float* d8, const int8_t* qs, const int16_t* bsums,
                     size_t groups, float* out, size_t row_begin, size_t row_end) {
@@ -172,6 +186,12 @@ void q6k_q8k_launch(rmi_ctx* ctx, const rmi_weight* w, const float* d8, const in
 }  // namespace
 
 size_t q6k_device_block_bytes() { return Q6K_DEV_BYTES; }
+
+int32_t launch_q6k_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out) {
+  if (m == 0) return RMI_OK;
+  q6k_embedding_kernel<<<dim3((unsigned)(w->n_in / 256), (unsigned)m), 256, 0, ctx->stream>>>(w->d_raw, w->n_in / 256, ids, out);
+  return rmi_post_launch(ctx, "q6k_embedding");
+}
 
 int32_t launch_q6k_q8k_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* d8, const int8_t* qs,
                               const int16_t* bsums, size_t m, float* out, size_t row_begin, size_t row_end) {

@@ -857,6 +857,25 @@ int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, con
   }
 }
 
+// embedding_lookup_q8_0 (src/ops/embedding.rs:12-22) from the tile16 layout: one CTA per requested row
+__global__ void q8_embedding_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint32_t* __restrict__ ids,
+                                    float* __restrict__ out) {
+  const uint32_t tok = ids[blockIdx.x];
+  const uint8_t* base = w + (size_t)(tok / 16) * blocks * Q8_REC_BYTES;
+  const int r = tok % 16;
+  for (size_t i = threadIdx.x; i < blocks * 32; i += blockDim.x) {
+    const uint8_t* rec = base + (i / 32) * Q8_REC_BYTES;
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(rec + 2 * r));
+    out[(size_t)blockIdx.x * blocks * 32 + i] = __fmul_rn(d, (float)(int8_t)rec[32 + 32 * r + (i & 31)]);
+  }
+}
+
+int32_t launch_q8_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out) {
+  if (m == 0) return RMI_OK;
+  q8_embedding_kernel<<<(unsigned)m, 256, 0, ctx->stream>>>(w->d_tile16, w->n_in / 32, ids, out);
+  return rmi_post_launch(ctx, "q8_embedding");
+}
+
 int32_t launch_q8_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, size_t m,
                              int32_t* sums) {
   size_t n = m * w->n_rows * (w->n_in / 32);

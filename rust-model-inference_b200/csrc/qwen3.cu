@@ -45,6 +45,8 @@ struct rmi_session {
   uint16_t *k_cache, *v_cache;
   float *x, *x2, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;  // x2: second residual buffer of the fused-norm path
   bool fused_norm;
+  int forward;    // RMI_FORWARD_*: which of the reference's copies of the forward this session reproduces
+  float* q32;     // f32 query after norm + rotation (CLI forward)
   bool fused_qk;  // q/k norm + rotation + cache write inside the attention kernel
   uint16_t* q16;
   uint8_t* q8;
@@ -270,6 +272,7 @@ static void free_session(rmi_session* s) {
   cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8);
   cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
   cudaFree(s->attn_dbg);
+  cudaFree(s->q32);
   cudaFree(s->argmax_v);
   cudaFree(s->argmax_i);
   s->magic = 0;
@@ -281,6 +284,20 @@ extern "C" int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s) {
   RMI_TRY(check_session(s));
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   free_session(s);
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  RMI_REQUIRE(forward == RMI_FORWARD_QWEN3_SESSION || forward == RMI_FORWARD_APP_TEXT, RMI_ERR_UNSUPPORTED,
+              "unknown forward variant %d", forward);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (s->forward != forward) {
+    RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+    drop_graphs(s);  // the captured step belongs to the other variant
+    s->forward = forward;
+  }
   return RMI_OK;
 }
 
@@ -340,6 +357,8 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->attn_dbg, batch * nq * 4);
   SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
+  s->forward = RMI_FORWARD_QWEN3_SESSION;
+  SESSION_ALLOC(s->q32, batch * nq * 4);
   s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
   s->fused_qk = batch <= 4 && getenv("RMI_NO_FUSED_QK") == nullptr;  // measured: a loss at batch 32
   for (const auto& l : model->layers) {
@@ -390,7 +409,12 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
       RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
       RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
     }
-    if (s->fused_qk) {
+    if (s->forward == RMI_FORWARD_APP_TEXT) {
+      // src/app/text.rs:257-648: f32 query, online soft-max over the F16 cache
+      RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
+                                     s->v_cache, l, s->q32));
+      RMI_TRY(launch_attention_online(ctx, d, s->q32, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+    } else if (s->fused_qk) {
       // q/k norm, rotation and the cache write happen inside the attention kernel
       RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs, s->qkv,
                                w.q_norm, w.k_norm, s->rope));
@@ -416,7 +440,8 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, m->output_norm, d.n_embd, d.eps, s->q8, s->xs, B));
   if (with_logits) {
     RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
-    RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i));
+    RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i,
+                          s->forward == RMI_FORWARD_APP_TEXT));
   }
   return launch_step_inc(ctx, s->d_step);
 }
@@ -511,7 +536,7 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
       passes++;
       rem %= p2;
     }
-  const uint64_t per_layer = 4 * passes + 1 + (s->fused_norm ? 0 : 2) + (s->fused_qk ? 0 : 1) + 1;
+  const uint64_t per_layer = 4 * passes + 1 + (s->fused_norm ? 0 : 2) + ((s->fused_qk && s->forward != RMI_FORWARD_APP_TEXT) ? 0 : 1) + 1;
   const uint64_t launches_per_body = 3 + d.n_layer * per_layer, launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;

@@ -47,6 +47,49 @@ def test_tiny_model_tokens_hidden_and_logits(rmi, ctx, tmp_path_factory, sem):
     model.free()
 
 
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
+def test_cli_forward_online_softmax_tokens_hidden_and_logits(rmi, ctx, tmp_path_factory, sem):
+    """The CLI's copy of the forward (src/app/text.rs:257-648): f32 query x f16 keys, online soft-max, last
+    maximal index.  Tokens identical, hidden state and logits bit-identical, in all three lane orders."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=2)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    prompt = rmi.synth.prompt_tokens(cfg["vocab"], 21, seed=9)
+    s = rmi.Qwen3Session(model, 21 + 30, forward=rmi.FORWARD_APP_TEXT)
+    got = s.generate(prompt, 30)[0]
+    ref, trace, logits = oracle.generate(prompt, 30, sem=sem, want_trace=True, want_logits=True, cli=True)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    assert np.array_equal(bits(s.logits()[0]), bits(logits))
+    # switching the same session back gives the Qwen3Session results again
+    s.set_forward(rmi.FORWARD_QWEN3_SESSION)
+    assert np.array_equal(s.generate(prompt, 30)[0], oracle.generate(prompt, 30, sem=sem))
+    with pytest.raises(rmi.RmiError):
+        s.set_forward(7)
+    s.free()
+    model.free()
+
+
+def test_cli_forward_qwen3_head_shape_long_context_and_batch(rmi, ctx, tmp_path_factory):
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_embd=1024, n_layer=2, n_head=16, n_head_kv=8, head_dim=128, n_ff=3072, vocab=2048)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=0)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    B = 3
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], 270, seed=20 + b) for b in range(B)])
+    s = rmi.Qwen3Session(model, 300, batch=B, forward=rmi.FORWARD_APP_TEXT)
+    got = s.generate(prompts, 30)
+    for b in range(B):
+        ref, trace = oracle.generate(prompts[b], 30, sem=orc.SEM_AVX2, threads=8, want_trace=True, cli=True)
+        assert np.array_equal(got[b], ref), b
+        assert np.array_equal(bits(s.hidden()[b]), bits(trace[-1])), b
+    s.free()
+    model.free()
+
+
 def test_batch_of_independent_sequences(rmi, ctx, tmp_path_factory):
     ctx.set_semantics(rmi.SEM_AVX2)
     cfg = tiny_cfg(n_layer=3)

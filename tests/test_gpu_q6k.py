@@ -92,3 +92,18 @@ def test_q6_k_rejects_neon_and_wrong_type(rmi, ctx):
     with pytest.raises(rmi.RmiError):
         rmi.dequantize_q6_k(q4)
     q4.free()
+
+
+@pytest.mark.parametrize("ggml,gen,row_bytes", [(8, "q8_0_weight", 34 / 32), (2, "q4_0_weight", 18 / 32), (14, "q6_k_weight", 210 / 256)])
+def test_embedding_lookup_bit_exact(rmi, ctx, ggml, gen, row_bytes):
+    """src/ops/embedding.rs:3-47 for the three table types."""
+    vocab, n_embd = 50, 512
+    wb = getattr(rmi.synth, gen)(vocab, n_embd, seed=ggml)
+    w = rmi.QuantizedTensor.from_bytes(wb, ggml, n_embd, vocab)
+    ids = [0, 49, 17, 17, 33]
+    got = rmi.embedding_lookup(w, ids)
+    ref = np.stack([orc.embedding_lookup(wb, t, n_embd, ggml) for t in ids])
+    assert np.array_equal(bits(got), bits(ref))
+    with pytest.raises(rmi.RmiError):
+        rmi.embedding_lookup(w, [50])
+    w.free()

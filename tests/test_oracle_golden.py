@@ -578,3 +578,27 @@ def test_q4_0_partition_equals_whole():
     for ith in range(4):
         orc.q4_0_forward_prequantized(w, q8, sc, n_in, n_out, ith, 4, output=parts)
     assert np.array_equal(whole.view(np.uint32), parts.view(np.uint32))
+
+
+# ---------------------------------------------------------------- the CLI forward's attention (src/app/text.rs)
+
+def test_cli_attention_helpers_and_tie_break():
+    lib = orc.lib()
+    lib.orc_dot_f16_f32.restype = orc.C.c_float
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(128).astype(np.float32)
+    b16 = rng.standard_normal(128).astype(np.float16)
+    ref = float((a.astype(np.float64) * b16.astype(np.float64)).sum())
+    for sem in (orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR):
+        got = lib.orc_dot_f16_f32(orc._p(a), orc._p(b16.view(np.uint16)), orc.C.c_size_t(128), orc.C.c_int(sem))
+        assert abs(got - ref) < 1e-4
+    # n = 5 exercises only the scalar tail in every variant: identical bits
+    tails = {sem: lib.orc_dot_f16_f32(orc._p(a), orc._p(b16.view(np.uint16)), orc.C.c_size_t(3), orc.C.c_int(sem))
+             for sem in (orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR)}
+    assert len({np.float32(v).tobytes() for v in tails.values()}) == 1
+    lib.orc_greedy_token_last.restype = orc.C.c_int64
+    x = np.array([1, 2, 2], np.float32)
+    assert lib.orc_greedy_token_last(orc._p(x), orc.C.c_size_t(3)) == 2       # max_by keeps the last maximum
+    assert orc.greedy_token(x) == 1                                           # Qwen3Session keeps the first
+    x[1] = np.nan
+    assert lib.orc_greedy_token_last(orc._p(x), orc.C.c_size_t(3)) == -1
