@@ -428,6 +428,8 @@ __global__ void __launch_bounds__(256)
 //   scores (all t in parallel)  ->  running maximum, rescale factors exp(ms_{t-1} - s_t) (1 where the maximum
 //   does not move: multiplying by 1 is the identity) and weights exp(s_t - ms_t)  ->  per output element the
 //   sequential chain over t (out = out * r_t; out = fma(w_t, v_t, out)), 128 chains side by side.
+constexpr int ATT_TILE = 64;
+
 template <int SEM>
 __global__ void __launch_bounds__(256)
     attention_online_kernel(const float* __restrict__ q32, const uint16_t* __restrict__ k_cache,
@@ -442,8 +444,9 @@ __global__ void __launch_bounds__(256)
   const size_t nq = n_head * hd, nk = n_head_kv * hd;
   const int T = *d_step + 1;
   float* sc = reinterpret_cast<float*>(smem);  // [capacity] scores, then weights
-  float* rs = sc + capacity;                   // [capacity] rescale factors
-  float* qs = rs + capacity;                   // [hd]
+  const size_t cap4 = (capacity + 3) & ~(size_t)3;
+  float* rs = sc + cap4;                       // [capacity] rescale factors
+  float* qs = rs + cap4;                       // [hd]
   float* seg = qs + hd;                        // [256] segment maxima
   const int tid = threadIdx.x, lane = tid & 31;
   const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
@@ -452,30 +455,51 @@ __global__ void __launch_bounds__(256)
   __syncthreads();
   const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
 
+  // K and V rows are staged through two shared-memory tiles of ATT_TILE positions with cp.async (the next
+  // tile is in flight while the current one is used): a chain must not wait on global memory every few steps
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(seg + 256);
+  const size_t row_bytes = hd * 2, tile_bytes = ATT_TILE * row_bytes, row16 = hd / 8;
+  const int n_tiles = (T + ATT_TILE - 1) / ATT_TILE;
+  auto stage = [&](const uint16_t* base, int tile, int buf) {
+    const int t0 = tile * ATT_TILE, nt = min(ATT_TILE, T - t0);
+    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
+    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
+      cp_async16(dst + (i / row16) * row_bytes + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
+    cp_async_commit();
+  };
+
   // scores: a group of LN threads per position, thread l takes elements l, l + LN, ... (one SIMD lane)
   {
     const int l = tid % LN, grp = tid / LN, n_grp = 256 / LN;
-    for (int t = grp; t < ((T + n_grp - 1) / n_grp) * n_grp; t += n_grp) {  // whole groups stay converged for the shuffles
-      float acc = 0.0f;
-      if (t < T) {
-        const uint16_t* kr = kbase + (size_t)t * nk;
-        for (size_t i = l; i < hd; i += LN) {
-          const float kv = f16_bits_to_f32(kr[i]);
-          acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qs[i], kv)) : __fmaf_rn(qs[i], kv, acc);
+    stage(kbase, 0, 0);
+    for (int tile = 0; tile < n_tiles; tile++) {
+      if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1);
+      if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+      __syncthreads();
+      const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
+      const int t0 = tile * ATT_TILE, nt = min(ATT_TILE, T - t0);
+      for (int tl = grp; tl < ((nt + n_grp - 1) / n_grp) * n_grp; tl += n_grp) {  // whole warps stay converged for the shuffles
+        float acc = 0.0f;
+        if (tl < nt) {
+          const uint16_t* kr = reinterpret_cast<const uint16_t*>(kt + (size_t)tl * row_bytes);
+          for (size_t i = l; i < hd; i += LN) {
+            const float kv = f16_bits_to_f32(kr[i]);
+            acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qs[i], kv)) : __fmaf_rn(qs[i], kv, acc);
+          }
         }
+        if (SEM == RMI_SEM_AVX2) {  // hsum_ps (dot.rs:447-456)
+          acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        } else if (SEM == RMI_SEM_NEON) {  // vaddvq_f32
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        }
+        if (l == 0 && tl < nt) sc[t0 + tl] = __fmul_rn(acc, kq_scale);
       }
-      if (SEM == RMI_SEM_AVX2) {  // hsum_ps (dot.rs:447-456)
-        acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-      } else if (SEM == RMI_SEM_NEON) {  // vaddvq_f32
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-      }
-      if (l == 0 && t < T) sc[t] = __fmul_rn(acc, kq_scale);
+      __syncthreads();  // the tile may be overwritten by the copy issued in the next iteration
     }
   }
-  __syncthreads();
 
   // running maximum (starts at 0): thread i owns the positions [i*S, (i+1)*S)
   const int S = (T + 255) / 256;
@@ -499,24 +523,26 @@ __global__ void __launch_bounds__(256)
   __syncthreads();
 
   // the chains over t, one per output element; every thread also carries s_sum
-  if ((size_t)tid < hd) {
-    float out = 0.0f, s_sum = 0.0f;
-    const uint16_t* vp = vbase + tid;
-    for (int t0 = 0; t0 < T; t0 += 8) {
-      uint16_t vv[8];
-#pragma unroll
-      for (int u = 0; u < 8; u++) vv[u] = t0 + u < T ? vp[(size_t)(t0 + u) * nk] : (uint16_t)0;
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        if (t0 + u < T) {
-          const float r = rs[t0 + u], wgt = sc[t0 + u], vf = f16_bits_to_f32(vv[u]);
-          out = __fmul_rn(out, r);
-          s_sum = __fmul_rn(s_sum, r);
-          out = SEM == RMI_SEM_SCALAR ? __fadd_rn(out, __fmul_rn(wgt, vf)) : __fmaf_rn(wgt, vf, out);
-          s_sum = __fadd_rn(s_sum, wgt);
-        }
+  float out = 0.0f, s_sum = 0.0f;
+  stage(vbase, 0, 0);
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    if ((size_t)tid < hd) {
+      const uint16_t* vt = reinterpret_cast<const uint16_t*>(tiles + (size_t)(tile & 1) * tile_bytes) + tid;
+      const int t0 = tile * ATT_TILE, nt = min(ATT_TILE, T - t0);
+      for (int tl = 0; tl < nt; tl++) {
+        const float r = rs[t0 + tl], wgt = sc[t0 + tl], vf = f16_bits_to_f32(vt[(size_t)tl * hd]);
+        out = __fmul_rn(out, r);
+        s_sum = __fmul_rn(s_sum, r);
+        out = SEM == RMI_SEM_SCALAR ? __fadd_rn(out, __fmul_rn(wgt, vf)) : __fmaf_rn(wgt, vf, out);
+        s_sum = __fadd_rn(s_sum, wgt);
       }
     }
+    __syncthreads();
+  }
+  if ((size_t)tid < hd) {
     out = __fmul_rn(out, __fdiv_rn(1.0f, s_sum));
     // this head's output, f32 (debug) and Q8_0 (one block per warp) for the Wo projection
     const size_t o = b * nq + head * hd + tid;
@@ -741,7 +767,7 @@ int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float*
                                 const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                                 float* scales) {
   RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "online attention needs head_dim %% 32 == 0 and <= 256");
-  const size_t smem = (2 * d.capacity + d.hd + 256) * 4;
+  const size_t smem = (2 * ((d.capacity + 3) & ~(size_t)3) + d.hd + 256) * 4 + 2 * ATT_TILE * d.hd * 2;
   auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_online_kernel<RMI_SEM_AVX2>
                                        : (ctx->sem == RMI_SEM_NEON ? attention_online_kernel<RMI_SEM_NEON>
                                                                    : attention_online_kernel<RMI_SEM_SCALAR>);
