@@ -428,6 +428,131 @@ __global__ void __launch_bounds__(256)
 //   scores (all t in parallel)  ->  running maximum, rescale factors exp(ms_{t-1} - s_t) (1 where the maximum
 //   does not move: multiplying by 1 is the identity) and weights exp(s_t - ms_t)  ->  per output element the
 //   sequential chain over t (out = out * r_t; out = fma(w_t, v_t, out)), 128 chains side by side.
+// Attention for one (sequence, kv head) by a single CTA: the variant for large batches, where there are enough
+// (sequence, kv head) pairs to fill the GPU and a cluster per pair only adds synchronisation.  Same arithmetic as
+// attention_kernel (sequential f64 dots of f16 values, soft-max with the sequential f32 sum, f16 probabilities,
+// sequential f64 P.V); K and V stream through two shared-memory tiles of SEQ_TILE positions.
+constexpr int SEQ_TILE = 128;
+
+template <int SEM>
+__global__ void __launch_bounds__(256)
+    attention_seq_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
+                         const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
+                         size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                         float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t kvh = blockIdx.x, b = blockIdx.y;
+  const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
+  const int T = *d_step + 1;
+  const size_t cs = (capacity + 7) & ~(size_t)7;  // keeps every array 16-byte aligned
+  float* sc = reinterpret_cast<float*>(smem);                       // [group][cs]
+  float* red = sc + group * cs;                                     // [group] (padded to 4)
+  uint16_t* qs = reinterpret_cast<uint16_t*>(red + ((group + 3) & ~(size_t)3));  // [group][hd]
+  uint16_t* p16 = qs + group * hd;                                  // [group][cs]
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(p16 + group * cs);    // 2 x SEQ_TILE x hd f16 (16-byte aligned: cs % 4 == 0, hd % 8 == 0)
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const size_t row_bytes = hd * 2, tile_bytes = SEQ_TILE * row_bytes, row16 = hd / 8;
+  const int n_tiles = (T + SEQ_TILE - 1) / SEQ_TILE;
+  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+  const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  auto stage = [&](const uint16_t* base, int tile, int buf) {
+    const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
+    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
+    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
+      cp_async16(dst + (i / row16) * row_bytes + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
+    cp_async_commit();
+  };
+  for (size_t i = tid; i < group * hd; i += blockDim.x) qs[i] = q16[b * nq + kvh * group * hd + i];
+  stage(kbase, 0, 0);
+  // scores[g][t] = f32(sum_f64 q*k) * kq_scale (dot.rs:115-118)
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
+    const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
+    for (size_t item = tid; item < (size_t)nt * group; item += blockDim.x) {
+      const size_t tl = item / group, g = item % group;
+      const uint32_t* kr = reinterpret_cast<const uint32_t*>(kt + tl * row_bytes);
+      const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + g * hd);
+      double s = 0.0;
+      for (size_t i = 0; i < hd / 2; i++) {
+        const uint32_t kk = kr[i], qq = qr[i];
+        s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq & 0xffff)), f16_bits_to_f32((uint16_t)(kk & 0xffff)));
+        s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq >> 16)), f16_bits_to_f32((uint16_t)(kk >> 16)));
+      }
+      sc[g * cs + t0 + tl] = __fmul_rn((float)s, kq_scale);
+    }
+    __syncthreads();
+  }
+  stage(vbase, 0, 0);  // the first V tile travels while the soft-max is evaluated
+  // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
+  for (size_t g = warp; g < group; g += nwarp) {
+    float mx = -INFINITY;
+    for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * cs + t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[g] = mx;
+  }
+  __syncthreads();
+  for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
+    const size_t g = i / T, t = i % T;
+    sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
+  }
+  __syncthreads();
+  for (size_t g = warp; g < group; g += nwarp) {
+    if (lane == 0) {
+      float sum = 0.0f;
+      const float* e = sc + g * cs;
+      for (int t = 0; t < T; t++) sum = __fadd_rn(sum, e[t]);
+      red[g] = sum;
+    }
+  }
+  __syncthreads();
+  for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
+    const size_t g = i / T, t = i % T;
+    float pv = sc[g * cs + t];
+    if (red[g] > 0.0f) pv = __fdiv_rn(pv, red[g]);
+    p16[g * cs + t] = f32_to_f16_bits(pv);
+  }
+  // out[g][d] = f32(sum_f64 over t of v[t][d] * p[g][t]), one output element per thread and pass
+  double accv[2] = {0.0, 0.0};
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    const uint16_t* vt = reinterpret_cast<const uint16_t*>(tiles + (size_t)(tile & 1) * tile_bytes);
+    const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
+    int pass = 0;
+    for (size_t o = tid; o < group * hd && pass < 2; o += blockDim.x, pass++) {
+      const size_t g = o / hd, dd = o % hd;
+      const uint16_t* pr = p16 + g * cs + t0;
+      double s = accv[pass];
+      for (int tl = 0; tl < nt; tl++)
+        s += (double)__fmul_rn(f16_bits_to_f32(vt[(size_t)tl * hd + dd]), f16_bits_to_f32(pr[tl]));
+      accv[pass] = s;
+    }
+    __syncthreads();
+  }
+  // f32 (debug) and Q8_0 blocks of this kv head's group*hd outputs: 32 consecutive outputs per warp and pass
+  const size_t out0 = kvh * group * hd;
+  int pass = 0;
+  for (size_t o = tid; o < group * hd && pass < 2; o += blockDim.x, pass++) {
+    const float v = (float)accv[pass];
+    if (attn_out) attn_out[b * nq + out0 + o] = v;
+    float a = fabsf(v);
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sft));
+    float dsc, inv;
+    q8_scale_pair<SEM>(a, &dsc, &inv);
+    q8[b * nq + out0 + o] = (uint8_t)(int8_t)q8_quant_value<SEM>(v, inv);
+    if (lane == 0) scales[(b * nq + out0 + o) / 32] = f16_round_trip(dsc);
+  }
+}
+
 constexpr int ATT_TILE = 64;
 
 template <int SEM>
@@ -760,6 +885,34 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
     return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "attention");
+}
+
+// One CTA per (kv head, sequence); needs group * head_dim <= 512 (two outputs per thread).
+bool attention_seq_eligible(const decode_dims& d) {
+  const size_t group = d.n_head / d.n_head_kv;
+  return group * d.hd <= 512 && (group * d.hd) % 32 == 0 && d.hd % 8 == 0 && d.batch * d.n_head_kv >= 128;
+}
+
+int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
+                             const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                             float* scales) {
+  const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
+  const size_t smem = group * cs * 4 + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 2 + group * cs * 2 +
+                      2 * (size_t)SEQ_TILE * d.hd * 2;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON>
+                                                                   : attention_seq_kernel<RMI_SEM_SCALAR>);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rmi_set_error("attention needs %zu B of shared memory", smem);
+    return RMI_ERR_UNSUPPORTED;
+  }
+  if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head_kv, (unsigned)d.batch), dim3(256), smem, q16, k_cache, v_cache, d_step,
+                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales) != cudaSuccess) {
+    rmi_set_error("launch of attention_seq failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
+  return rmi_post_launch(ctx, "attention_seq");
 }
 
 // The CLI forward's attention: one CTA per (head, sequence).

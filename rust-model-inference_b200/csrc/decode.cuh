@@ -20,6 +20,10 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
                          uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                          float* scales, const float* qkv = nullptr, const float* q_norm = nullptr,
                          const float* k_norm = nullptr, const float* rope = nullptr);
+bool attention_seq_eligible(const decode_dims& d);
+int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
+                             const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                             float* scales);
 int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
                                 const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                                 float* scales);

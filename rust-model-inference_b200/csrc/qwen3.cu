@@ -47,6 +47,7 @@ struct rmi_session {
   bool fused_norm;
   int forward;    // RMI_FORWARD_*: which of the reference's copies of the forward this session reproduces
   float* q32;     // f32 query after norm + rotation (CLI forward)
+  bool seq_attention;  // one CTA per (sequence, kv head) instead of a cluster: large batches
   bool fused_qk;  // q/k norm + rotation + cache write inside the attention kernel
   uint16_t* q16;
   uint8_t* q8;
@@ -358,6 +359,7 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   s->forward = RMI_FORWARD_QWEN3_SESSION;
+  s->seq_attention = attention_seq_eligible(s->d) && getenv("RMI_NO_SEQ_ATTENTION") == nullptr;
   SESSION_ALLOC(s->q32, batch * nq * 4);
   s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
   s->fused_qk = batch <= 4 && getenv("RMI_NO_FUSED_QK") == nullptr;  // measured: a loss at batch 32
@@ -421,7 +423,10 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
     } else {
       RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
                                      s->v_cache, l));
-      RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+      if (s->seq_attention)
+        RMI_TRY(launch_attention_seq(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+      else
+        RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
     }
     RMI_TRY(launch_q8_gemv(ctx, w.wo, s->q8, s->xs, B, s->proj, d.n_embd, 0, d.n_embd));
     if (s->fused_norm) {

@@ -90,6 +90,28 @@ def test_cli_forward_qwen3_head_shape_long_context_and_batch(rmi, ctx, tmp_path_
     model.free()
 
 
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON])
+def test_large_batch_uses_the_single_cta_attention_and_stays_bit_exact(rmi, ctx, tmp_path_factory, sem):
+    """batch * n_head_kv >= 128 switches to attention_seq_kernel (one CTA per sequence and kv head, K/V streamed
+    through shared-memory tiles); head_dim 128, 300 positions cross the tile and the 256-padding boundaries."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg(n_embd=512, n_layer=2, n_head=8, n_head_kv=4, head_dim=128, n_ff=1024, vocab=512)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=3)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    B, P, G = 33, 280, 12
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], P, seed=300 + b) for b in range(B)])
+    s = rmi.Qwen3Session(model, P + G, batch=B)
+    got = s.generate(prompts, G)
+    hidden = s.hidden()
+    for b in (0, 17, 32):
+        ref, trace = oracle.generate(prompts[b], G, sem=sem, threads=8, want_trace=True)
+        assert np.array_equal(got[b], ref), b
+        assert np.array_equal(bits(hidden[b]), bits(trace[-1])), b
+    s.free()
+    model.free()
+
+
 def test_batch_of_independent_sequences(rmi, ctx, tmp_path_factory):
     ctx.set_semantics(rmi.SEM_AVX2)
     cfg = tiny_cfg(n_layer=3)
