@@ -246,7 +246,7 @@ def test_error_paths(rmi, ctx):
         rmi.QuantizedTensor.from_bytes(np.zeros(33, np.uint8), rmi.GGML_Q8_0, 32, 1)   # short buffer
     assert e.value.status == 2
     with pytest.raises(rmi.RmiError) as e:
-        rmi.QuantizedTensor.from_bytes(np.zeros(64, np.uint8), 2, 32, 1)               # Q4_0 not on this path
+        rmi.QuantizedTensor.from_bytes(np.zeros(64, np.uint8), 3, 32, 1)               # Q4_1 is not on this path
     assert e.value.status == 6
     w = rmi.QuantizedTensor.from_bytes(make_q8_0_weight(4, 32, 0), rmi.GGML_Q8_0, 32, 4)
     with pytest.raises(rmi.RmiError) as e:
