@@ -351,7 +351,7 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=1)
     ap.add_argument("--decode-prompt", type=int, default=512)
     ap.add_argument("--decode-gen", type=int, default=128)
-    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv", "decode"],
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv", "decode", "q4k"],
                     help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -377,6 +377,22 @@ def main():
     ctx.set_stream(stream.cuda_stream)
     hbm_peak, bf16_peak, bf16_sus, peak_kind = measured_peaks()
     sm_count, l2_bytes, _ = ctx.device_info()
+    if args.workload == "q4k":
+        # BASELINE config 3 on its own: W [4096, 4096] Q4_K, M in {1, 8, 256}, both reference paths
+        if rank == 0:
+            res = q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=max(3, min(args.steps, 10)))
+            top = res["q8k_m1"]
+            print(json.dumps({"metric": "Q4_K x Q8_K matmul (4096x4096, M=1) achieved bandwidth", "value": top["gbs"],
+                              "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+                              "config": {"workload": "configs[2]: Q4_K 4096x4096, M in {1,8,256}, 16 weight copies > L2"},
+                              "roofline": {"bound": "hbm", "kernel": "q8k_quantize_kernel + q4k_q8k_matmul_kernel<AVX2,1>",
+                                           "achieved": top["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                                           "frac": top["gbs"] / hbm_peak, "peak_source": f"copy bandwidth, of {peak_kind}",
+                                           "traffic": None},
+                              "results": res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload == "decode":
         # BASELINE config 4 on its own: Qwen3-0.6B-architecture greedy decode (synthetic GGUF, seed 0)
         if rank == 0:

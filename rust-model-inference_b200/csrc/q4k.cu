@@ -84,18 +84,15 @@ __global__ void q8k_quantize_kernel(const float* __restrict__ x, size_t n_blocks
 // bytes: group j = l/8 (sub-blocks 2j and 2j+1) and AVX2 lane L = l%8.
 // The 16-byte header of a super-block as four words (d | dmin<<16, then the 12 scale bytes) and the 6-bit
 // unpack of mod.rs:25-33 on those words.
-__device__ __forceinline__ int hdr_byte(uint32_t w1, uint32_t w2, uint32_t w3, int b) {
-  const uint32_t w = b < 4 ? w1 : (b < 8 ? w2 : w3);
-  return (int)((w >> (8 * (b & 3))) & 0xffu);
-}
 __device__ __forceinline__ void scale_min_w(uint32_t w1, uint32_t w2, uint32_t w3, int j, int* sc, int* mn) {
-  if (j < 4) {
-    *sc = hdr_byte(w1, w2, w3, j) & 63;
-    *mn = hdr_byte(w1, w2, w3, j + 4) & 63;
-  } else {
-    *sc = (hdr_byte(w1, w2, w3, j + 4) & 0xF) | ((hdr_byte(w1, w2, w3, j - 4) >> 6) << 4);
-    *mn = (hdr_byte(w1, w2, w3, j + 4) >> 4) | ((hdr_byte(w1, w2, w3, j) >> 6) << 4);
-  }
+  // bytes 0..3 = w1, 4..7 = w2, 8..11 = w3.  j < 4: sc = q[j] & 63, mn = q[j+4] & 63;
+  // j >= 4: sc = (q[j+4] & 15) | ((q[j-4] >> 6) << 4), mn = (q[j+4] >> 4) | ((q[j] >> 6) << 4)
+  const int sh = 8 * (j & 3);
+  const uint32_t a = w1 >> sh, b = w2 >> sh, c = w3 >> sh;
+  const int sc_lo = (int)(a & 63u), mn_lo = (int)(b & 63u);
+  const int sc_hi = (int)((c & 0xFu) | ((a >> 2) & 0x30u)), mn_hi = (int)(((c >> 4) & 0xFu) | ((b >> 2) & 0x30u));
+  *sc = j < 4 ? sc_lo : sc_hi;
+  *mn = j < 4 ? mn_lo : mn_hi;
 }
 
 // Super-blocks of a row are fetched Q4K_U at a time: lane h loads the 16-byte header of super-block i0+h (one
