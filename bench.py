@@ -334,7 +334,7 @@ def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
                       "roofline": {"bound": "hbm", "kernel": "q8_gemv_short_kernel<AVX2,16,1>", "achieved": top["gbs"],
                                    "peak": hbm_peak, "unit": "GB/s", "frac": top["gbs"] / hbm_peak,
                                    "peak_source": f"copy bandwidth, of {peak_kind}",
-                                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch (profiles/q8_gemv_short_logits.md)
+                                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised under profiles/
                                    "traffic": 169306000},
                       "results": res}), flush=True)
 
@@ -487,8 +487,8 @@ def main():
                     "down_gemm_avg_us": (ms_d / n_d * 1e3) if n_d else None,
                     "down_gemm_tops": (OPS_DOWN / (ms_d / n_d / 1e3) / 1e12) if n_d else None,
                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
-                    # the committed ncu capture (profiles/gemm_tc_swiglu_ffn_m512.md); algorithmic bytes 7.65 MB
-                    "traffic": 7703552, "traffic_source": "ncu capture summarised in profiles/gemm_tc_swiglu_ffn_m512.md"}
+                    # the committed ncu capture summarised under profiles/; algorithmic bytes 7.65 MB
+                    "traffic": 7703552, "traffic_source": "ncu --set full capture of one launch, summary under profiles/"}
     else:   # AVX2 semantics keep every M on the CUDA-core kernels
         n_g, ms_g = ctx.prof_read("q8_gemv")
         roofline = {"bound": "tensor", "kernel": "q8_gemv_kernel (CUDA cores; AVX2 semantics)", "achieved": value,
