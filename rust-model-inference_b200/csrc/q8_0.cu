@@ -364,9 +364,19 @@ __global__ void __launch_bounds__(256)
   pdl_wait();
   pdl_launch_dependents();
   {
+    // four 16-byte loads in flight per thread: a rolled loop would wait for each one in turn
     const int4* src = reinterpret_cast<const int4*>(xq);
     int4* dst = reinterpret_cast<int4*>(xq_s);
-    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    const size_t n16 = MP * K / 16;
+    for (size_t i0 = threadIdx.x; i0 < n16; i0 += 4 * blockDim.x) {
+      int4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+        if (i0 + u * blockDim.x < n16) v[u] = __ldg(src + i0 + u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+        if (i0 + u * blockDim.x < n16) dst[i0 + u * blockDim.x] = v[u];
+    }
     for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
   }
   __syncthreads();
@@ -722,7 +732,10 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
     }
   }
   // fewer warps per CTA when the problem is small so that more SMs take part
+  // several activation rows per pass: fatter CTAs share one staging of the MP*K activation bytes between more
+  // weight rows (a 2-warp CTA would stage as many activation bytes as it reads weight bytes)
   int wpc = short_rows ? 8 : (warps * n_groups >= (size_t)ctx->sm_count * 8 ? 4 : 2);
+  if (MP >= 4 && wpc == 2) wpc = 4;
   dim3 grid((unsigned)((warps + wpc - 1) / wpc), (unsigned)n_groups);
   const int pr = rmi_prof_begin(ctx, "q8_gemv");
   cudaError_t le = rmi_launch(ctx, kern, grid, dim3(wpc * 32), smem, w->d_tile16, blocks, xq, xs, out, out_stride,
