@@ -23,7 +23,7 @@ import os
 
 import numpy as np
 
-from . import gguf, sharding, synth  # noqa: F401  (host utilities: synthetic checkpoints, rank partition)
+from . import gguf, load_plan, sharding, synth  # noqa: F401  (host utilities: synthetic checkpoints, rank partition, placement plans)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "librmi_cuda.so")

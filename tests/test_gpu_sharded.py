@@ -190,3 +190,43 @@ def test_two_ranks_on_two_gpus_store_into_each_other(rmi, tmp_path):
         outs.append(out)
     for p, out in zip(procs, outs):
         assert p.returncode == 0 and "RANK_OK" in out, out[-2000:]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_load_plan_row_ranges_uploaded_from_gguf_equal_the_full_matmul(rmi, tmp_path, world):
+    """A TensorSplit plan over `world` logical devices, every device's placements executed on this GPU through
+    the GGUF upload entry point: the per-device matmuls, laid side by side, are the unsharded matmul (oracle
+    checked), and the unsplit tensors come back as mapped bytes."""
+    from oracle import orc
+    lp, g = rmi.load_plan, rmi.gguf
+    ctx = rmi.context(0)
+    ctx.set_semantics(rmi.SEM_AVX2)
+    n, k, m = 96, 128, 5
+    w = rmi.synth.q8_0_weight_rows(n, k, seed=21, row_begin=0, row_end=n)
+    norm = rmi.synth.normal((k,), seed=22)
+    path = str(tmp_path / "plan.gguf")
+    g.write_gguf(path, [("general.architecture", g.T_STR, "qwen3"), ("qwen3.block_count", g.T_U32, 1)],
+                 [("token_embd.weight", [32], g.GGML_F32, np.zeros(128, np.uint8)),
+                  ("blk.0.attn_norm.weight", [k], g.GGML_F32, norm.view(np.uint8)),
+                  ("blk.0.ffn_up.weight", [k, n], g.GGML_Q8_0, w)])
+    idx = lp.PackageIndex.from_gguf_file(path)
+    devices = lp.balanced_devices(idx, world, slack_rows=1)
+    plan = lp.build_load_plan(idx, [0], devices, "cuda0", lp.TENSOR_SPLIT)
+    loader = rmi.GGUFLoader.from_file(path)
+    x = rmi.synth.normal((m, k), seed=23)
+    out = np.zeros((m, n), np.float32)
+    covered = 0
+    seen_norm = 0
+    for d in devices:
+        got = lp.execute_plan(rmi, loader, plan, idx, d.id, ctx=ctx)
+        for s, e, wt in got.get("blk.0.ffn_up.weight", []):
+            assert s == covered and wt.n_out == e - s and wt.n_in == k
+            out[:, s:e] = rmi.matmul_q8_0(wt, x)
+            covered = e
+        for s, e, raw in got.get("blk.0.attn_norm.weight", []):
+            assert (s, e) == (0, 1) and np.array_equal(np.asarray(raw).view(np.float32), norm)
+            seen_norm += 1
+    assert covered == n and seen_norm == 1
+    ref = orc.q8_forward_batched(w, x, k, n, orc.SEM_AVX2)
+    assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+    loader.close()
