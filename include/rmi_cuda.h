@@ -258,13 +258,18 @@ int32_t rmi_qwen3_config(const rmi_qwen3* model, size_t* n_embd, size_t* n_layer
 int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size_t batch, size_t capacity,
                            rmi_session** out);
 int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s);
-/* Which of the reference's copies of the Qwen3 forward the session reproduces (both with the F16 KV cache):
+/* Which of the reference's copies of the Qwen3 forward the session reproduces:
  * RMI_FORWARD_QWEN3_SESSION (default) = Qwen3Session::generate_inner (src/models/qwen3.rs:581-1158): f16 query,
  *   scores buffer + softmax, first maximal index as the greedy token;
  * RMI_FORWARD_APP_TEXT = the CLI's loop (src/app/text.rs:257-648): f32 query against the f16 keys
  *   (dot_f16_f32), online soft-max with a running maximum starting at 0, vec_mad_f16_f32 / vec_scale_f32 on
- *   the output row, and the last maximal index as the greedy token (:664-670). */
-enum { RMI_FORWARD_QWEN3_SESSION = 0, RMI_FORWARD_APP_TEXT = 1 };
+ *   the output row, and the last maximal index as the greedy token (:664-670);
+ * RMI_FORWARD_APP_TEXT_F32KV = the same loop with `--kv-cache f32` (src/app/text.rs:183-186, :393-405, :458-496):
+ *   K and V kept in f32, scores by dot_f32, soft-max over the scores padded to a multiple of 256, one dot_f32
+ *   over the positions per output element.  The F32 caches are allocated by this call on first use; sessions
+ *   longer than 512 positions are rejected (RMI_ERR_BAD_SHAPE; the reference's 512-entry value array panics).
+ * The first two use the F16 cache. */
+enum { RMI_FORWARD_QWEN3_SESSION = 0, RMI_FORWARD_APP_TEXT = 1, RMI_FORWARD_APP_TEXT_F32KV = 2 };
 int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward);
 /* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): feeds the prompts one
  * position at a time, then generates n_gen tokens per sequence; the whole step runs on the

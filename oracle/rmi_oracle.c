@@ -1102,6 +1102,7 @@ typedef struct {
   float* scores;       /* [nth][2*score_stride] (second half reused as f16 scratch) */
   size_t score_stride;
   int sem;
+  const float *k32, *v32; /* F32 KV caches of the CLI forward (NULL otherwise) */
 } attn_job;
 
 static void attn_job_fn(void* p, size_t ith, size_t nth) {
@@ -1216,6 +1217,72 @@ static void attn_cli_job_fn(void* p, size_t ith, size_t nth) {
   }
 }
 
+/* src/ops/dot.rs:8-76: f32 x f32 dot in the order of the selected instruction set */
+float orc_dot_f32(const float* a, const float* b, size_t n, int sem) {
+  if (sem == ORC_SEM_AVX2) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8)
+      for (int l = 0; l < 8; l++) acc[l] = fmaf(a[i + l], b[i + l], acc[l]);
+    float sum = hsum8(acc);
+    for (; i < n; i++) {
+      float t = a[i] * b[i];
+      sum = sum + t;
+    }
+    return sum;
+  }
+  if (sem == ORC_SEM_NEON) {
+    float acc[16] = {0}; /* acc0..acc3, four lanes each */
+    size_t i = 0;
+    for (; i + 16 <= n; i += 16)
+      for (int l = 0; l < 16; l++) acc[l] = fmaf(a[i + l], b[i + l], acc[l]);
+    float c[4];
+    for (int l = 0; l < 4; l++) {
+      float c0 = acc[l] + acc[8 + l], c1 = acc[4 + l] + acc[12 + l]; /* acc0+acc2, acc1+acc3 */
+      c[l] = c0 + c1;
+    }
+    float sum = (c[0] + c[1]) + (c[2] + c[3]); /* vaddvq_f32 */
+    for (; i < n; i++) {
+      float t = a[i] * b[i];
+      sum = sum + t;
+    }
+    return sum;
+  }
+  float s = 0.0f;
+  for (size_t i = 0; i < n; i++) {
+    float t = a[i] * b[i];
+    s = s + t;
+  }
+  return s;
+}
+
+static void attn_cli_f32_job_fn(void* p, size_t ith, size_t nth) {
+  /* src/app/text.rs:458-496: F32 cache: scores padded with -inf to a multiple of 256, soft-max, then one
+   * dot over the gathered column of V per output element (a 512-entry stack array in the reference) */
+  attn_job* j = (attn_job*)p;
+  const orc_qwen3_config* c = &j->m->cfg;
+  size_t hd = c->head_dim, kv_stride = c->n_head_kv * hd;
+  size_t group = c->n_head / c->n_head_kv;
+  float kq_scale = 1.0f / sqrtf((float)hd);
+  size_t h0 = ith * c->n_head / nth, h1 = (ith + 1) * c->n_head / nth;
+  size_t layer_base = j->layer * j->capacity * kv_stride;
+  size_t n_cached = j->step + 1, n_padded = (n_cached + 255) / 256 * 256;
+  float* scores = j->scores + ith * 2 * j->score_stride;
+  for (size_t head = h0; head < h1; head++) {
+    size_t kvh = head / group;
+    for (size_t t = 0; t < n_cached; t++)
+      scores[t] = orc_dot_f32(j->q + head * hd, j->k32 + layer_base + t * kv_stride + kvh * hd, hd, j->sem) * kq_scale;
+    for (size_t t = n_cached; t < n_padded; t++) scores[t] = -INFINITY;
+    orc_softmax(scores, n_padded);
+    float values[512];
+    memset(values, 0, sizeof(values));
+    for (size_t d = 0; d < hd; d++) {
+      for (size_t t = 0; t < n_cached; t++) values[t] = j->v32[layer_base + t * kv_stride + kvh * hd + d];
+      j->attn_out[head * hd + d] = orc_dot_f32(values, scores, n_padded, j->sem);
+    }
+  }
+}
+
 /* Iterator::max_by(partial_cmp): the last maximal index (src/app/text.rs:664-670); -1 on NaN (the reference panics) */
 int64_t orc_greedy_token_last(const float* logits, size_t n) {
   if (n == 0) return 0;
@@ -1259,6 +1326,15 @@ int64_t orc_qwen3_generate_cli(const orc_qwen3_model* model, const uint32_t* pro
   return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last, 1);
 }
 
+/* the same loop with `--kv-cache f32` (src/app/text.rs:183-186, :393-405, :458-496); -2 when the context is
+ * longer than the 512 positions the reference's stack array holds (it panics there) */
+int64_t orc_qwen3_generate_cli_f32kv(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                                     size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                                     float* logits_last) {
+  if ((n_prompt + n_gen + 255) / 256 * 256 > 512) return -2;
+  return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last, 2);
+}
+
 static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
                                       size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
                                       float* logits_last, int cli) {
@@ -1288,6 +1364,8 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
   uint8_t* q8 = (uint8_t*)calloc(max_n_in, 1);
   float* xs = (float*)calloc(max_n_in / 32 + 1, 4);
   float* scores = (float*)calloc((size_t)threads * 2 * score_stride, 4);
+  float* k32 = cli == 2 ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
+  float* v32 = cli == 2 ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
 
   int64_t n_out = 0;
   int failed = 0;
@@ -1308,10 +1386,15 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
       orc_rope_neox(q, nq, pos, hd, c->freq_base);
       orc_rope_neox(k, nk, pos, hd, c->freq_base);
       size_t row = layer * capacity * kv_stride + step * kv_stride;
-      orc_f32_slice_to_f16(k, k_cache + row, nk);
-      orc_f32_slice_to_f16(v, v_cache + row, nk);
-      attn_job aj = {model, layer, step, capacity, q, attn_out, k_cache, v_cache, scores, score_stride, sem};
-      orc_compute(threads, cli ? attn_cli_job_fn : attn_job_fn, &aj);
+      if (cli == 2) {
+        memcpy(k32 + row, k, 4 * nk);
+        memcpy(v32 + row, v, 4 * nk);
+      } else {
+        orc_f32_slice_to_f16(k, k_cache + row, nk);
+        orc_f32_slice_to_f16(v, v_cache + row, nk);
+      }
+      attn_job aj = {model, layer, step, capacity, q, attn_out, k_cache, v_cache, scores, score_stride, sem, k32, v32};
+      orc_compute(threads, cli == 2 ? attn_cli_f32_job_fn : (cli ? attn_cli_job_fn : attn_job_fn), &aj);
       quantize_any(attn_out, n_attn, q8, xs, sem);
       pooled_gemv(w->wo, q8, xs, proj, n_attn, c->n_embd, sem, threads);
       for (size_t i = 0; i < c->n_embd; i++) x[i] = x[i] + proj[i];
@@ -1341,6 +1424,7 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
   if (logits_last) memcpy(logits_last, logits, 4 * c->vocab);
   free(k_cache); free(v_cache); free(x); free(normed); free(q); free(k); free(v);
   free(attn_out); free(proj); free(gate); free(up); free(logits); free(q8); free(xs); free(scores);
+  free(k32); free(v32);
   return failed ? -1 : n_out;
 }
 

@@ -205,7 +205,8 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
                                        const float* __restrict__ rope, const int* __restrict__ d_step,
                                        uint16_t* __restrict__ q16, uint16_t* __restrict__ k_cache,
                                        uint16_t* __restrict__ v_cache, size_t layer, size_t n_layer,
-                                       size_t capacity, float* __restrict__ q32) {
+                                       size_t capacity, float* __restrict__ q32, float* __restrict__ k32_cache,
+                                       float* __restrict__ v32_cache) {
   pdl_wait();
   pdl_launch_dependents();
   const size_t b = blockIdx.x, head = blockIdx.y;
@@ -214,9 +215,18 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, size_t n_h
   const size_t nq = n_head * hd, nk = n_head_kv * hd;
   const float* src = qkv + b * (nq + 2 * nk) + head * hd;
   const size_t cache_row = ((b * n_layer + layer) * capacity + (size_t)step) * nk;
-  if (head >= n_head + n_head_kv) {  // V: straight f16 conversion
+  if (head >= n_head + n_head_kv) {  // V: straight f16 conversion, or an f32 copy (text.rs:393-405)
     const size_t kvh = head - n_head - n_head_kv;
+    if (v32_cache) {
+      for (size_t i = lane; i < hd; i += 32) v32_cache[cache_row + kvh * hd + i] = src[i];
+      return;
+    }
     for (size_t i = lane; i < hd; i += 32) v_cache[cache_row + kvh * hd + i] = f32_to_f16_bits(src[i]);
+    return;
+  }
+  if (k32_cache && head >= n_head) {  // K kept in f32
+    norm_rope_head_f16(src, k_norm, eps, rope + (size_t)step * hd, hd, lane, nullptr,
+                       k32_cache + cache_row + (head - n_head) * hd);
     return;
   }
   const bool is_q = head < n_head;
@@ -682,6 +692,142 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The CLI forward with an F32 cache (src/app/text.rs:458-496), one CTA per (head, sequence): scores =
+// dot_f32(q, k_t) * scale in the lane order of the selected instruction set (src/ops/dot.rs:8-76: eight AVX2
+// lanes; four NEON accumulators of four lanes, combined (acc0+acc2)+(acc1+acc3) then pairwise; one scalar chain
+// with separate multiply and add), the soft-max of src/ops/attention.rs:28-38 over the scores (the -inf padding to
+// a multiple of 256 adds exact zeros), then out[d] = dot_f32(V[:, d], weights) in the same lane order over the
+// positions: chain l of element d takes the positions l, l + LN, ...; the chains of one element are combined
+// through shared memory.  Padded positions multiply a zero by a zero weight and leave every chain unchanged.
+template <int SEM>
+__global__ void __launch_bounds__(256)
+    attention_f32kv_kernel(const float* __restrict__ q32, const float* __restrict__ k_cache,
+                           const float* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
+                           size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                           float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  constexpr int LN = SEM == RMI_SEM_AVX2 ? 8 : (SEM == RMI_SEM_NEON ? 16 : 1);
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t head = blockIdx.x, b = blockIdx.y, kvh = head / (n_head / n_head_kv);
+  const size_t nq = n_head * hd, nk = n_head_kv * hd;
+  const int T = *d_step + 1;
+  const size_t cap4 = (capacity + 3) & ~(size_t)3;
+  float* sc = reinterpret_cast<float*>(smem);  // [capacity] scores, then weights
+  float* qs = sc + cap4;                       // [hd]
+  float* part = qs + hd;                       // [LN][hd] chain results
+  float* red = part + (size_t)LN * hd;         // [32]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const float* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  for (size_t i = tid; i < hd; i += blockDim.x) qs[i] = q32[b * nq + head * hd + i];
+  __syncthreads();
+  const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+
+  {  // scores: LN threads per position, thread l takes elements l, l + LN, ... (one SIMD lane)
+    const int l = tid % LN, grp = tid / LN, n_grp = 256 / LN;
+    for (int t = grp; t < ((T + n_grp - 1) / n_grp) * n_grp; t += n_grp) {  // whole warps stay converged
+      float acc = 0.0f;
+      if (t < T) {
+        const float* kr = kbase + (size_t)t * nk;
+        for (size_t i0 = l; i0 < hd; i0 += 4 * LN) {  // the loads of four steps are issued together
+          float kv[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) kv[u] = i0 + (size_t)u * LN < hd ? __ldg(kr + i0 + (size_t)u * LN) : 0.0f;
+#pragma unroll
+          for (int u = 0; u < 4; u++)
+            if (i0 + (size_t)u * LN < hd) {
+              const float qv = qs[i0 + (size_t)u * LN];
+              acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qv, kv[u])) : __fmaf_rn(qv, kv[u], acc);
+            }
+        }
+      }
+      if (SEM == RMI_SEM_AVX2) {  // hsum_ps
+        acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+      } else if (SEM == RMI_SEM_NEON) {  // (acc0 + acc2) + (acc1 + acc3), then vaddvq_f32
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+      }
+      if (l == 0 && t < T) sc[t] = __fmul_rn(acc, kq_scale);
+    }
+  }
+  __syncthreads();
+
+  // soft-max: maximum, exp, sequential f32 sum, divide
+  float mx = -INFINITY;
+  for (int t = tid; t < T; t += 256) mx = fmaxf(mx, sc[t]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  for (int t = tid; t < T; t += 256) sc[t] = exp_cr(__fsub_rn(sc[t], mx));
+  __syncthreads();
+  if (tid == 0) {
+    float sum = 0.0f;
+    for (int t = 0; t < T; t++) sum = __fadd_rn(sum, sc[t]);
+    red[16] = sum;
+  }
+  __syncthreads();
+  const float sum = red[16];
+  if (sum > 0.0f)
+    for (int t = tid; t < T; t += 256) sc[t] = __fdiv_rn(sc[t], sum);
+  __syncthreads();
+
+  // chains: item = l * hd + d, so a warp reads 32 consecutive elements of one V row
+  for (size_t item = tid; item < (size_t)LN * hd; item += 256) {
+    const size_t l = item / hd, d = item % hd;
+    const float* vc = vbase + d;
+    float acc = 0.0f;
+    for (int t0 = (int)l; t0 < T; t0 += 4 * LN) {
+      float vv[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) vv[u] = t0 + u * LN < T ? __ldg(vc + (size_t)(t0 + u * LN) * nk) : 0.0f;
+#pragma unroll
+      for (int u = 0; u < 4; u++)
+        if (t0 + u * LN < T) {
+          const float wgt = sc[t0 + u * LN];
+          acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(vv[u], wgt)) : __fmaf_rn(vv[u], wgt, acc);
+        }
+    }
+    part[item] = acc;
+  }
+  __syncthreads();
+  if ((size_t)tid < hd) {
+    float out;
+    const float* p = part + tid;
+    if (SEM == RMI_SEM_AVX2) {
+      const float s0 = __fadd_rn(p[4 * hd], p[0]), s1 = __fadd_rn(p[5 * hd], p[hd]);
+      const float s2 = __fadd_rn(p[6 * hd], p[2 * hd]), s3 = __fadd_rn(p[7 * hd], p[3 * hd]);
+      out = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
+    } else if (SEM == RMI_SEM_NEON) {
+      float c[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        c[i] = __fadd_rn(__fadd_rn(p[(size_t)i * hd], p[(size_t)(8 + i) * hd]),
+                         __fadd_rn(p[(size_t)(4 + i) * hd], p[(size_t)(12 + i) * hd]));
+      out = __fadd_rn(__fadd_rn(c[0], c[1]), __fadd_rn(c[2], c[3]));
+    } else {
+      out = p[0];
+    }
+    const size_t o = b * nq + head * hd + tid;
+    if (attn_out) attn_out[o] = out;
+    float a = fabsf(out);
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sft));
+    float dsc, inv;
+    q8_scale_pair<SEM>(a, &dsc, &inv);
+    q8[o] = (uint8_t)(int8_t)q8_quant_value<SEM>(out, inv);
+    if (lane == 0) scales[o / 32] = f16_round_trip(dsc);
+  }
+}
+
 // Greedy token in two stages: ARGMAX_SLICES CTAs per sequence each reduce a slice of the logits to
 // (value, first index), then one CTA per sequence combines the slices.  Larger value wins, equal
 // values keep the lower index (first maximum); a non-finite logit raises *flag.
@@ -814,10 +960,12 @@ int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const flo
 
 int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
                                const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
-                               uint16_t* k_cache, uint16_t* v_cache, size_t layer, float* q32) {
+                               uint16_t* k_cache, uint16_t* v_cache, size_t layer, float* q32, float* k32_cache,
+                               float* v32_cache) {
   dim3 grid((unsigned)d.batch, (unsigned)(d.n_head + 2 * d.n_head_kv));
   if (rmi_launch(ctx, qk_norm_rope_kv_kernel, grid, dim3(32), 0, qkv, d.n_head, d.n_head_kv, d.hd, q_norm, k_norm, d.eps,
-                 rope, d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity, q32) != cudaSuccess) {
+                 rope, d_step, q16, k_cache, v_cache, layer, d.n_layer, d.capacity, q32, k32_cache, v32_cache) !=
+      cudaSuccess) {
     rmi_set_error("launch of qk_norm_rope_kv failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }
@@ -935,6 +1083,27 @@ int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float*
     return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "attention_online");
+}
+
+int32_t launch_attention_f32kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const float* k_cache,
+                               const float* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                               float* scales) {
+  RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "F32-cache attention needs head_dim %% 32 == 0 and <= 256");
+  const size_t smem = (((d.capacity + 3) & ~(size_t)3) + d.hd + 16 * d.hd + 32) * 4;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_f32kv_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? attention_f32kv_kernel<RMI_SEM_NEON>
+                                                                   : attention_f32kv_kernel<RMI_SEM_SCALAR>);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    rmi_set_error("F32-cache attention needs %zu B of shared memory", smem);
+    return RMI_ERR_UNSUPPORTED;
+  }
+  if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head, (unsigned)d.batch), dim3(256), smem, q32, k_cache, v_cache, d_step,
+                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales) != cudaSuccess) {
+    rmi_set_error("launch of attention_f32kv failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return RMI_ERR_CUDA;
+  }
+  return rmi_post_launch(ctx, "attention_f32kv");
 }
 
 size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }

@@ -14,7 +14,8 @@ int32_t launch_rmsnorm_quant(rmi_ctx* ctx, float* x, const float* add, const flo
                              uint8_t* q8, float* scales, size_t batch);
 int32_t launch_qk_norm_rope_kv(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
                                const float* k_norm, const float* rope, const int* d_step, uint16_t* q16,
-                               uint16_t* k_cache, uint16_t* v_cache, size_t layer, float* q32 = nullptr);
+                               uint16_t* k_cache, uint16_t* v_cache, size_t layer, float* q32 = nullptr,
+                               float* k32_cache = nullptr, float* v32_cache = nullptr);
 size_t attention_smem_bytes(const decode_dims& d);
 int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, uint16_t* k_cache,
                          uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
@@ -27,6 +28,9 @@ int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t*
 int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
                                 const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                                 float* scales);
+int32_t launch_attention_f32kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const float* k_cache,
+                               const float* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                               float* scales);
 size_t argmax_scratch_floats(size_t batch);
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
                       size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i, bool last_index = false);

@@ -47,6 +47,7 @@ struct rmi_session {
   bool fused_norm;
   int forward;    // RMI_FORWARD_*: which of the reference's copies of the forward this session reproduces
   float* q32;     // f32 query after norm + rotation (CLI forward)
+  float *k32_cache, *v32_cache;  // F32 caches of the CLI forward with `--kv-cache f32`; allocated on first use
   bool seq_attention;  // one CTA per (sequence, kv head) instead of a cluster: large batches
   bool fused_qk;  // q/k norm + rotation + cache write inside the attention kernel
   uint16_t* q16;
@@ -274,6 +275,8 @@ static void free_session(rmi_session* s) {
   cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
   cudaFree(s->attn_dbg);
   cudaFree(s->q32);
+  cudaFree(s->k32_cache);
+  cudaFree(s->v32_cache);
   cudaFree(s->argmax_v);
   cudaFree(s->argmax_i);
   s->magic = 0;
@@ -288,17 +291,36 @@ extern "C" int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s) {
   return RMI_OK;
 }
 
+static bool is_cli_forward(int forward) { return forward != RMI_FORWARD_QWEN3_SESSION; }
+
 extern "C" int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward) {
   RMI_TRY(rmi_check_ctx(ctx));
   RMI_TRY(check_session(s));
-  RMI_REQUIRE(forward == RMI_FORWARD_QWEN3_SESSION || forward == RMI_FORWARD_APP_TEXT, RMI_ERR_UNSUPPORTED,
-              "unknown forward variant %d", forward);
+  RMI_REQUIRE(forward == RMI_FORWARD_QWEN3_SESSION || forward == RMI_FORWARD_APP_TEXT ||
+                  forward == RMI_FORWARD_APP_TEXT_F32KV,
+              RMI_ERR_UNSUPPORTED, "unknown forward variant %d", forward);
   std::lock_guard<std::mutex> lock(ctx->mu);
-  if (s->forward != forward) {
-    RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
-    drop_graphs(s);  // the captured step belongs to the other variant
-    s->forward = forward;
+  if (s->forward == forward) return RMI_OK;
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  if (forward == RMI_FORWARD_APP_TEXT_F32KV && !s->k32_cache) {
+    // the reference gathers a column of V into a 512-entry array (src/app/text.rs:478) and panics beyond it
+    RMI_REQUIRE((s->d.capacity + 255) / 256 * 256 <= 512, RMI_ERR_BAD_SHAPE,
+                "the F32 cache holds at most 512 positions, session capacity is %zu", s->d.capacity);
+    const size_t kv = s->d.batch * s->d.n_layer * s->d.capacity * s->d.n_head_kv * s->d.hd * 4;
+    float *k32 = nullptr, *v32 = nullptr;
+    if (cudaMalloc((void**)&k32, kv) != cudaSuccess || cudaMalloc((void**)&v32, kv) != cudaSuccess) {
+      (void)cudaGetLastError();
+      cudaFree(k32);
+      rmi_set_error("allocation of the F32 caches (2 x %zu bytes) failed", kv);
+      return RMI_ERR_OOM;
+    }
+    cudaMemset(k32, 0, kv);
+    cudaMemset(v32, 0, kv);
+    s->k32_cache = k32;
+    s->v32_cache = v32;
   }
+  drop_graphs(s);  // the captured step belongs to the other variant
+  s->forward = forward;
   return RMI_OK;
 }
 
@@ -359,6 +381,7 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->argmax_v, argmax_scratch_floats(batch) * 4);
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   s->forward = RMI_FORWARD_QWEN3_SESSION;
+  s->k32_cache = s->v32_cache = nullptr;
   s->seq_attention = attention_seq_eligible(s->d) && getenv("RMI_NO_SEQ_ATTENTION") == nullptr;
   SESSION_ALLOC(s->q32, batch * nq * 4);
   s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
@@ -411,7 +434,12 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
       RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
       RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
     }
-    if (s->forward == RMI_FORWARD_APP_TEXT) {
+    if (s->forward == RMI_FORWARD_APP_TEXT_F32KV) {
+      // src/app/text.rs:393-405, :458-496: f32 query and F32 cache, padded soft-max, one dot per output element
+      RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
+                                     s->v_cache, l, s->q32, s->k32_cache, s->v32_cache));
+      RMI_TRY(launch_attention_f32kv(ctx, d, s->q32, s->k32_cache, s->v32_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+    } else if (s->forward == RMI_FORWARD_APP_TEXT) {
       // src/app/text.rs:257-648: f32 query, online soft-max over the F16 cache
       RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
                                      s->v_cache, l, s->q32));
@@ -446,7 +474,7 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   if (with_logits) {
     RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
     RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i,
-                          s->forward == RMI_FORWARD_APP_TEXT));
+                          is_cli_forward(s->forward)));
   }
   return launch_step_inc(ctx, s->d_step);
 }
@@ -541,7 +569,7 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
       passes++;
       rem %= p2;
     }
-  const uint64_t per_layer = 4 * passes + 1 + (s->fused_norm ? 0 : 2) + ((s->fused_qk && s->forward != RMI_FORWARD_APP_TEXT) ? 0 : 1) + 1;
+  const uint64_t per_layer = 4 * passes + 1 + (s->fused_norm ? 0 : 2) + ((s->fused_qk && !is_cli_forward(s->forward)) ? 0 : 1) + 1;
   const uint64_t launches_per_body = 3 + d.n_layer * per_layer, launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;

@@ -72,6 +72,54 @@ def test_cli_forward_online_softmax_tokens_hidden_and_logits(rmi, ctx, tmp_path_
     model.free()
 
 
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
+def test_cli_forward_f32_kv_cache_tokens_hidden_and_logits(rmi, ctx, tmp_path_factory, sem):
+    """The CLI loop with `--kv-cache f32` (src/app/text.rs:393-405, :458-496): f32 K/V, dot_f32 scores, padded
+    soft-max, one dot over the positions per output element.  Bit-identical in all three lane orders."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=2)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    prompt = rmi.synth.prompt_tokens(cfg["vocab"], 21, seed=9)
+    s = rmi.Qwen3Session(model, 21 + 30, forward=rmi.FORWARD_APP_TEXT_F32KV)
+    got = s.generate(prompt, 30)[0]
+    ref, trace, logits = oracle.generate(prompt, 30, sem=sem, want_trace=True, want_logits=True, cli=True, kv_f32=True)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    assert np.array_equal(bits(s.logits()[0]), bits(logits))
+    # the F16-cache variant on the same session still gives its own results afterwards
+    s.set_forward(rmi.FORWARD_APP_TEXT)
+    assert np.array_equal(s.generate(prompt, 30)[0], oracle.generate(prompt, 30, sem=sem, cli=True))
+    s.free()
+    model.free()
+
+
+def test_cli_forward_f32_kv_qwen3_head_shape_batch_and_context_limit(rmi, ctx, tmp_path_factory):
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_embd=1024, n_layer=2, n_head=16, n_head_kv=8, head_dim=128, n_ff=3072, vocab=2048)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=0)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    B = 3
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], 270, seed=20 + b) for b in range(B)])
+    s = rmi.Qwen3Session(model, 300, batch=B, forward=rmi.FORWARD_APP_TEXT_F32KV)
+    got = s.generate(prompts, 30)
+    for b in range(B):
+        ref, trace = oracle.generate(prompts[b], 30, sem=orc.SEM_AVX2, threads=8, want_trace=True, cli=True, kv_f32=True)
+        assert np.array_equal(got[b], ref), b
+        assert np.array_equal(bits(s.hidden()[b]), bits(trace[-1])), b
+    s.free()
+    # the reference's 512-entry value array: longer sessions are rejected, and the session keeps its variant
+    long = rmi.Qwen3Session(model, 513)
+    with pytest.raises(rmi.RmiError):
+        long.set_forward(rmi.FORWARD_APP_TEXT_F32KV)
+    long.free()
+    with pytest.raises(RuntimeError):
+        oracle.generate(prompts[0], 300, cli=True, kv_f32=True)
+    model.free()
+
+
 def test_cli_forward_qwen3_head_shape_long_context_and_batch(rmi, ctx, tmp_path_factory):
     ctx.set_semantics(rmi.SEM_AVX2)
     cfg = tiny_cfg(n_embd=1024, n_layer=2, n_head=16, n_head_kv=8, head_dim=128, n_ff=3072, vocab=2048)

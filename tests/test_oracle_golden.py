@@ -602,3 +602,48 @@ def test_cli_attention_helpers_and_tie_break():
     assert orc.greedy_token(x) == 1                                           # Qwen3Session keeps the first
     x[1] = np.nan
     assert lib.orc_greedy_token_last(orc._p(x), orc.C.c_size_t(3)) == -1
+
+
+def test_dot_f32_neon_pinned_vector_and_lane_orders():
+    """src/ops/matmul_tests.rs:240-258: the four-accumulator NEON reduction on 16 pinned inputs."""
+    lib = orc.lib()
+    lib.orc_dot_f32.restype = orc.C.c_float
+    a = np.array([1035226804, 3189287613, 3181886457, 3193572547, 1042787479, 3172027867, 1034549374, 3188264325,
+                  1056115932, 3201905443, 3188891406, 1051732974, 1049988604, 3191259790, 3197162127, 1039754039],
+                 np.uint32).view(np.float32)
+    b = np.array([1075433967, 1074732927, 1057635659, 3215511252, 3198768119, 1079784837, 1023408184, 3203974092,
+                  3215464821, 3191576483, 1049344900, 1021989171, 3207345090, 3229966761, 3189361871, 1036416888],
+                 np.uint32).view(np.float32)
+    got = np.float32(lib.orc_dot_f32(orc._p(a), orc._p(b), orc.C.c_size_t(16), orc.C.c_int(orc.SEM_NEON)))
+    assert int(got.view(np.uint32)) == 0x3d071678
+    rng = np.random.default_rng(11)
+    x, y = rng.standard_normal(256).astype(np.float32), rng.standard_normal(256).astype(np.float32)
+    ref = float((x.astype(np.float64) * y.astype(np.float64)).sum())
+    for sem in (orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR):
+        assert abs(lib.orc_dot_f32(orc._p(x), orc._p(y), orc.C.c_size_t(256), orc.C.c_int(sem)) - ref) < 1e-4
+    # the scalar order, restated in numpy f32
+    s = np.float32(0)
+    for i in range(40):
+        s = np.float32(s + np.float32(x[i] * y[i]))
+    got = np.float32(lib.orc_dot_f32(orc._p(x), orc._p(y), orc.C.c_size_t(40), orc.C.c_int(orc.SEM_SCALAR)))
+    assert got.tobytes() == s.tobytes()
+
+
+def test_cli_f32_cache_oracle_runs_and_tracks_the_f16_cache_variant():
+    """The F32-cache branch of the CLI loop differs from the F16-cache branch only by the cache rounding and the
+    soft-max form: hidden states stay close on a small model, and the first position (one cached key, weight
+    exactly 1) is identical except for the f16 rounding of V."""
+    from synth_model import tiny_model
+    cfg, tensors = tiny_model(seed=2)
+    oracle = orc.Qwen3(cfg, tensors)
+    prompt = np.arange(1, 13, dtype=np.uint32) % cfg["vocab"]
+    t32, tr32 = oracle.generate(prompt, 6, want_trace=True, cli=True, kv_f32=True)
+    t16, tr16 = oracle.generate(prompt, 6, want_trace=True, cli=True)
+    assert t32.shape == t16.shape == (6,)
+    assert np.isfinite(tr32).all()
+    assert np.abs(tr32[0] - tr16[0]).max() <= 2e-2 * max(1.0, np.abs(tr16[0]).max())
+    with pytest.raises(ValueError):
+        oracle.generate(prompt, 6, kv_f32=True)
+    for sem in (orc.SEM_NEON, orc.SEM_SCALAR):
+        alt = oracle.generate(prompt, 6, sem=sem, want_trace=True, cli=True, kv_f32=True)[1]
+        assert np.abs(alt - tr32).max() <= 1e-2 * max(1.0, np.abs(tr32).max())
