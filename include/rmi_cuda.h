@@ -268,8 +268,19 @@ int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s);
  *   K and V kept in f32, scores by dot_f32, soft-max over the scores padded to a multiple of 256, one dot_f32
  *   over the positions per output element.  The F32 caches are allocated by this call on first use; sessions
  *   longer than 512 positions are rejected (RMI_ERR_BAD_SHAPE; the reference's 512-entry value array panics).
- * The first two use the F16 cache. */
-enum { RMI_FORWARD_QWEN3_SESSION = 0, RMI_FORWARD_APP_TEXT = 1, RMI_FORWARD_APP_TEXT_F32KV = 2 };
+ * RMI_FORWARD_APP_LOGITS / RMI_FORWARD_APP_LOGITS_F32KV = the logits tool's loop (src/app/logits.rs:474-560) over the
+ *   F16 / F32 cache: scores by dot_f16_f32 / dot_f32, soft-max over the cached positions, then one sequential
+ *   chain per output element (val += p_t * v_t, separate multiply and add), first maximal index as the
+ *   reported token (:766-773); no 512-position limit.
+ * The server's loop (src/bin/server.rs:595-641) is the F16 branch of the text loop statement for statement
+ * (RMI_FORWARD_APP_TEXT). */
+enum {
+  RMI_FORWARD_QWEN3_SESSION = 0,
+  RMI_FORWARD_APP_TEXT = 1,
+  RMI_FORWARD_APP_TEXT_F32KV = 2,
+  RMI_FORWARD_APP_LOGITS = 3,
+  RMI_FORWARD_APP_LOGITS_F32KV = 4
+};
 int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward);
 /* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): feeds the prompts one
  * position at a time, then generates n_gen tokens per sequence; the whole step runs on the

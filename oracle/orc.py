@@ -387,22 +387,26 @@ class Qwen3:
         self._m = m
 
     def generate(self, prompt, n_gen, sem=SEM_AVX2, threads=1, want_trace=False, want_logits=False, cli=False,
-                 kv_f32=False):
+                 kv_f32=False, logits_tool=False):
         """cli=False: Qwen3Session (src/models/qwen3.rs); cli=True: the CLI's forward (src/app/text.rs:257-648),
-        with kv_f32 its `--kv-cache f32` branch."""
+        with kv_f32 its `--kv-cache f32` branch; logits_tool=True: the logits tool's loop (src/app/logits.rs)."""
         prompt = np.ascontiguousarray(prompt, np.uint32)
         out = np.zeros(max(n_gen, 1), np.uint32)
         steps = prompt.size + n_gen - 1
         trace = np.zeros((steps, self.cfg["n_embd"]), np.float32) if want_trace else None
         logits = np.zeros(self.cfg["vocab"], np.float32) if want_logits else None
         fn = lib().orc_qwen3_generate_cli if cli else lib().orc_qwen3_generate
-        if kv_f32:
+        extra = ()
+        if logits_tool:
+            fn = lib().orc_qwen3_generate_logits_tool
+            extra = (C.c_int(1 if kv_f32 else 0),)
+        elif kv_f32:
             if not cli:
                 raise ValueError("the F32 cache exists only in the CLI forward")
             fn = lib().orc_qwen3_generate_cli_f32kv
         fn.restype = C.c_int64
         n = fn(C.byref(self._m), _p(prompt), C.c_size_t(prompt.size), C.c_size_t(n_gen), _p(out), C.c_int(sem),
-               C.c_int(threads), _p(trace), _p(logits))
+               C.c_int(threads), _p(trace), _p(logits), *extra)
         if n == -2:
             raise RuntimeError("context longer than 512 positions (the reference's F32-cache value array)")
         if n < 0:

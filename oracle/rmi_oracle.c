@@ -1283,6 +1283,39 @@ static void attn_cli_f32_job_fn(void* p, size_t ith, size_t nth) {
   }
 }
 
+static void attn_logits_job_fn(void* p, size_t ith, size_t nth) {
+  /* src/app/logits.rs:474-560: scores (dot_f16_f32 over the F16 cache, dot_f32 over the F32 cache), soft-max
+   * over the cached positions, then val += p_t * v_t in position order for every output element */
+  attn_job* j = (attn_job*)p;
+  const orc_qwen3_config* c = &j->m->cfg;
+  size_t hd = c->head_dim, kv_stride = c->n_head_kv * hd;
+  size_t group = c->n_head / c->n_head_kv;
+  float kq_scale = 1.0f / sqrtf((float)hd);
+  size_t h0 = ith * c->n_head / nth, h1 = (ith + 1) * c->n_head / nth;
+  size_t layer_base = j->layer * j->capacity * kv_stride;
+  size_t n_cached = j->step + 1;
+  float* scores = j->scores + ith * 2 * j->score_stride;
+  for (size_t head = h0; head < h1; head++) {
+    size_t kvh = head / group;
+    for (size_t t = 0; t < n_cached; t++) {
+      size_t at = layer_base + t * kv_stride + kvh * hd;
+      float dot = j->k32 ? orc_dot_f32(j->q + head * hd, j->k32 + at, hd, j->sem)
+                         : orc_dot_f16_f32(j->q + head * hd, j->k_cache + at, hd, j->sem);
+      scores[t] = dot * kq_scale;
+    }
+    orc_softmax(scores, n_cached);
+    for (size_t d = 0; d < hd; d++) {
+      float val = 0.0f;
+      for (size_t t = 0; t < n_cached; t++) {
+        size_t at = layer_base + t * kv_stride + kvh * hd + d;
+        float prod = scores[t] * (j->v32 ? j->v32[at] : orc_f16_to_f32(j->v_cache[at]));
+        val = val + prod;
+      }
+      j->attn_out[head * hd + d] = val;
+    }
+  }
+}
+
 /* Iterator::max_by(partial_cmp): the last maximal index (src/app/text.rs:664-670); -1 on NaN (the reference panics) */
 int64_t orc_greedy_token_last(const float* logits, size_t n) {
   if (n == 0) return 0;
@@ -1335,6 +1368,14 @@ int64_t orc_qwen3_generate_cli_f32kv(const orc_qwen3_model* model, const uint32_
   return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last, 2);
 }
 
+/* the logits tool's copy of the loop (src/app/logits.rs:255-700) over the F16 (kv_f32 = 0) or F32 cache */
+int64_t orc_qwen3_generate_logits_tool(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                                       size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                                       float* logits_last, int kv_f32) {
+  return qwen3_generate_variant(model, prompt, n_prompt, n_gen, out_tokens, sem, threads, trace, logits_last,
+                                kv_f32 ? 4 : 3);
+}
+
 static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
                                       size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
                                       float* logits_last, int cli) {
@@ -1364,8 +1405,8 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
   uint8_t* q8 = (uint8_t*)calloc(max_n_in, 1);
   float* xs = (float*)calloc(max_n_in / 32 + 1, 4);
   float* scores = (float*)calloc((size_t)threads * 2 * score_stride, 4);
-  float* k32 = cli == 2 ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
-  float* v32 = cli == 2 ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
+  float* k32 = (cli == 2 || cli == 4) ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
+  float* v32 = (cli == 2 || cli == 4) ? (float*)calloc(c->n_layer * capacity * kv_stride, 4) : NULL;
 
   int64_t n_out = 0;
   int failed = 0;
@@ -1386,7 +1427,7 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
       orc_rope_neox(q, nq, pos, hd, c->freq_base);
       orc_rope_neox(k, nk, pos, hd, c->freq_base);
       size_t row = layer * capacity * kv_stride + step * kv_stride;
-      if (cli == 2) {
+      if (k32) {
         memcpy(k32 + row, k, 4 * nk);
         memcpy(v32 + row, v, 4 * nk);
       } else {
@@ -1394,7 +1435,7 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
         orc_f32_slice_to_f16(v, v_cache + row, nk);
       }
       attn_job aj = {model, layer, step, capacity, q, attn_out, k_cache, v_cache, scores, score_stride, sem, k32, v32};
-      orc_compute(threads, cli == 2 ? attn_cli_f32_job_fn : (cli ? attn_cli_job_fn : attn_job_fn), &aj);
+      orc_compute(threads, cli >= 3 ? attn_logits_job_fn : (cli == 2 ? attn_cli_f32_job_fn : (cli ? attn_cli_job_fn : attn_job_fn)), &aj);
       quantize_any(attn_out, n_attn, q8, xs, sem);
       pooled_gemv(w->wo, q8, xs, proj, n_attn, c->n_embd, sem, threads);
       for (size_t i = 0; i < c->n_embd; i++) x[i] = x[i] + proj[i];
@@ -1413,7 +1454,8 @@ static int64_t qwen3_generate_variant(const orc_qwen3_model* model, const uint32
     quantize_any(normed, c->n_embd, q8, xs, sem);
     pooled_gemv(model->output, q8, xs, logits, c->n_embd, c->vocab, sem, threads);
     if (step + 1 < n_prompt) continue;
-    int64_t t = cli ? orc_greedy_token_last(logits, c->vocab) : orc_greedy_token(logits, c->vocab);
+    /* text loop: last maximal index; Qwen3Session and the logits tool (src/app/logits.rs:766-773): the first */
+    int64_t t = (cli == 1 || cli == 2) ? orc_greedy_token_last(logits, c->vocab) : orc_greedy_token(logits, c->vocab);
     if (t < 0) {
       failed = 1;
       break;

@@ -219,6 +219,9 @@ int64_t orc_qwen3_generate_cli(const orc_qwen3_model* model, const uint32_t* pro
 int64_t orc_qwen3_generate_cli_f32kv(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
                                      size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
                                      float* logits_last);
+int64_t orc_qwen3_generate_logits_tool(const orc_qwen3_model* model, const uint32_t* prompt, size_t n_prompt,
+                                       size_t n_gen, uint32_t* out_tokens, int sem, int threads, float* trace,
+                                       float* logits_last, int kv_f32);
 float orc_dot_f32(const float* a, const float* b, size_t n, int sem);
 float orc_dot_f16_f32(const float* a, const uint16_t* b, size_t n, int sem);
 void orc_vec_mad_f16_f32(float* y, const uint16_t* x, float v, size_t n, int sem);

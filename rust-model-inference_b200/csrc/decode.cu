@@ -692,20 +692,35 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// The CLI forward with an F32 cache (src/app/text.rs:458-496), one CTA per (head, sequence): scores =
-// dot_f32(q, k_t) * scale in the lane order of the selected instruction set (src/ops/dot.rs:8-76: eight AVX2
-// lanes; four NEON accumulators of four lanes, combined (acc0+acc2)+(acc1+acc3) then pairwise; one scalar chain
-// with separate multiply and add), the soft-max of src/ops/attention.rs:28-38 over the scores (the -inf padding to
-// a multiple of 256 adds exact zeros), then out[d] = dot_f32(V[:, d], weights) in the same lane order over the
-// positions: chain l of element d takes the positions l, l + LN, ...; the chains of one element are combined
-// through shared memory.  Padded positions multiply a zero by a zero weight and leave every chain unchanged.
-template <int SEM>
+// Score-buffer attention of the CLI forwards, one CTA per (head, sequence), over an F32 or an F16 cache:
+//   * `--kv-cache f32` of the text loop (src/app/text.rs:458-496; KV16 = false, SEQ_PV = false): scores =
+//     dot_f32(q, k_t) * scale in the lane order of the selected instruction set (src/ops/dot.rs:8-76: eight AVX2
+//     lanes; four NEON accumulators of four lanes, combined (acc0+acc2)+(acc1+acc3) then pairwise; one scalar chain
+//     with separate multiply and add), the soft-max of src/ops/attention.rs:28-38 (the -inf padding to a multiple
+//     of 256 adds exact zeros), then out[d] = dot_f32(V[:, d], weights) in the same lane order over the positions:
+//     chain l of element d takes the positions l, l + LN, ...; the chains of one element are combined through
+//     shared memory.  Padded positions multiply a zero by a zero weight and leave every chain unchanged.
+//   * the logits tool (src/app/logits.rs:474-560; SEQ_PV = true): scores by dot_f16_f32 over the F16 cache
+//     (KV16 = true: eight AVX2 lanes, four NEON lanes, src/ops/dot.rs:79-97, :241-276) or dot_f32 over the F32
+//     cache, the same soft-max, then one sequential chain per output element, val += p_t * v_t with separate
+//     multiply and add in every instruction set.
+template <bool KV16>
+struct kv_elem { using type = float; };
+template <>
+struct kv_elem<true> { using type = uint16_t; };
+__device__ __forceinline__ float kv_load(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float kv_load(const uint16_t* p) { return f16_bits_to_f32(__ldg(p)); }
+
+template <int SEM, bool KV16, bool SEQ_PV>
 __global__ void __launch_bounds__(256)
-    attention_f32kv_kernel(const float* __restrict__ q32, const float* __restrict__ k_cache,
-                           const float* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
-                           size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
-                           float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
-  constexpr int LN = SEM == RMI_SEM_AVX2 ? 8 : (SEM == RMI_SEM_NEON ? 16 : 1);
+    attention_softmax_kernel(const float* __restrict__ q32, const typename kv_elem<KV16>::type* __restrict__ k_cache,
+                             const typename kv_elem<KV16>::type* __restrict__ v_cache, const int* __restrict__ d_step,
+                             size_t n_head, size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
+                             float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+  using kv_t = typename kv_elem<KV16>::type;
+  constexpr int LN = SEM == RMI_SEM_AVX2 ? 8 : (SEM == RMI_SEM_NEON ? (KV16 ? 4 : 16) : 1);  // score lanes
+  constexpr int LP = SEQ_PV ? 1 : LN;                                                        // chains per element
+  constexpr bool PV_FMA = !SEQ_PV && SEM != RMI_SEM_SCALAR;
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -715,11 +730,11 @@ __global__ void __launch_bounds__(256)
   const size_t cap4 = (capacity + 3) & ~(size_t)3;
   float* sc = reinterpret_cast<float*>(smem);  // [capacity] scores, then weights
   float* qs = sc + cap4;                       // [hd]
-  float* part = qs + hd;                       // [LN][hd] chain results
-  float* red = part + (size_t)LN * hd;         // [32]
+  float* part = qs + hd;                       // [16][hd] chain results
+  float* red = part + 16 * hd;                 // [32]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
-  const float* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const kv_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const kv_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
   for (size_t i = tid; i < hd; i += blockDim.x) qs[i] = q32[b * nq + head * hd + i];
   __syncthreads();
   const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
@@ -729,11 +744,11 @@ __global__ void __launch_bounds__(256)
     for (int t = grp; t < ((T + n_grp - 1) / n_grp) * n_grp; t += n_grp) {  // whole warps stay converged
       float acc = 0.0f;
       if (t < T) {
-        const float* kr = kbase + (size_t)t * nk;
+        const kv_t* kr = kbase + (size_t)t * nk;
         for (size_t i0 = l; i0 < hd; i0 += 4 * LN) {  // the loads of four steps are issued together
           float kv[4];
 #pragma unroll
-          for (int u = 0; u < 4; u++) kv[u] = i0 + (size_t)u * LN < hd ? __ldg(kr + i0 + (size_t)u * LN) : 0.0f;
+          for (int u = 0; u < 4; u++) kv[u] = i0 + (size_t)u * LN < hd ? kv_load(kr + i0 + (size_t)u * LN) : 0.0f;
 #pragma unroll
           for (int u = 0; u < 4; u++)
             if (i0 + (size_t)u * LN < hd) {
@@ -746,10 +761,12 @@ __global__ void __launch_bounds__(256)
         acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-      } else if (SEM == RMI_SEM_NEON) {  // (acc0 + acc2) + (acc1 + acc3), then vaddvq_f32
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+      } else if (SEM == RMI_SEM_NEON) {
+        if (!KV16) {  // (acc0 + acc2) + (acc1 + acc3)
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+        }
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));  // vaddvq_f32
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
       }
       if (l == 0 && t < T) sc[t] = __fmul_rn(acc, kq_scale);
@@ -781,19 +798,19 @@ __global__ void __launch_bounds__(256)
   __syncthreads();
 
   // chains: item = l * hd + d, so a warp reads 32 consecutive elements of one V row
-  for (size_t item = tid; item < (size_t)LN * hd; item += 256) {
+  for (size_t item = tid; item < (size_t)LP * hd; item += 256) {
     const size_t l = item / hd, d = item % hd;
-    const float* vc = vbase + d;
+    const kv_t* vc = vbase + d;
     float acc = 0.0f;
-    for (int t0 = (int)l; t0 < T; t0 += 4 * LN) {
+    for (int t0 = (int)l; t0 < T; t0 += 4 * LP) {
       float vv[4];
 #pragma unroll
-      for (int u = 0; u < 4; u++) vv[u] = t0 + u * LN < T ? __ldg(vc + (size_t)(t0 + u * LN) * nk) : 0.0f;
+      for (int u = 0; u < 4; u++) vv[u] = t0 + u * LP < T ? kv_load(vc + (size_t)(t0 + u * LP) * nk) : 0.0f;
 #pragma unroll
       for (int u = 0; u < 4; u++)
-        if (t0 + u * LN < T) {
-          const float wgt = sc[t0 + u * LN];
-          acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(vv[u], wgt)) : __fmaf_rn(vv[u], wgt, acc);
+        if (t0 + u * LP < T) {
+          const float wgt = sc[t0 + u * LP];
+          acc = PV_FMA ? __fmaf_rn(vv[u], wgt, acc) : __fadd_rn(acc, __fmul_rn(vv[u], wgt));
         }
     }
     part[item] = acc;
@@ -802,11 +819,11 @@ __global__ void __launch_bounds__(256)
   if ((size_t)tid < hd) {
     float out;
     const float* p = part + tid;
-    if (SEM == RMI_SEM_AVX2) {
+    if (LP == 8) {
       const float s0 = __fadd_rn(p[4 * hd], p[0]), s1 = __fadd_rn(p[5 * hd], p[hd]);
       const float s2 = __fadd_rn(p[6 * hd], p[2 * hd]), s3 = __fadd_rn(p[7 * hd], p[3 * hd]);
       out = __fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3));
-    } else if (SEM == RMI_SEM_NEON) {
+    } else if (LP == 16) {
       float c[4];
 #pragma unroll
       for (int i = 0; i < 4; i++)
@@ -1085,25 +1102,41 @@ int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float*
   return rmi_post_launch(ctx, "attention_online");
 }
 
-int32_t launch_attention_f32kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const float* k_cache,
-                               const float* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
-                               float* scales) {
-  RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "F32-cache attention needs head_dim %% 32 == 0 and <= 256");
+template <bool KV16, bool SEQ_PV>
+static int32_t launch_attention_softmax_t(rmi_ctx* ctx, const decode_dims& d, const float* q32,
+                                          const typename kv_elem<KV16>::type* k_cache,
+                                          const typename kv_elem<KV16>::type* v_cache, const int* d_step, size_t layer,
+                                          float* attn_out, uint8_t* q8, float* scales) {
+  RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "score-buffer attention needs head_dim %% 32 == 0 and <= 256");
   const size_t smem = (((d.capacity + 3) & ~(size_t)3) + d.hd + 16 * d.hd + 32) * 4;
-  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_f32kv_kernel<RMI_SEM_AVX2>
-                                       : (ctx->sem == RMI_SEM_NEON ? attention_f32kv_kernel<RMI_SEM_NEON>
-                                                                   : attention_f32kv_kernel<RMI_SEM_SCALAR>);
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_softmax_kernel<RMI_SEM_AVX2, KV16, SEQ_PV>
+                                       : (ctx->sem == RMI_SEM_NEON ? attention_softmax_kernel<RMI_SEM_NEON, KV16, SEQ_PV>
+                                                                   : attention_softmax_kernel<RMI_SEM_SCALAR, KV16, SEQ_PV>);
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
-    rmi_set_error("F32-cache attention needs %zu B of shared memory", smem);
+    rmi_set_error("score-buffer attention needs %zu B of shared memory", smem);
     return RMI_ERR_UNSUPPORTED;
   }
   if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head, (unsigned)d.batch), dim3(256), smem, q32, k_cache, v_cache, d_step,
                  d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales) != cudaSuccess) {
-    rmi_set_error("launch of attention_f32kv failed: %s", cudaGetErrorString(cudaGetLastError()));
+    rmi_set_error("launch of attention_softmax failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }
-  return rmi_post_launch(ctx, "attention_f32kv");
+  return rmi_post_launch(ctx, "attention_softmax");
+}
+
+int32_t launch_attention_f32kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const float* k_cache,
+                               const float* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
+                               float* scales, bool sequential_pv) {
+  return sequential_pv
+             ? launch_attention_softmax_t<false, true>(ctx, d, q32, k_cache, v_cache, d_step, layer, attn_out, q8, scales)
+             : launch_attention_softmax_t<false, false>(ctx, d, q32, k_cache, v_cache, d_step, layer, attn_out, q8, scales);
+}
+
+int32_t launch_attention_scores_f16kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
+                                      const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out,
+                                      uint8_t* q8, float* scales) {
+  return launch_attention_softmax_t<true, true>(ctx, d, q32, k_cache, v_cache, d_step, layer, attn_out, q8, scales);
 }
 
 size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }

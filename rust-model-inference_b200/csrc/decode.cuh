@@ -30,7 +30,10 @@ int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float*
                                 float* scales);
 int32_t launch_attention_f32kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const float* k_cache,
                                const float* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
-                               float* scales);
+                               float* scales, bool sequential_pv = false);
+int32_t launch_attention_scores_f16kv(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
+                                      const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out,
+                                      uint8_t* q8, float* scales);
 size_t argmax_scratch_floats(size_t batch);
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
                       size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i, bool last_index = false);

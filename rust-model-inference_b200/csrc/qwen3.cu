@@ -292,20 +292,22 @@ extern "C" int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s) {
 }
 
 static bool is_cli_forward(int forward) { return forward != RMI_FORWARD_QWEN3_SESSION; }
+static bool uses_f32_cache(int forward) {
+  return forward == RMI_FORWARD_APP_TEXT_F32KV || forward == RMI_FORWARD_APP_LOGITS_F32KV;
+}
 
 extern "C" int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward) {
   RMI_TRY(rmi_check_ctx(ctx));
   RMI_TRY(check_session(s));
-  RMI_REQUIRE(forward == RMI_FORWARD_QWEN3_SESSION || forward == RMI_FORWARD_APP_TEXT ||
-                  forward == RMI_FORWARD_APP_TEXT_F32KV,
-              RMI_ERR_UNSUPPORTED, "unknown forward variant %d", forward);
+  RMI_REQUIRE(forward >= RMI_FORWARD_QWEN3_SESSION && forward <= RMI_FORWARD_APP_LOGITS_F32KV, RMI_ERR_UNSUPPORTED,
+              "unknown forward variant %d", forward);
   std::lock_guard<std::mutex> lock(ctx->mu);
   if (s->forward == forward) return RMI_OK;
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
-  if (forward == RMI_FORWARD_APP_TEXT_F32KV && !s->k32_cache) {
-    // the reference gathers a column of V into a 512-entry array (src/app/text.rs:478) and panics beyond it
-    RMI_REQUIRE((s->d.capacity + 255) / 256 * 256 <= 512, RMI_ERR_BAD_SHAPE,
-                "the F32 cache holds at most 512 positions, session capacity is %zu", s->d.capacity);
+  // the text loop gathers a column of V into a 512-entry array (src/app/text.rs:478) and panics beyond it
+  RMI_REQUIRE(forward != RMI_FORWARD_APP_TEXT_F32KV || (s->d.capacity + 255) / 256 * 256 <= 512, RMI_ERR_BAD_SHAPE,
+              "the text loop's F32 cache holds at most 512 positions, session capacity is %zu", s->d.capacity);
+  if (uses_f32_cache(forward) && !s->k32_cache) {
     const size_t kv = s->d.batch * s->d.n_layer * s->d.capacity * s->d.n_head_kv * s->d.hd * 4;
     float *k32 = nullptr, *v32 = nullptr;
     if (cudaMalloc((void**)&k32, kv) != cudaSuccess || cudaMalloc((void**)&v32, kv) != cudaSuccess) {
@@ -434,11 +436,18 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
       RMI_TRY(launch_rmsnorm_quant(ctx, xc, pending, w.attn_norm, d.n_embd, d.eps, s->q8, s->xs, B));
       RMI_TRY(launch_q8_gemv(ctx, w.wqkv, s->q8, s->xs, B, s->qkv, nq + 2 * nk, 0, nq + 2 * nk));
     }
-    if (s->forward == RMI_FORWARD_APP_TEXT_F32KV) {
-      // src/app/text.rs:393-405, :458-496: f32 query and F32 cache, padded soft-max, one dot per output element
+    if (uses_f32_cache(s->forward)) {
+      // src/app/text.rs:393-405, :458-496: f32 query and F32 cache, padded soft-max, one dot per output element;
+      // src/app/logits.rs:513-560: the same scores and soft-max, then a sequential chain per output element
       RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
                                      s->v_cache, l, s->q32, s->k32_cache, s->v32_cache));
-      RMI_TRY(launch_attention_f32kv(ctx, d, s->q32, s->k32_cache, s->v32_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+      RMI_TRY(launch_attention_f32kv(ctx, d, s->q32, s->k32_cache, s->v32_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs,
+                                     s->forward == RMI_FORWARD_APP_LOGITS_F32KV));
+    } else if (s->forward == RMI_FORWARD_APP_LOGITS) {
+      // src/app/logits.rs:474-512: f32 query x F16 cache scores, soft-max, sequential chain per output element
+      RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
+                                     s->v_cache, l, s->q32));
+      RMI_TRY(launch_attention_scores_f16kv(ctx, d, s->q32, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
     } else if (s->forward == RMI_FORWARD_APP_TEXT) {
       // src/app/text.rs:257-648: f32 query, online soft-max over the F16 cache
       RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
@@ -474,7 +483,7 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   if (with_logits) {
     RMI_TRY(launch_q8_gemv(ctx, m->output, s->q8, s->xs, B, s->logits, d.vocab, 0, d.vocab));
     RMI_TRY(launch_argmax(ctx, s->logits, d.vocab, s->d_step, n_prompt, s->gen, n_gen, s->d_flag, B, s->argmax_v, s->argmax_i,
-                          is_cli_forward(s->forward)));
+                          s->forward == RMI_FORWARD_APP_TEXT || s->forward == RMI_FORWARD_APP_TEXT_F32KV));
   }
   return launch_step_inc(ctx, s->d_step);
 }

@@ -120,6 +120,49 @@ def test_cli_forward_f32_kv_qwen3_head_shape_batch_and_context_limit(rmi, ctx, t
     model.free()
 
 
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
+@pytest.mark.parametrize("kv_f32", [False, True])
+def test_logits_tool_forward_tokens_hidden_and_logits(rmi, ctx, tmp_path_factory, sem, kv_f32):
+    """The logits tool's loop (src/app/logits.rs:474-560) over the F16 and the F32 cache: lane-ordered scores,
+    soft-max, sequential chain per output element.  Bit-identical in all three lane orders."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=4)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    prompt = rmi.synth.prompt_tokens(cfg["vocab"], 37, seed=12)
+    fwd = rmi.FORWARD_APP_LOGITS_F32KV if kv_f32 else rmi.FORWARD_APP_LOGITS
+    s = rmi.Qwen3Session(model, 37 + 9, forward=fwd)
+    got = s.generate(prompt, 9)[0]
+    ref, trace, logits = oracle.generate(prompt, 9, sem=sem, want_trace=True, want_logits=True, logits_tool=True,
+                                         kv_f32=kv_f32)
+    assert np.array_equal(got, ref)
+    assert np.array_equal(bits(s.hidden()[0]), bits(trace[-1]))
+    assert np.array_equal(bits(s.logits()[0]), bits(logits))
+    s.free()
+    model.free()
+
+
+def test_logits_tool_forward_qwen3_head_shape_beyond_512_positions(rmi, ctx, tmp_path_factory):
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_embd=512, n_layer=2, n_head=8, n_head_kv=4, head_dim=128, n_ff=1024, vocab=512)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=6)
+    model = rmi.Qwen3Model.from_file(path)
+    oracle = orc.Qwen3(cfg, tensors)
+    B, P, G = 2, 530, 4
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], P, seed=40 + b) for b in range(B)])
+    for kv_f32 in (False, True):
+        s = rmi.Qwen3Session(model, P + G, batch=B,
+                             forward=rmi.FORWARD_APP_LOGITS_F32KV if kv_f32 else rmi.FORWARD_APP_LOGITS)
+        got = s.generate(prompts, G)
+        for b in range(B):
+            ref, trace = oracle.generate(prompts[b], G, threads=8, want_trace=True, logits_tool=True, kv_f32=kv_f32)
+            assert np.array_equal(got[b], ref), (kv_f32, b)
+            assert np.array_equal(bits(s.hidden()[b]), bits(trace[-1])), (kv_f32, b)
+        s.free()
+    model.free()
+
+
 def test_cli_forward_qwen3_head_shape_long_context_and_batch(rmi, ctx, tmp_path_factory):
     ctx.set_semantics(rmi.SEM_AVX2)
     cfg = tiny_cfg(n_embd=1024, n_layer=2, n_head=16, n_head_kv=8, head_dim=128, n_ff=3072, vocab=2048)

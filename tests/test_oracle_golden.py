@@ -647,3 +647,8 @@ def test_cli_f32_cache_oracle_runs_and_tracks_the_f16_cache_variant():
     for sem in (orc.SEM_NEON, orc.SEM_SCALAR):
         alt = oracle.generate(prompt, 6, sem=sem, want_trace=True, cli=True, kv_f32=True)[1]
         assert np.abs(alt - tr32).max() <= 1e-2 * max(1.0, np.abs(tr32).max())
+    # the logits tool's loop: same scores and soft-max, sequential value chains; first maximal index
+    for kv_f32 in (False, True):
+        tl, trl = oracle.generate(prompt, 6, want_trace=True, logits_tool=True, kv_f32=kv_f32)
+        assert tl.shape == (6,) and np.isfinite(trl).all()
+        assert np.abs(trl - (tr32 if kv_f32 else tr16)).max() <= 1e-2 * max(1.0, np.abs(tr16).max())
