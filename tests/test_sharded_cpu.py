@@ -138,3 +138,46 @@ def test_exchange_handles_rejects_duplicates_and_gaps():
     with pytest.raises(ValueError):
         pkg.sharding.exchange_handles(b"a", 0, 2, gap)
     assert pkg.sharding.rotate_own_first([10, 11, 12, 13], 2) == [12, 13, 10, 11]
+
+
+def _plan_worker(rank, world, port, n, k, m, q):
+    """Each rank builds the TensorSplit plan itself (it is deterministic), takes the rows the plan puts on its
+    device, computes them with the oracle and all-gathers."""
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    from oracle import orc
+    pkg = load_package()
+    lp = pkg.load_plan
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        idx = lp.PackageIndex.from_tensor_table([("token_embd.weight", [32], 0), ("blk.0.ffn_up.weight", [k, n], 8)], 1)
+        devices = lp.balanced_devices(idx, world)
+        plan = lp.build_load_plan(idx, [0], devices, devices[0].id, lp.TENSOR_SPLIT)
+        (rows,) = plan.rows_on("blk.0.ffn_up.weight", devices[rank].id)
+        s, e = rows
+        shard = pkg.synth.q8_0_weight_rows(n, k, seed=5, row_begin=s, row_end=e)
+        x = pkg.synth.normal((m, k), seed=6)
+        local = orc.q8_forward_batched(shard, x, k, e - s, orc.SEM_AVX2)
+        full = pkg.sharding.all_gather_cols_cpu(local)
+        whole = pkg.synth.q8_0_weight_rows(n, k, seed=5, row_begin=0, row_end=n)
+        ref = orc.q8_forward_batched(whole, x, k, n, orc.SEM_AVX2)
+        q.put((rank, (s, e), bool(np.array_equal(full.view(np.uint32), ref.view(np.uint32)))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_take_their_rows_from_a_tensor_split_plan():
+    world, n, k, m = 2, 256, 128, 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_plan_worker, args=(r, world, port, n, k, m, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert [r[1] for r in res] == [(0, 128), (128, 256)]
+    assert all(r[2] for r in res)
