@@ -708,8 +708,12 @@ template <bool KV16>
 struct kv_elem { using type = float; };
 template <>
 struct kv_elem<true> { using type = uint16_t; };
-__device__ __forceinline__ float kv_load(const float* p) { return __ldg(p); }
-__device__ __forceinline__ float kv_load(const uint16_t* p) { return f16_bits_to_f32(__ldg(p)); }
+__device__ __forceinline__ float kv_val(const float* p) { return *p; }
+__device__ __forceinline__ float kv_val(const uint16_t* p) { return f16_bits_to_f32(*p); }
+
+// K and V pass through two shared-memory tiles of SM_TILE positions (cp.async, the next tile in flight while the
+// current one is used; rows padded by 16 bytes against bank conflicts): a chain must not wait on global memory.
+constexpr int SM_TILE = 64;
 
 template <int SEM, bool KV16, bool SEQ_PV>
 __global__ void __launch_bounds__(256)
@@ -721,6 +725,7 @@ __global__ void __launch_bounds__(256)
   constexpr int LN = SEM == RMI_SEM_AVX2 ? 8 : (SEM == RMI_SEM_NEON ? (KV16 ? 4 : 16) : 1);  // score lanes
   constexpr int LP = SEQ_PV ? 1 : LN;                                                        // chains per element
   constexpr bool PV_FMA = !SEQ_PV && SEM != RMI_SEM_SCALAR;
+  constexpr int MAX_ITEMS = LP;  // LP * hd / 256 chains per thread with hd <= 256
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -732,47 +737,61 @@ __global__ void __launch_bounds__(256)
   float* qs = sc + cap4;                       // [hd]
   float* part = qs + hd;                       // [16][hd] chain results
   float* red = part + 16 * hd;                 // [32]
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(red + 32);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const kv_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
   const kv_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
   for (size_t i = tid; i < hd; i += blockDim.x) qs[i] = q32[b * nq + head * hd + i];
-  __syncthreads();
   const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+
+  const size_t row_bytes = hd * sizeof(kv_t), row_stride = row_bytes + 16, tile_bytes = SM_TILE * row_stride;
+  const size_t row16 = row_bytes / 16;
+  const int n_tiles = (T + SM_TILE - 1) / SM_TILE;
+  auto stage = [&](const kv_t* base, int tile, int buf) {
+    const int t0 = tile * SM_TILE, nt = min(SM_TILE, T - t0);
+    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
+    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
+      cp_async16(dst + (i / row16) * row_stride + (i % row16) * 16,
+                 reinterpret_cast<const uint8_t*>(base + (size_t)(t0 + i / row16) * nk) + (i % row16) * 16);
+    cp_async_commit();
+  };
 
   {  // scores: LN threads per position, thread l takes elements l, l + LN, ... (one SIMD lane)
     const int l = tid % LN, grp = tid / LN, n_grp = 256 / LN;
-    for (int t = grp; t < ((T + n_grp - 1) / n_grp) * n_grp; t += n_grp) {  // whole warps stay converged
-      float acc = 0.0f;
-      if (t < T) {
-        const kv_t* kr = kbase + (size_t)t * nk;
-        for (size_t i0 = l; i0 < hd; i0 += 4 * LN) {  // the loads of four steps are issued together
-          float kv[4];
-#pragma unroll
-          for (int u = 0; u < 4; u++) kv[u] = i0 + (size_t)u * LN < hd ? kv_load(kr + i0 + (size_t)u * LN) : 0.0f;
-#pragma unroll
-          for (int u = 0; u < 4; u++)
-            if (i0 + (size_t)u * LN < hd) {
-              const float qv = qs[i0 + (size_t)u * LN];
-              acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qv, kv[u])) : __fmaf_rn(qv, kv[u], acc);
-            }
+    stage(kbase, 0, 0);
+    for (int tile = 0; tile < n_tiles; tile++) {
+      if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1);
+      if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+      __syncthreads();  // also orders the staging of qs before its first use
+      const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
+      const int t0 = tile * SM_TILE, nt = min(SM_TILE, T - t0);
+      for (int tl = grp; tl < ((nt + n_grp - 1) / n_grp) * n_grp; tl += n_grp) {  // whole warps stay converged
+        float acc = 0.0f;
+        if (tl < nt) {
+          const kv_t* kr = reinterpret_cast<const kv_t*>(kt + (size_t)tl * row_stride);
+          for (size_t i = l; i < hd; i += LN) {
+            const float kv = kv_val(kr + i);
+            acc = SEM == RMI_SEM_SCALAR ? __fadd_rn(acc, __fmul_rn(qs[i], kv)) : __fmaf_rn(qs[i], kv, acc);
+          }
         }
-      }
-      if (SEM == RMI_SEM_AVX2) {  // hsum_ps
-        acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
-      } else if (SEM == RMI_SEM_NEON) {
-        if (!KV16) {  // (acc0 + acc2) + (acc1 + acc3)
-          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
-          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+        if (SEM == RMI_SEM_AVX2) {  // hsum_ps
+          acc = __fadd_rn(__shfl_xor_sync(0xffffffffu, acc, 4), acc);
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        } else if (SEM == RMI_SEM_NEON) {
+          if (!KV16) {  // (acc0 + acc2) + (acc1 + acc3)
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+            acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+          }
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));  // vaddvq_f32
+          acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
         }
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));  // vaddvq_f32
-        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+        if (l == 0 && tl < nt) sc[t0 + tl] = __fmul_rn(acc, kq_scale);
       }
-      if (l == 0 && t < T) sc[t] = __fmul_rn(acc, kq_scale);
+      __syncthreads();  // the tile may be overwritten by the copy issued in the next iteration
     }
   }
-  __syncthreads();
+  stage(vbase, 0, 0);  // the first V tile arrives during the soft-max
 
   // soft-max: maximum, exp, sequential f32 sum, divide
   float mx = -INFINITY;
@@ -795,25 +814,39 @@ __global__ void __launch_bounds__(256)
   const float sum = red[16];
   if (sum > 0.0f)
     for (int t = tid; t < T; t += 256) sc[t] = __fdiv_rn(sc[t], sum);
-  __syncthreads();
 
-  // chains: item = l * hd + d, so a warp reads 32 consecutive elements of one V row
-  for (size_t item = tid; item < (size_t)LP * hd; item += 256) {
-    const size_t l = item / hd, d = item % hd;
-    const kv_t* vc = vbase + d;
-    float acc = 0.0f;
-    for (int t0 = (int)l; t0 < T; t0 += 4 * LP) {
-      float vv[4];
+  // chains: item = l * hd + d (a warp reads 32 consecutive elements of one V row); chain l of element d takes the
+  // positions l, l + LP, ...; SM_TILE is a multiple of LP, so inside every tile chain l starts at local position l
+  float acc[MAX_ITEMS];
 #pragma unroll
-      for (int u = 0; u < 4; u++) vv[u] = t0 + u * LP < T ? kv_load(vc + (size_t)(t0 + u * LP) * nk) : 0.0f;
+  for (int it = 0; it < MAX_ITEMS; it++) acc[it] = 0.0f;
+  for (int tile = 0; tile < n_tiles; tile++) {
+    if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();  // also orders the weights written above before their first use
+    const uint8_t* vt = tiles + (size_t)(tile & 1) * tile_bytes;
+    const int t0 = tile * SM_TILE, nt = min(SM_TILE, T - t0);
 #pragma unroll
-      for (int u = 0; u < 4; u++)
-        if (t0 + u * LP < T) {
-          const float wgt = sc[t0 + u * LP];
-          acc = PV_FMA ? __fmaf_rn(vv[u], wgt, acc) : __fadd_rn(acc, __fmul_rn(vv[u], wgt));
+    for (int it = 0; it < MAX_ITEMS; it++) {
+      const size_t item = (size_t)tid + 256 * (size_t)it;
+      if (item < (size_t)LP * hd) {
+        const int l = (int)(item / hd);
+        const kv_t* vc = reinterpret_cast<const kv_t*>(vt) + item % hd;
+        float a = acc[it];
+        for (int tl = l; tl < nt; tl += LP) {
+          const float vv = kv_val(reinterpret_cast<const kv_t*>(reinterpret_cast<const uint8_t*>(vc) + (size_t)tl * row_stride));
+          const float wgt = sc[t0 + tl];
+          a = PV_FMA ? __fmaf_rn(vv, wgt, a) : __fadd_rn(a, __fmul_rn(vv, wgt));
         }
+        acc[it] = a;
+      }
     }
-    part[item] = acc;
+    __syncthreads();
+  }
+#pragma unroll
+  for (int it = 0; it < MAX_ITEMS; it++) {
+    const size_t item = (size_t)tid + 256 * (size_t)it;
+    if (item < (size_t)LP * hd) part[item] = acc[it];
   }
   __syncthreads();
   if ((size_t)tid < hd) {
@@ -1108,7 +1141,8 @@ static int32_t launch_attention_softmax_t(rmi_ctx* ctx, const decode_dims& d, co
                                           const typename kv_elem<KV16>::type* v_cache, const int* d_step, size_t layer,
                                           float* attn_out, uint8_t* q8, float* scales) {
   RMI_REQUIRE(d.hd % 32 == 0 && d.hd <= 256, RMI_ERR_UNSUPPORTED, "score-buffer attention needs head_dim %% 32 == 0 and <= 256");
-  const size_t smem = (((d.capacity + 3) & ~(size_t)3) + d.hd + 16 * d.hd + 32) * 4;
+  const size_t smem = (((d.capacity + 3) & ~(size_t)3) + d.hd + 16 * d.hd + 32) * 4 +
+                      2 * SM_TILE * (d.hd * sizeof(typename kv_elem<KV16>::type) + 16);
   auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_softmax_kernel<RMI_SEM_AVX2, KV16, SEQ_PV>
                                        : (ctx->sem == RMI_SEM_NEON ? attention_softmax_kernel<RMI_SEM_NEON, KV16, SEQ_PV>
                                                                    : attention_softmax_kernel<RMI_SEM_SCALAR, KV16, SEQ_PV>);
