@@ -227,10 +227,13 @@ def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10):
     return res
 
 
-def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem):
+FORWARDS = {"session": 0, "text": 1, "text_f32kv": 2, "logits": 3, "logits_f32kv": 4}
+
+
+def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="session"):
     ctx.set_semantics(sem)
     model = pkg.Qwen3Model.from_file(path)
-    s = pkg.Qwen3Session(model, n_prompt + n_gen, batch=batch)
+    s = pkg.Qwen3Session(model, n_prompt + n_gen, batch=batch, forward=FORWARDS[forward])
     prompts = np.stack([pkg.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=1000 + b) for b in range(batch)])
     toks = s.generate(prompts, n_gen)
     res = {"batch": batch, "prompt": n_prompt, "gen": n_gen, "tok_s": batch * n_gen / (s.gen_ms / 1e3),
@@ -351,6 +354,9 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=1)
     ap.add_argument("--decode-prompt", type=int, default=512)
     ap.add_argument("--decode-gen", type=int, default=128)
+    ap.add_argument("--decode-forward", default="session", choices=sorted(FORWARDS),
+                    help="which of the reference's copies of the forward the session reproduces "
+                         "(text_f32kv holds at most 512 positions)")
     ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv", "decode", "q4k"],
                     help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
@@ -401,13 +407,15 @@ def main():
             path = os.path.join(tempfile.gettempdir(), "rmi_qwen3_0_6b_seed0.gguf")
             if not os.path.exists(path):
                 pkg.synth.write_qwen3_gguf(path, cfg, pkg.synth.qwen3_tensors(cfg, 0))
-            res, _ = decode_bench(pkg, ctx, cfg, path, args.decode_batch, args.decode_prompt, args.decode_gen, sem)
+            res, _ = decode_bench(pkg, ctx, cfg, path, args.decode_batch, args.decode_prompt, args.decode_gen, sem,
+                                  args.decode_forward)
             kv = 28 * (args.decode_prompt + args.decode_gen // 2) * 1024 * 2 * 2
             roof = hbm_peak * 1e9 / (633233408 + args.decode_batch * kv) * args.decode_batch
             print(json.dumps({"metric": "Qwen3-0.6B-architecture greedy decode throughput", "value": res["tok_s"],
                               "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8", "data": "synthetic",
                               "config": {"workload": "configs[3]: decode", "batch": args.decode_batch,
-                                         "prompt": args.decode_prompt, "gen": args.decode_gen, "semantics": args.semantics},
+                                         "prompt": args.decode_prompt, "gen": args.decode_gen, "semantics": args.semantics,
+                                         "forward": args.decode_forward},
                               "roofline": {"bound": "hbm", "achieved": res["tok_s"], "peak": roof, "unit": "tok/s",
                                            "frac": res["tok_s"] / roof,
                                            "peak_source": f"copy bandwidth ({peak_kind}) / bytes per step (weights once + KV per sequence)"},
