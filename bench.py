@@ -349,7 +349,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--threads", type=int, default=0, help="CPU threads of the reference arm / cpu baseline (0 = all)")
-    ap.add_argument("--semantics", default="neon", choices=["neon", "scalar", "avx2"])
+    ap.add_argument("--semantics", default="avx2", choices=["neon", "scalar", "avx2"],
+                    help="which instruction-set variant of the reference the device reproduces (avx2 = an x86 host, "
+                         "the library default and what the reference arm runs)")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary figures (GEMV, decode)")
     ap.add_argument("--decode-batch", type=int, default=1)
     ap.add_argument("--decode-prompt", type=int, default=512)
@@ -476,6 +478,26 @@ def main():
     ms_total = float(ms.item())
     value = world * OPS_STEP * args.steps / (ms_total / 1e3) / 1e12
 
+    # AVX2 semantics: the same steps on the bit-exact CUDA-core kernels (rmi_set_prefill_exact), reported beside
+    exact = None
+    if sem == pkg.SEM_AVX2:
+        ctx.set_prefill_exact(True)
+        n_exact = max(3, min(args.steps, 2 * R))
+        for i in range(3):
+            step(i)
+        barrier()
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        x0.record(stream)
+        for i in range(n_exact):
+            step(i)
+        x1.record(stream)
+        barrier()
+        ctx.set_prefill_exact(False)
+        ms_x = x0.elapsed_time(x1) / n_exact
+        exact = {"value": OPS_STEP / (ms_x / 1e3) / 1e12, "unit": "TOPS", "ms_per_step": ms_x, "steps": n_exact,
+                 "what": "same FFN steps with rmi_set_prefill_exact(1): CUDA-core kernels that reproduce the reference's "
+                         "eight-lane AVX2 accumulation bit for bit (per GPU)"}
+
     # per-kernel timing of the same steps (second pass, events around the tagged launches)
     ksteps = min(args.steps, 2000)
     ctx.prof_enable(True)
@@ -554,6 +576,8 @@ def main():
                        f"({R * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB) rotated every step",
                        "int8_ops_per_step": OPS_STEP, "parallelism": f"replicas x{world}, no collective"},
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary()}
+    if exact is not None:
+        line["avx2_bit_exact_cuda_cores"] = exact
 
     if rank == 0 and world == 1:
         threads = args.threads or os.cpu_count() or 1

@@ -56,12 +56,18 @@ enum { RMI_GGML_F32 = 0, RMI_GGML_F16 = 1, RMI_GGML_Q4_0 = 2, RMI_GGML_Q8_0 = 8,
  *   AVX2   src/ops/quant/q8_0.rs:176-230 + src/ops/kernel/q8_0/avx2.rs:53-174
  *   NEON   src/ops/quant/q8_0.rs:75-165  + src/ops/kernel/q8_0/neon.rs:49-73
  *   SCALAR src/ops/quant/q8_0.rs:49-71   + src/ops/kernel/q8_0/scalar.rs:31-58
- * The tensor-core GEMM (M > 32) yields whole-block int32 sums, which is how the NEON and
- * SCALAR variants accumulate, so those two run on tcgen05.  The AVX2 variant accumulates
- * eight partial sums per block; under AVX2 every M stays on the CUDA-core kernels so that
- * the result remains bit-exact (slower for M > 32).  Element-wise steps (rms_norm, rope,
- * softmax, SiLU) follow the reference's portable x86 code under all three settings; exp()
- * is the correctly rounded f32 exponential. */
+ * Calls of up to 32 activation rows (decode) run memory-bound GEMV kernels and are bit-exact
+ * under all three settings.  Calls of more than 32 rows (prefill) run the tcgen05 int8 GEMM:
+ * one MMA per 32-block gives the exact int32 block sum, and the epilogue accumulates
+ * sum = fma(f32(dot), wd*xs, sum) per block -- bit for bit the NEON order, and with a separate
+ * multiply and add the SCALAR order.  The AVX2 variant accumulates eight partial sums per block
+ * (avx2.rs:96-153), an order the tensor core cannot deliver.  For it the GEMM keeps the AVX2
+ * quantizer (activation bytes and scale bits are those of q8_0.rs:176-230) and the exact block
+ * sums, and accumulates whole blocks: each matmul's f32 output is within 1e-5 (max |a-b| /
+ * max |ref|) of the eight-lane order on the same quantized input.  rmi_set_prefill_exact(ctx, 1)
+ * keeps AVX2 calls of every size on the bit-exact CUDA-core kernels instead (slower).
+ * Element-wise steps (rms_norm, rope, softmax, SiLU) follow the reference's portable x86 code
+ * under all three settings; exp() is the correctly rounded f32 exponential. */
 typedef enum { RMI_SEM_AVX2 = 0, RMI_SEM_NEON = 1, RMI_SEM_SCALAR = 2 } rmi_semantics;
 
 /* ---- context ------------------------------------------------------------------------
@@ -72,6 +78,10 @@ int32_t rmi_destroy(rmi_ctx* ctx);
 const char* rmi_last_error(void);
 int32_t rmi_set_semantics(rmi_ctx* ctx, int32_t sem);
 int32_t rmi_get_semantics(rmi_ctx* ctx, int32_t* sem);
+/* AVX2 semantics only (see above): on != 0 keeps calls of more than 32 rows on the CUDA-core kernels
+ * that reproduce matmul_q8_0_vs_q8_0_avx2 (src/ops/kernel/q8_0/avx2.rs:53-174) bit for bit; the
+ * default (0) runs them on the tensor cores. */
+int32_t rmi_set_prefill_exact(rmi_ctx* ctx, int32_t on);
 /* Use an existing cudaStream_t (e.g. the framework's current stream); NULL restores the
  * context's own stream. */
 int32_t rmi_set_stream(rmi_ctx* ctx, void* cuda_stream);
@@ -135,7 +145,8 @@ int32_t rmi_matmul_q8_0_prequantized_dev(rmi_ctx* ctx, const rmi_weight* w, cons
                                          const float* scales, size_t m, float* output,
                                          size_t row_begin, size_t row_end);
 /* Kernel::forward / forward_batched (src/ops/kernel/trait_.rs:57-109): per row quantize,
- * then the matmul.  m <= 32 runs the memory-bound GEMV kernels, m > 32 the tcgen05 GEMM. */
+ * then the matmul.  m <= 32 runs the memory-bound GEMV kernels (NEON / SCALAR: swapped-operand GEMM
+ * from 9 rows), m > 32 the tcgen05 GEMM. */
 int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
 int32_t rmi_matmul_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
                             float* output);

@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "librmi_oracle.so")
 
 SEM_AVX2, SEM_NEON, SEM_SCALAR = 0, 1, 2
+SEM_AVX2_BLOCK = 3   # x86 quantizer + whole-block accumulation: what the tensor-core GEMM computes for an x86 host
 EXP_LIBM, EXP_CR = 0, 1
 
 

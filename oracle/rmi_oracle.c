@@ -122,7 +122,7 @@ void orc_quantize_q8_0(const float* input, size_t n, uint8_t* q8, float* scales,
       float a = fabsf(v[i]);
       if (a > amax) amax = a;
     }
-    if (sem == ORC_SEM_AVX2) {
+    if (sem == ORC_SEM_AVX2 || sem == ORC_SEM_AVX2_BLOCK) {
       /* q8_0.rs:208-229: d = amax/127, id = 127/amax, round-to-nearest-even, clamp [-128,127] */
       float d = amax == 0.0f ? 0.0f : amax / 127.0f;
       float id = amax == 0.0f ? 0.0f : 127.0f / amax;
@@ -203,7 +203,7 @@ void orc_matmul_q8_0_range(const uint8_t* weight, const uint8_t* input_q8,
     float sum;
     if (sem == ORC_SEM_AVX2) {
       sum = q8_row_avx2(r, input_q8, input_scales, blocks);
-    } else if (sem == ORC_SEM_NEON) {
+    } else if (sem == ORC_SEM_NEON || sem == ORC_SEM_AVX2_BLOCK) {
       /* neon.rs:59-70: sum = fma(f32(dot), wd*xs[b], sum) */
       sum = 0.0f;
       for (size_t b = 0; b < blocks; b++) {
@@ -484,7 +484,7 @@ static void gemv_job_fn(void* p, size_t ith, size_t nth) {
 }
 
 static void quantize_any(const float* x, size_t n, uint8_t* q8, float* scales, int sem) {
-  if (sem == ORC_SEM_AVX2 && orc_quantize_q8_0_avx2_fast(x, n, q8, scales)) return;
+  if ((sem == ORC_SEM_AVX2 || sem == ORC_SEM_AVX2_BLOCK) && orc_quantize_q8_0_avx2_fast(x, n, q8, scales)) return;
   orc_quantize_q8_0(x, n, q8, scales, sem);
 }
 

@@ -32,7 +32,13 @@ extern "C" {
 enum {
   ORC_SEM_AVX2 = 0,   /* x86_64 production path  */
   ORC_SEM_NEON = 1,   /* aarch64 production path */
-  ORC_SEM_SCALAR = 2  /* portable fallback; also `--features parity-trace` quantizer */
+  ORC_SEM_SCALAR = 2, /* portable fallback; also `--features parity-trace` quantizer */
+  /* Not a variant of the reference: the x86 quantizer (src/ops/quant/q8_0.rs:176-230) followed by
+   * whole-block accumulation sum = fma(f32(dot32), wd*xs, sum) (the order of neon.rs:59-70).  It
+   * states what the device's tensor-core GEMM computes for an x86 host (exact int32 block sums,
+   * one f32 chain per output); its f32 results are within 1e-5 of ORC_SEM_AVX2, not bit-equal.
+   * Accepted by the Q8_0 quantizer, matmul and FFN entry points only. */
+  ORC_SEM_AVX2_BLOCK = 3
 };
 
 /* How exp() is evaluated inside softmax / SiLU. The reference calls the platform libm.

@@ -90,6 +90,10 @@ class Context:
     def set_semantics(self, sem: int):
         _check(lib().rmi_set_semantics(self._h, C.c_int32(sem)))
 
+    def set_prefill_exact(self, on: bool):
+        """AVX2 semantics: True keeps calls of more than 32 rows on the bit-exact CUDA-core kernels."""
+        _check(lib().rmi_set_prefill_exact(self._h, C.c_int32(1 if on else 0)))
+
     def semantics(self) -> int:
         v = C.c_int32()
         _check(lib().rmi_get_semantics(self._h, C.byref(v)))

@@ -166,6 +166,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->mem_bytes = prop.totalGlobalMem;
   c->smem_optin = prop.sharedMemPerBlockOptin;
   c->sem = RMI_SEM_AVX2;
+  c->prefill_exact = false;
   c->launches = 0;
   c->prof_on = false;
   c->pdl = false;
@@ -215,6 +216,12 @@ extern "C" int32_t rmi_set_semantics(rmi_ctx* ctx, int32_t sem) {
   RMI_TRY(rmi_check_ctx(ctx));
   RMI_REQUIRE(sem >= RMI_SEM_AVX2 && sem <= RMI_SEM_SCALAR, RMI_ERR_UNSUPPORTED, "unknown semantics %d", sem);
   ctx->sem = sem;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_set_prefill_exact(rmi_ctx* ctx, int32_t on) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  ctx->prefill_exact = on != 0;
   return RMI_OK;
 }
 
@@ -528,19 +535,22 @@ int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* cw, bool gate_up_inte
 constexpr size_t SWAP_AB_MAX_M = 96;
 
 static bool use_tensor_cores(const rmi_ctx* ctx, size_t m) {
-  // The tcgen05 path produces whole-block sums, which is how the NEON and scalar variants
-  // accumulate.  The AVX2 variant accumulates eight partial sums per block, so it stays on
-  // the CUDA-core kernels at every m to remain bit-exact.
-  static const bool disabled = getenv("RMI_DISABLE_TC") != nullptr;
-  static const size_t min_m = getenv("RMI_TC_MIN_M") ? (size_t)atoi(getenv("RMI_TC_MIN_M")) : 32;
-  return m > min_m && ctx->sem != RMI_SEM_AVX2 && !disabled;
+  // Prefill-shaped calls (m > 32) run on the tcgen05 GEMM.  It produces exact whole-block int32 sums
+  // and accumulates them as sum = fma(f32(dot), wd*xs, sum): bit-exact for the NEON and SCALAR
+  // variants of the reference.  The AVX2 variant accumulates eight partial sums per block
+  // (avx2.rs:96-153), which the tensor core cannot deliver; for it the GEMM keeps the AVX2 quantizer
+  // (activation bytes and scale bits unchanged), the exact block sums, and the whole-block chain,
+  // whose f32 result is within 1e-5 of the eight-lane order.  rmi_set_prefill_exact(ctx, 1) keeps
+  // AVX2 calls of every m on the bit-exact CUDA-core kernels instead.
+  return m > 32 && !(ctx->sem == RMI_SEM_AVX2 && ctx->prefill_exact);
 }
 
-// Plain matmuls (no fused epilogue) also take the tensor cores for 8 < m <= 32, with swapped operands.
+// Plain matmuls (no fused epilogue) also take the tensor cores for 8 < m <= 32, with swapped operands,
+// where that is bit-exact (NEON and SCALAR); AVX2 calls of m <= 32 stay on the GEMV kernels, so the
+// decode path is bit-exact under every setting.
 static bool matmul_on_tensor_cores(const rmi_ctx* ctx, size_t m) {
-  static const bool disabled = getenv("RMI_DISABLE_TC") != nullptr || getenv("RMI_DISABLE_SWAP_AB") != nullptr;
   if (use_tensor_cores(ctx, m)) return true;
-  return m > 8 && m <= SWAP_AB_MAX_M && ctx->sem != RMI_SEM_AVX2 && !disabled;
+  return m > 8 && m <= SWAP_AB_MAX_M && ctx->sem != RMI_SEM_AVX2;
 }
 
 extern "C" int32_t rmi_quantize_q8_0_dev(rmi_ctx* ctx, const float* x, size_t m, size_t n, uint8_t* q8,

@@ -80,6 +80,7 @@ struct rmi_ctx {
   cudaStream_t own_stream;
   cudaStream_t stream;
   int sem;
+  bool prefill_exact;  // AVX2 semantics: keep m > 32 on the bit-exact CUDA-core kernels
   std::atomic<uint64_t> launches;
   std::mutex mu;
   rmi_dev_status* d_status;  // device

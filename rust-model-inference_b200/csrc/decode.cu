@@ -270,6 +270,9 @@ __global__ void __launch_bounds__(256)
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
+  // Distributed shared memory of another CTA may only be touched once that CTA is known to run: every CTA
+  // arrives here and waits just before its first remote store (the staging below overlaps the barrier).
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const size_t b = blockIdx.y, kvh = blockIdx.x / CL;
   const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
   const int T = *d_step + 1;
@@ -345,6 +348,7 @@ __global__ void __launch_bounds__(256)
   }
   cp_async_wait<1>();
   __syncthreads();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // all CTAs of the cluster have started
 
   // scores[g][t] = f32(sum_f64 q*k) * kq_scale, sequential over the head dimension (dot.rs:115-118)
   for (size_t item = tid; item < (size_t)n_t * group; item += blockDim.x) {

@@ -316,7 +316,8 @@ __device__ __forceinline__ void mbar_arrive_a(uint32_t bar_addr) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
 }
 
-// NT: tile columns (32 or 64).  EPI: GEMM_EPI_*.  SEM: RMI_SEM_NEON or RMI_SEM_SCALAR.
+// NT: tile columns (32 or 64).  EPI: GEMM_EPI_*.  SEM: RMI_SEM_NEON, RMI_SEM_SCALAR, or RMI_SEM_AVX2 (x86
+// quantizer in the SwiGLU epilogue, whole-block fma accumulate).
 // Tensor memory holds two slab buffers of four K-blocks each (2 * 4 * NT columns): the MMA
 // warp fills one slab buffer (four MMAs, one commit) while the epilogue drains the other,
 // so barriers are exchanged once per 128-byte K slab instead of once per block.
@@ -502,11 +503,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
 #pragma unroll
               for (int c = 0; c < CPW / 2; c++) {
                 const uint64_t s2 = mul2(wsp[c], xs2);
-#ifdef RMI_GEMM_MAGIC_CVT
-                const uint64_t f2 = pack2(small_int_to_f32(d[j][2 * c]), small_int_to_f32(d[j][2 * c + 1]));
-#else
                 const uint64_t f2 = pack2(__int2float_rn(d[j][2 * c]), __int2float_rn(d[j][2 * c + 1]));
-#endif
                 if (SEM == RMI_SEM_SCALAR) {
                   // scalar.rs:55: separate multiply and add.  Written with scalar instructions: the
                   // packed mul/add pair did not reproduce the two roundings on the device.
@@ -620,7 +617,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
 template <int NT, int EPI>
 int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
   constexpr size_t smem = 1024 + STAGES * stage_layout<NT>::BYTES + (EPI == GEMM_EPI_SWIGLU_Q8 ? 128 * 65 * 4 : 0);
-  auto kern = ctx->sem == RMI_SEM_SCALAR ? gemm_tc_kernel<NT, EPI, RMI_SEM_SCALAR> : gemm_tc_kernel<NT, EPI, RMI_SEM_NEON>;
+  // SEM selects the accumulate (SCALAR: separate multiply and add; otherwise one fma per block) and the
+  // quantizer of the SwiGLU epilogue.  AVX2 = the x86 quantizer with the whole-block fma chain; only the
+  // SwiGLU epilogue quantizes, so the other epilogues share the NEON instantiation.
+  auto kern = ctx->sem == RMI_SEM_SCALAR ? gemm_tc_kernel<NT, EPI, RMI_SEM_SCALAR>
+              : (ctx->sem == RMI_SEM_AVX2 && EPI == GEMM_EPI_SWIGLU_Q8) ? gemm_tc_kernel<NT, EPI, RMI_SEM_AVX2>
+                                                                        : gemm_tc_kernel<NT, EPI, RMI_SEM_NEON>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed: %s", smem, cudaGetErrorString(e));
@@ -642,16 +644,12 @@ int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a) {
   const bool swiglu = a.epilogue == GEMM_EPI_SWIGLU_Q8;
   RMI_REQUIRE((swiglu ? w->d_umma_gu_q : w->d_umma_q) != nullptr, RMI_ERR_BAD_HANDLE,
               "tcgen05 weight layout was not built");
-  RMI_REQUIRE(ctx->sem != RMI_SEM_AVX2 || a.epilogue == GEMM_EPI_BLOCK_SUMS, RMI_ERR_UNSUPPORTED,
-              "the tcgen05 GEMM accumulates whole-block sums (NEON or SCALAR semantics)");
   if (a.swap_ab) {
     // small batches: the weight is the 128-row operand, the activation rows are the tile columns, so no
     // tensor-core or epilogue work is spent on padding rows; the result is stored transposed
     RMI_REQUIRE(a.epilogue == GEMM_EPI_F32 && a.col_begin == 0 && a.col_end == w->n_rows, RMI_ERR_UNSUPPORTED,
                 "swapped-operand GEMM: f32 output of all weight rows only");
     RMI_REQUIRE(w->d_umma_q != nullptr, RMI_ERR_BAD_HANDLE, "tcgen05 weight layout was not built");
-    RMI_REQUIRE(ctx->sem != RMI_SEM_AVX2, RMI_ERR_UNSUPPORTED,
-                "the tcgen05 GEMM accumulates whole-block sums (NEON or SCALAR semantics)");
     if (a.m == 0 || w->n_rows == 0) return RMI_OK;
     gemm_params p = {};
     p.a_img = w->d_umma_q;

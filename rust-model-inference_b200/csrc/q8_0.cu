@@ -791,8 +791,7 @@ static int32_t gemv_dispatch_mp(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
   const size_t blocks = w->n_in / 32;
   size_t t = 0;
   // largest pass whose staged activations fit in shared memory
-  static const size_t env_mp = getenv("RMI_GEMV_MAX_MP") ? (size_t)atoi(getenv("RMI_GEMV_MAX_MP")) : 8;
-  size_t max_mp = env_mp;
+  size_t max_mp = 8;
   while (max_mp > 1 && max_mp * (w->n_in + blocks * 4) > ctx->smem_optin - 1024) max_mp >>= 1;
   RMI_REQUIRE(w->n_in + blocks * 4 <= ctx->smem_optin - 1024, RMI_ERR_UNSUPPORTED,
               "n_in=%zu does not fit the GEMV activation staging buffer", w->n_in);

@@ -384,10 +384,10 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   s->forward = RMI_FORWARD_QWEN3_SESSION;
   s->k32_cache = s->v32_cache = nullptr;
-  s->seq_attention = attention_seq_eligible(s->d) && getenv("RMI_NO_SEQ_ATTENTION") == nullptr;
+  s->seq_attention = attention_seq_eligible(s->d);
   SESSION_ALLOC(s->q32, batch * nq * 4);
-  s->fused_norm = getenv("RMI_NO_FUSED_NORM") == nullptr;
-  s->fused_qk = batch <= 4 && getenv("RMI_NO_FUSED_QK") == nullptr;  // measured: a loss at batch 32
+  s->fused_norm = true;
+  s->fused_qk = batch <= 4;  // measured: a loss at batch 32
   for (const auto& l : model->layers) {
     s->fused_norm = s->fused_norm && q8_gemv_fused_norm_eligible(ctx, l.wqkv, batch) && q8_gemv_fused_norm_eligible(ctx, l.wgu, batch);
   }
@@ -497,7 +497,7 @@ static int32_t build_graphs(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
     RMI_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     // programmatic dependent launch along the step's kernel chain: the next kernel's weight copy
     // overlaps the tail of the current one.  Measured gain for small batches only (large grids lose).
-    ctx->pdl = s->d.batch <= 4 && getenv("RMI_NO_PDL") == nullptr;
+    ctx->pdl = s->d.batch <= 4;
     int32_t st = enqueue_step(ctx, s, n_prompt, n_gen, which == 1);
     ctx->pdl = false;
     cudaGraph_t g = nullptr;

@@ -44,6 +44,37 @@ def test_noalloc_matches_the_regular_entry_point_on_two_consecutive_calls(rmi):
     ctx.set_semantics(rmi.SEM_AVX2)
 
 
+@pytest.mark.parametrize("sem", ["SEM_NEON", "SEM_SCALAR"])
+def test_noalloc_equals_the_regular_entry_point_where_their_kernels_differ(rmi, sem):
+    """Whole-block semantics with 9..32 rows: the regular entry point runs the swapped-operand tensor-core
+    GEMM, the allocation-free one the GEMV.  Both must carry the oracle's bits.  The last case fills the
+    fixed array exactly (32 x 16384 = 524288 values)."""
+    from oracle import orc
+    ctx = rmi.context(0)
+    ctx.set_semantics(getattr(rmi, sem))
+    ctx.prof_enable(False)
+    try:
+        for n, k, m, seed in [(1000, 256, 16, 5), (384, 1024, 32, 6), (48, 16384, 32, 7)]:
+            wb = rmi.synth.q8_0_weight(n, k, seed=seed)
+            w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q8_0, k, n)
+            x = rmi.synth.normal((m, k), seed=seed + 50)
+            dx = _dev(ctx, x)
+            d_ref, d_new = ctx.dev_alloc(m * n * 4), ctx.dev_alloc(m * n * 4)
+            rmi.matmul_q8_0_dev(w, dx, m, d_ref)
+            rmi.matmul_q8_0_dev_noalloc(w, dx, m, d_new)
+            ref, got = np.zeros((m, n), np.float32), np.zeros((m, n), np.float32)
+            ctx.d2h(ref, d_ref)
+            ctx.d2h(got, d_new)
+            assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), (n, k, m)
+            want = orc.q8_forward_batched(wb, x, k, n, getattr(orc, sem), threads=4)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (n, k, m)
+            for p in (dx, d_ref, d_new):
+                ctx.dev_free(p)
+            w.free()
+    finally:
+        ctx.set_semantics(rmi.SEM_AVX2)
+
+
 def test_noalloc_rejects_sizes_beyond_the_fixed_array(rmi):
     ctx = rmi.context(0)
     w = rmi.QuantizedTensor.from_bytes(rmi.synth.q8_0_weight(16, 32768, seed=1), rmi.GGML_Q8_0, 32768, 16)
