@@ -11,7 +11,10 @@ prefill shape M=512, K=1024, n_ff=3072 (x -> quantize -> gate|up GEMM + SiLU*mul
             events on the launching stream
   cpu_baseline / --impl reference: the CPU oracle port of the reference's AVX2 path, timed on
             this box's host cores
-Secondary figures (GEMV GB/s, decode tok/s, Q4_K) are carried in "also" at N=1.
+Secondary figures (GEMV GB/s, decode tok/s, Q4_K, the 1-GPU times of the sharded sweep) are carried in
+"also" at N=1, each with the CPU oracle's time for the same work beside it.  With N > 1 GPUs the line also
+carries "sharded_sweep": BASELINE config 5 (W [32768, 8192] split by row across the ranks, every rank ends
+with the whole [M, 32768] result) per M, with each exchange, against the 1-GPU time measured in the same run.
 """
 from __future__ import annotations
 
@@ -142,10 +145,41 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem):
-    """GB/s of the decode GEMV with `copies` distinct weight buffers so every launch streams from HBM."""
+_WEIGHTS = {}
+
+
+def q8_weight_cached(pkg, n, k, seed=0):
+    """Synthetic Q8_0 weight bytes, generated once per (shape, seed) in this process."""
+    key = (n, k, seed)
+    if key not in _WEIGHTS:
+        _WEIGHTS[key] = pkg.synth.q8_0_weight(n, k, seed=seed)
+    return _WEIGHTS[key]
+
+
+def cpu_gemv(pkg, n, k, threads, m=1, budget_s=2.0):
+    """The oracle's AVX2 GEMV (quantize + row-partitioned matmul, all host threads) on the same shape."""
+    from oracle import orc
+    wb = q8_weight_cached(pkg, n, k)
+    x = pkg.synth.normal((m, k), seed=1)
+    orc.q8_forward_batched(wb, x, k, n, orc.SEM_AVX2, threads)
+    times, t_all = [], time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_all < budget_s and len(times) < 200):
+        t0 = time.perf_counter()
+        orc.q8_forward_batched(wb, x, k, n, orc.SEM_AVX2, threads)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    algo = n * (k // 32) * 34 + m * (k + (k // 32) * 4) + m * n * 4
+    return {"us": t * 1e6, "gbs": algo / t / 1e9, "cores": threads, "kind": "port",
+            "sample": f"{len(times)} calls of the C oracle's AVX2 path (quantize + GEMV, {threads} threads, rows split "
+                      f"ceil(n/threads) per thread; the reference's default is min(cores, 8) threads), median"}
+
+
+def gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, sem, min_ms=250.0, dependent_launch=False):
+    """GB/s of the decode GEMV with `copies` distinct weight buffers so every launch streams from HBM.  The timed
+    region is at least `min_ms` long (graph replays back to back).  dependent_launch: the GEMVs of the graph are
+    launched with programmatic stream serialization, so a GEMV's weight fetch overlaps its predecessor's tail."""
     ctx.set_semantics(sem)
-    wb = pkg.synth.q8_0_weight(n, k, seed=0)
+    wb = q8_weight_cached(pkg, n, k)
     ws = [pkg.QuantizedTensor.from_bytes(wb, pkg.GGML_Q8_0, k, n) for _ in range(copies)]
     x = torch.from_numpy(pkg.synth.normal((1, k), seed=1)).cuda()
     q8 = torch.empty(k, dtype=torch.uint8, device="cuda")
@@ -160,34 +194,49 @@ def gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem):
     for _ in range(3):
         burst()
     stream.synchronize()
-    mode = "stream"
-    graph = None
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            burst()
-        graph.replay()
-        stream.synchronize()
-        mode = "cuda-graph"
-    except Exception:
-        graph = None
-        ctx.set_stream(stream.cuda_stream)
+    # one launch alone, cold L2 (the weight copy used was last touched `copies` launches ago)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    lat = []
+    with torch.cuda.stream(stream):
+        for w in ws[:min(copies, 8)]:
+            e0.record(stream)
+            pkg.matmul_q8_0_prequantized_dev(w, q8.data_ptr(), sc.data_ptr(), 1, out.data_ptr())
+            e1.record(stream)
+            stream.synchronize()
+            lat.append(e0.elapsed_time(e1) * 1e3)
+    ctx.set_dependent_launch(dependent_launch)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        burst()
+    ctx.set_dependent_launch(False)
+    graph.replay()
+    stream.synchronize()
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            graph.replay()
+        e0.record(stream)
+        for _ in range(4):
+            graph.replay()
+        e1.record(stream)
+    stream.synchronize()
+    iters = max(3, int(min_ms / max(e0.elapsed_time(e1) / 4, 1e-3)) + 1)
     with torch.cuda.stream(stream):
         e0.record(stream)
         for _ in range(iters):
-            graph.replay() if graph is not None else burst()
+            graph.replay()
         e1.record(stream)
     stream.synchronize()
-    per = e0.elapsed_time(e1) / 1e3 / (iters * copies)
+    total_ms = e0.elapsed_time(e1)
+    per = total_ms / 1e3 / (iters * copies)
     algo = n * (k // 32) * 34 + k + (k // 32) * 4 + n * 4   # weights + pre-quantized x + y
     for w in ws:
         w.free()
     return {"shape": [n, k], "us_per_gemv": per * 1e6, "gbs": algo / per / 1e9, "algorithmic_bytes": algo,
-            "distinct_weight_copies": copies, "launch": mode}
+            "distinct_weight_copies": copies, "launch": "cuda-graph" + (" + dependent launch" if dependent_launch else ""),
+            "timed_ms": total_ms, "gemvs_timed": iters * copies, "single_launch_us_median": statistics.median(lat)}
 
 
-def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10):
+def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10, cpu_threads=0):
     """BASELINE config 3: W [4096, 4096] Q4_K, M in {1, 8, 256}; both reference paths (dequantize-and-matmul,
     Q4_K x Q8_K).  16 distinct weight copies (151 MB > L2) rotate inside one CUDA graph."""
     n = k = 4096
@@ -224,6 +273,27 @@ def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10):
                                    "tflops": 2.0 * m * n * k / per / 1e12, "algorithmic_bytes": algo}
     for w in ws:
         w.free()
+    if cpu_threads:
+        # CPU oracle beside it: Q4_KKernel::forward_prepared (Q8_K activation + vec_dot_q4k_q8k) and
+        # QuantizedLinear::forward_dequant, row-partitioned as the reference does; M > 1 = per-row loop,
+        # timed on a bounded sample of rows and scaled
+        from oracle import orc
+        xr = pkg.synth.normal((k,), seed=1)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 1.5 or reps < 2:
+            buf = np.zeros(n, np.float32)
+            for ith in range(1):
+                orc.q4k_forward_prepared(wb, xr, k, n, 0, 1, orc.SEM_AVX2, buf)
+            reps += 1
+        per_row_q8k = (time.perf_counter() - t0) / reps
+        t0 = time.perf_counter()
+        orc.q4k_forward_dequant(wb, n, k, xr)
+        per_row_deq = time.perf_counter() - t0
+        res["cpu_baseline"] = {"q8k_us_per_row": per_row_q8k * 1e6, "dequant_us_per_row": per_row_deq * 1e6, "cores": 1,
+                               "kind": "port",
+                               "sample": f"{reps} rows through the C oracle's Q4_K x Q8_K path and 1 row through its "
+                                         "dequantize-then-dot path, one thread; M rows cost M times this (per-row loop)"}
     return res
 
 
@@ -243,53 +313,66 @@ def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="sess
     return res, toks
 
 
-def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak):
-    """BASELINE config 5: W [32768, 8192] Q8_0 sharded by row across the ranks, x [M, 8192] replicated,
-    all-gather of [M, 32768] f32.  One JSON line with per-M device times (max over ranks)."""
+def cpu_decode(pkg, cfg, tensors, threads, n_prompt=8, n_gen=6):
+    """The oracle's Qwen3Session on host cores for a bounded sample (short prompt, a few generated tokens):
+    seconds per step, which is what a token costs the reference's CPU path at batch 1."""
+    from oracle import orc
+    model = orc.Qwen3(cfg, tensors)
+    prompt = pkg.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=1000)
+    model.generate(prompt[:2], 1, sem=orc.SEM_AVX2, threads=threads)   # page the weights in, start the pool
+    t0 = time.perf_counter()
+    model.generate(prompt, n_gen, sem=orc.SEM_AVX2, threads=threads)
+    dt = time.perf_counter() - t0
+    steps = n_prompt + n_gen - 1
+    return {"value": steps / dt, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{steps} steps ({n_prompt} prompt + {n_gen} generated tokens, positions 0..{steps - 1}) of the C "
+                      f"oracle's Qwen3Session, {threads} threads; one sequence (batch B costs B times this)"}
+
+
+def sharded_sweep(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak, ms=(1, 16, 256, 4096),
+                  cpu_threads=0):
+    """BASELINE config 5: W [32768, 8192] Q8_0 split by row across the ranks, x [M, 8192] replicated, every rank
+    ends with the whole [M, 32768] f32 result.  Per M, device times (CUDA events on the context's stream, max
+    over ranks): the 1-GPU matmul of the whole weight (every rank runs it alone on its own GPU), the local
+    shard, and the shard plus each exchange -- NCCL all-gather + un-shard, fused peer stores, copy-engine peer
+    copies overlapped with the matmul.  The results of all exchanges are compared bit for bit with the 1-GPU
+    result.  Library defaults: AVX2 semantics, m > 32 on the tensor cores."""
     n, k = 32768, 8192
-    ctx.set_semantics(pkg.SEM_NEON)
-    s, e = pkg.sharding.shard_rows(n, world, rank)
-    shard_bytes = pkg.synth.q8_0_weight_rows(n, k, seed=0, row_begin=s, row_end=e)
-    lin = pkg.sharding.ShardedLinear(pkg, shard_bytes, k, n, rank, world)
-    # fused variant: the matmul stores its columns into every rank's [M, N] buffer over peer pointers
-    peer = pkg.sharding.PeerShardedLinear(pkg, shard_bytes, k, n, rank, world, m_max=4096)
-    results = {}
-    for m in (1, 16, 256, 4096):
-        x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
-        out_local = torch.empty((m, n // world), dtype=torch.float32, device="cuda")
-        gathered = torch.empty((world, m, n // world), dtype=torch.float32, device="cuda")
-        out_full = torch.empty((m, n), dtype=torch.float32, device="cuda")
-        iters = max(3, min(args.steps, 50 if m <= 256 else 10))
-        times = {}
-        for mode in ("local", "gathered"):
-            with torch.cuda.stream(stream):
-                for _ in range(3):
-                    lin.forward_dev(x, out_local, gathered if mode == "gathered" else None, out_full)
-                if world > 1:
-                    dist.barrier()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for _ in range(iters):
-                    lin.forward_dev(x, out_local, gathered if mode == "gathered" else None, out_full)
-                e1.record(stream)
-                if world > 1:
-                    dist.barrier()
-                torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device="cuda")
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            times[mode] = float(t.item())
+    ctx.set_semantics(pkg.SEM_AVX2)
+    npr = n // world
+    s_row, e_row = pkg.sharding.shard_rows(n, world, rank)
+    shard_bytes = pkg.synth.q8_0_weight_rows(n, k, seed=0, row_begin=s_row, row_end=e_row)
+    if world > 1:
+        # the whole weight for the 1-GPU reference: all-gather of the shards' bytes
+        mine = torch.from_numpy(shard_bytes).cuda()
+        allb = torch.empty(world * mine.numel(), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(allb, mine)
+        full_bytes = allb.cpu().numpy()
+        del mine, allb
+    else:
+        full_bytes = shard_bytes
+    w_full = pkg.QuantizedTensor.from_bytes(full_bytes, pkg.GGML_Q8_0, k, n)
+    comm = None
+    if world > 1:
+        def bcast(obj):
+            box = [obj]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+        comm = pkg.NcclComm(ctx, world, rank, bcast)
+    lin = pkg.sharding.ShardedLinear(pkg, shard_bytes, k, n, rank, world, comm=comm) if world > 1 else None
+    peer = pkg.sharding.PeerShardedLinear(pkg, shard_bytes, k, n, rank, world, m_max=max(ms)) if world > 1 else None
+
+    def timed(fn, iters):
         with torch.cuda.stream(stream):
             for _ in range(3):
-                peer.forward_dev(x.data_ptr(), m)
+                fn()
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(iters):
-                peer.forward_dev(x.data_ptr(), m)
+                fn()
             e1.record(stream)
             torch.cuda.synchronize()
             ctx.check_status()
@@ -298,38 +381,98 @@ def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16
         t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        times["fused"] = float(t.item())
-        fused = np.empty((m, n), np.float32)
-        ctx.d2h(fused, peer.out_ptr)
-        same = bool(np.array_equal(fused.view(np.uint32), out_full.cpu().numpy().view(np.uint32)))
-        w_bytes = (n // world) * (k // 32) * 34
+        return float(t.item())
+
+    results = {}
+    for m in ms:
+        x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
+        ref_full = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        iters = max(3, min(args.steps, 50 if m <= 256 else 10))
         ops = 2.0 * m * k * n
-        results[f"M={m}"] = {"ms_local": times["local"], "ms_with_allgather": times["gathered"],
-                             "ms_fused_peer_stores": times["fused"], "fused_equals_allgather_bits": same,
-                             "per_gpu_weight_gbs": w_bytes / (times["local"] / 1e3) / 1e9,
-                             "frac_of_hbm_peak": w_bytes / (times["local"] / 1e3) / 1e9 / hbm_peak,
-                             "whole_job_tops": ops / (times["local"] / 1e3) / 1e12,
-                             "allgather_bytes_in_per_gpu": (world - 1) * m * (n // world) * 4}
-    peer.close()
+        r = {"ms_1gpu": timed(lambda: pkg.matmul_q8_0_dev(w_full, x.data_ptr(), m, ref_full.data_ptr()), iters)}
+        r["tops_1gpu"] = ops / (r["ms_1gpu"] / 1e3) / 1e12
+        r["weight_gbs_1gpu"] = n * (k // 32) * 34 / (r["ms_1gpu"] / 1e3) / 1e9
+        r["frac_of_hbm_peak_1gpu"] = r["weight_gbs_1gpu"] / hbm_peak
+        r["frac_of_int8_peak_1gpu"] = r["tops_1gpu"] / (2.0 * bf16_peak)
+        if world > 1:
+            out_local = torch.empty((m, npr), dtype=torch.float32, device="cuda")
+            gathered = torch.empty((world, m, npr), dtype=torch.float32, device="cuda")
+            out_full = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            r["ms_local_shard"] = timed(lambda: lin.forward_dev(x, out_local), iters)
+            r["ms_nccl_allgather"] = timed(lambda: lin.forward_dev(x, out_local, gathered, out_full), iters)
+            same = {"nccl_allgather": bool(torch.equal(out_full.view(torch.int32), ref_full.view(torch.int32)))}
+            for name, mode in (("fused_peer_stores", pkg.EXCHANGE_FUSED_STORES), ("peer_copy_overlapped", pkg.EXCHANGE_PEER_COPY)):
+                r["ms_" + name] = timed(lambda: peer.forward_dev(x.data_ptr(), m, mode), iters)
+                got = np.empty((m, n), np.float32)
+                ctx.d2h(got, peer.out_ptr)
+                same[name] = bool(np.array_equal(got.view(np.uint32), ref_full.cpu().numpy().view(np.uint32)))
+                if world > 1:
+                    dist.barrier()
+            best = min(("nccl_allgather", "fused_peer_stores", "peer_copy_overlapped"), key=lambda nm: r["ms_" + nm])
+            r["best_exchange"] = best
+            r["ms_best"] = r["ms_" + best]
+            r["speedup_vs_1gpu"] = r["ms_1gpu"] / r["ms_best"]
+            r["efficiency_vs_1gpu"] = r["ms_1gpu"] / (world * r["ms_best"])
+            r["whole_job_tops"] = ops / (r["ms_best"] / 1e3) / 1e12          # exchange included
+            r["frac_of_int8_peak_all_gpus"] = r["whole_job_tops"] / (world * 2.0 * bf16_peak)
+            r["per_gpu_weight_gbs"] = npr * (k // 32) * 34 / (r["ms_best"] / 1e3) / 1e9
+            r["frac_of_hbm_peak"] = r["per_gpu_weight_gbs"] / hbm_peak
+            r["exchange_bytes_in_per_gpu"] = (world - 1) * m * npr * 4
+            r["exchange_gbs_in_per_gpu"] = r["exchange_bytes_in_per_gpu"] / (max(r["ms_best"] - r["ms_local_shard"], 1e-6) / 1e3) / 1e9
+            r["bits_equal_1gpu_result"] = same
+        results[f"M={m}"] = r
+    _WEIGHTS[(n, k, 0)] = full_bytes   # the GEMV bandwidth leg and the CPU baseline use the same bytes
+    if cpu_threads and rank == 0:
+        results["cpu_baseline"] = cpu_gemv(pkg, n, k, cpu_threads)
+        results["cpu_baseline"]["what"] = "M=1 (one GEMV of the whole weight); M rows cost M times this (per-row loop)"
+    if peer is not None:
+        peer.close()
+    if comm is not None:
+        comm.destroy()
+    w_full.free()
+    return results
+
+
+def run_sharded(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak):
+    results = sharded_sweep(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak,
+                            cpu_threads=args.threads or os.cpu_count() or 1)
     if rank == 0:
-        print(json.dumps({"metric": "sharded Q8_0 GEMM sweep (N=32768,K=8192), rows split across GPUs + all-gather",
-                          "n_gpus": world, "scaling": "strong", "dtype": "int8", "data": "synthetic",
-                          "config": {"workload": "configs[4]: sharded Q8_0 GEMM sweep", "semantics": "neon"},
+        top = results["M=4096"]
+        print(json.dumps({"metric": "sharded Q8_0 GEMM sweep (N=32768,K=8192,M=4096): whole-job int8 throughput, exchange included",
+                          "value": top.get("whole_job_tops", top["tops_1gpu"]), "unit": "TOPS",
+                          "n_gpus": world, "scaling": "strong", "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+                          "config": {"workload": "configs[4]: sharded Q8_0 GEMM sweep", "semantics": "avx2"},
                           "results": results}), flush=True)
 
 
-def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
-    """The HBM-bound decode GEMVs on their own (configs[0] shape, the logits shape, the config-5 M=1 shape):
-    one JSON line, `roofline` for the logits GEMV."""
-    ctx.set_stream(stream.cuda_stream)
-    iters = max(10, min(args.steps, 50))
+GEMV_SHAPES = {"c1_3072x1024": (3072, 1024, 160, True), "logits_151936x1024": (151936, 1024, 4, False),
+               "c5_m1_32768x8192": (32768, 8192, 3, False)}
+
+
+def gemv_suite(pkg, ctx, torch, stream, hbm_peak, sems, cpu_threads):
+    """The HBM-bound decode GEMVs (configs[0] shape, the logits shape, the config-5 M=1 shape).  The small
+    configs[0] GEMV (3.3 MB, a few microseconds) is timed twice: launches fully serialised, and with
+    programmatic dependent launch inside the graph (how the decode step runs it)."""
     res = {}
-    for name, (n, k, copies) in {"c1_3072x1024": (3072, 1024, 160), "logits_151936x1024": (151936, 1024, 4),
-                                 "c5_m1_32768x8192": (32768, 8192, 3)}.items():
-        for sem_name, sem in (("avx2", pkg.SEM_AVX2), ("neon", pkg.SEM_NEON)):
-            r = gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, iters, sem)
+    for name, (n, k, copies, small) in GEMV_SHAPES.items():
+        for sem_name, sem in sems:
+            r = gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, sem)
             r["frac_of_hbm_peak"] = r["gbs"] / hbm_peak
             res[f"{name}_{sem_name}"] = r
+            if small:
+                r2 = gemv_bandwidth(pkg, ctx, torch, stream, n, k, copies, sem, dependent_launch=True)
+                r2["frac_of_hbm_peak"] = r2["gbs"] / hbm_peak
+                res[f"{name}_{sem_name}_dependent_launch"] = r2
+        if cpu_threads:
+            res[f"{name}_cpu_baseline"] = cpu_gemv(pkg, n, k, cpu_threads)
+    return res
+
+
+def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
+    """--workload gemv: one JSON line, `roofline` for the logits GEMV."""
+    ctx.set_stream(stream.cuda_stream)
+    res = gemv_suite(pkg, ctx, torch, stream, hbm_peak, (("avx2", pkg.SEM_AVX2), ("neon", pkg.SEM_NEON)),
+                     args.threads or os.cpu_count() or 1)
     top = res["logits_151936x1024_avx2"]
     print(json.dumps({"metric": "Q8_0 decode GEMV achieved HBM bandwidth (logits shape 151936x1024, M=1)",
                       "value": top["gbs"], "unit": "GB/s", "n_gpus": 1, "higher_is_better": True, "dtype": "int8",
@@ -337,7 +480,7 @@ def run_gemv(args, pkg, ctx, torch, stream, hbm_peak, peak_kind):
                       "roofline": {"bound": "hbm", "kernel": "q8_gemv_short_kernel<AVX2,16,1>", "achieved": top["gbs"],
                                    "peak": hbm_peak, "unit": "GB/s", "frac": top["gbs"] / hbm_peak,
                                    "peak_source": f"copy bandwidth, of {peak_kind}",
-                                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised under profiles/
+                                   # dram__bytes_read.sum + dram__bytes_write.sum of one launch in a committed ncu capture
                                    "traffic": 169306000},
                       "results": res}), flush=True)
 
@@ -377,7 +520,9 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a rank that fails must not leave the others waiting for the default ten minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
     ctx = pkg.context(local_rank)
     sem = {"neon": pkg.SEM_NEON, "scalar": pkg.SEM_SCALAR, "avx2": pkg.SEM_AVX2}[args.semantics]
     ctx.set_semantics(sem)
@@ -516,9 +661,9 @@ def main():
                     "frac_of_bf16_peak": achieved / bf16_peak, "avg_kernel_us": ms_k / n_k * 1e3, "launches": n_k,
                     "down_gemm_avg_us": (ms_d / n_d * 1e3) if n_d else None,
                     "down_gemm_tops": (OPS_DOWN / (ms_d / n_d / 1e3) / 1e12) if n_d else None,
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from
-                    # the committed ncu capture summarised under profiles/; algorithmic bytes 7.65 MB
-                    "traffic": 7703552, "traffic_source": "ncu --set full capture of one launch, summary under profiles/"}
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload in a
+                    # committed ncu capture (a constant, not measured by this run); algorithmic bytes 7.65 MB
+                    "traffic": 7703552, "traffic_source": "constant from an ncu capture of one launch of this kernel on this workload"}
     else:   # AVX2 semantics keep every M on the CUDA-core kernels
         n_g, ms_g = ctx.prof_read("q8_gemv")
         roofline = {"bound": "tensor", "kernel": "q8_gemv_kernel (CUDA cores; AVX2 semantics)", "achieved": value,
@@ -578,6 +723,16 @@ def main():
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary()}
     if exact is not None:
         line["avx2_bit_exact_cuda_cores"] = exact
+    if world > 1:
+        # BASELINE config 5 across these GPUs (strong scaling, the one exchange of the path)
+        try:
+            ctx.set_stream(stream.cuda_stream)
+            sweep = sharded_sweep(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf16_peak)
+            line["sharded_sweep"] = {"workload": "configs[4]: W [32768, 8192] Q8_0 split by row across the GPUs, x [M, 8192] "
+                                                 "replicated, whole [M, 32768] f32 result on every GPU", "scaling": "strong",
+                                     "semantics": "avx2", "n_gpus": world, "results": sweep}
+        except Exception as ex:
+            line["sharded_sweep"] = {"error": repr(ex)}
 
     if rank == 0 and world == 1:
         threads = args.threads or os.cpu_count() or 1
@@ -589,30 +744,36 @@ def main():
             also = {}
             try:
                 ctx.set_stream(stream.cuda_stream)
-                also["gemv_c1_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 3072, 1024, 160, 10, pkg.SEM_AVX2)
-                also["gemv_logits_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 151936, 1024, 4, 10, pkg.SEM_AVX2)
-                also["gemv_c5_m1_avx2"] = gemv_bandwidth(pkg, ctx, torch, stream, 32768, 8192, 3, 10, pkg.SEM_AVX2)
-                for k_ in list(also):
-                    also[k_]["frac_of_hbm_peak"] = also[k_]["gbs"] / hbm_peak
-                also["hbm_peak_gbs"] = hbm_peak
+                # config 5 on one GPU (the 1-GPU column of the sharded sweep), with the CPU's GEMV beside it
+                also["sharded_c5_1gpu"] = sharded_sweep(args, pkg, ctx, torch, dist, 0, 1, stream, hbm_peak, bf16_peak,
+                                                        cpu_threads=threads)
             except Exception as ex:   # secondary figures never break the headline line
+                also["sharded_error"] = repr(ex)
+            try:
+                ctx.set_stream(stream.cuda_stream)
+                also.update({"gemv_" + k_: v for k_, v in
+                             gemv_suite(pkg, ctx, torch, stream, hbm_peak, (("avx2", pkg.SEM_AVX2),), threads).items()})
+                also["hbm_peak_gbs"] = hbm_peak
+            except Exception as ex:
                 also["gemv_error"] = repr(ex)
             try:
-                also["q4_k_4096x4096"] = q4k_bench(pkg, ctx, torch, stream, hbm_peak)
+                also["q4_k_4096x4096"] = q4k_bench(pkg, ctx, torch, stream, hbm_peak, cpu_threads=threads)
             except Exception as ex:
                 also["q4k_error"] = repr(ex)
             try:
                 ctx.set_stream(None)
                 cfg = dict(pkg.synth.QWEN3_0_6B)
                 path = os.path.join(tempfile.gettempdir(), "rmi_qwen3_0_6b_seed0.gguf")
+                tensors = pkg.synth.qwen3_tensors(cfg, 0)
                 if not os.path.exists(path):
-                    pkg.synth.write_qwen3_gguf(path, cfg, pkg.synth.qwen3_tensors(cfg, 0))
+                    pkg.synth.write_qwen3_gguf(path, cfg, tensors)
                 for b in (1, 32):
                     res, _ = decode_bench(pkg, ctx, cfg, path, b, 512, 128, pkg.SEM_AVX2)
                     kv = 28 * (512 + 64) * 1024 * 2 * 2
                     res["roofline_tok_s"] = hbm_peak * 1e9 / (633233408 + b * kv) * b
                     res["frac_of_roofline"] = res["tok_s"] / res["roofline_tok_s"]
                     also[f"decode_qwen3_0_6b_b{b}_avx2"] = res
+                also["decode_cpu_baseline"] = cpu_decode(pkg, cfg, tensors, threads)
             except Exception as ex:
                 also["decode_error"] = repr(ex)
             line["also"] = also

@@ -86,6 +86,13 @@ int32_t rmi_set_prefill_exact(rmi_ctx* ctx, int32_t on);
  * context's own stream. */
 int32_t rmi_set_stream(rmi_ctx* ctx, void* cuda_stream);
 int32_t rmi_sync(rmi_ctx* ctx);
+/* on != 0: the decode-shaped kernels (GEMVs, norm/quantize, attention, SiLU) are launched with programmatic
+ * stream serialization: a kernel may start while its predecessor in the stream drains, fetches what no
+ * earlier kernel writes (its weights), and waits (griddepcontrol.wait) before it touches anything else.
+ * Results are unchanged; chains of small dependent kernels run closer together.  Off by default; the
+ * decode session turns it on for its own captured step.  The reference's counterpart is the absence of
+ * a launch gap between operators inside one thread-pool dispatch (src/core/thread_pool.rs:119-161). */
+int32_t rmi_set_dependent_launch(rmi_ctx* ctx, int32_t on);
 /* sm count, L2 bytes, total device memory */
 int32_t rmi_device_info(rmi_ctx* ctx, int32_t* sm_count, size_t* l2_bytes, size_t* mem_bytes);
 /* Number of kernels this library has launched on this context (for launch accounting). */
@@ -332,13 +339,67 @@ int32_t rmi_ipc_close(rmi_ctx* ctx, void* ptr);
  * flags[rank] is this rank's own, the others are IPC mappings).  Enqueues a kernel that writes
  * `epoch` into slot `rank` of every array after all earlier stores of this stream, then waits
  * until all slots of its own array reached `epoch`.  Epochs must increase by one per round.
- * The wait gives up after two seconds and records RMI_ERR_TIMEOUT in the context's device
- * status, which rmi_check_status reports.  Every rank must run on its own GPU. */
+ * The wait gives up after the context's wait limit (two seconds unless rmi_set_wait_limit_ms changed
+ * it) and records RMI_ERR_TIMEOUT in the context's device status, which rmi_check_status reports.
+ * Every rank must run on its own GPU. */
 int32_t rmi_peer_signal_wait_dev(rmi_ctx* ctx, uint32_t* const* flags, int32_t world, int32_t rank,
                                  uint32_t epoch);
 /* Synchronises the stream and returns RMI_ERR_TIMEOUT if a device-side wait gave up since the
  * last check (the `_dev` entry points return before their kernels finish). */
 int32_t rmi_check_status(rmi_ctx* ctx);
+/* Time limit of every bounded device-side wait of this context (flag rounds between ranks, the GEMM's
+ * barrier waits): 1..60000 ms, default 2000.  The reference's only wait of this kind, the thread pool's
+ * spin barrier (src/core/thread_pool.rs:136-157), has no limit. */
+int32_t rmi_set_wait_limit_ms(rmi_ctx* ctx, uint32_t ms);
+
+/* ---- row-sharded matmul with its exchange (one context per GPU, ranks on one node) ----------------
+ * The multi-GPU form of matmul_q8_0_quantized_parallel_rows (src/ops/kernel/q8_0/parallel.rs:102-139):
+ * rank r of `world` holds weight rows [r*n_out/world, (r+1)*n_out/world) (rmi_weight_upload with that
+ * row range, the PlacementSlice::Rows of src/format/load_plan.rs:19-22), x is replicated, and every
+ * rank ends up with the whole row-major y [m, n_out] in its own result buffer.
+ *   rmi_shard_group_create   allocates this rank's two result buffers [m_max, n_out] (they alternate
+ *                            by round) and its flag array
+ *   rmi_shard_group_export   192 bytes of CUDA IPC handles to send to every other rank
+ *   rmi_shard_group_connect  all ranks' handles, 192 bytes each, ordered by rank (the own entry is
+ *                            ignored); maps the peers' buffers.  All ranks must have connected before
+ *                            the first matmul (a host-side barrier).
+ *   rmi_matmul_q8_0_sharded_dev  x [m, n_in] on the device; enqueues the shard's matmul and the exchange
+ *                            and returns this round's result buffer, complete once the enqueued work
+ *                            has run.  RMI_EXCHANGE_FUSED_STORES: the matmul's epilogue stores its
+ *                            columns into every rank's buffer over NVLink (best for small m);
+ *                            RMI_EXCHANGE_PEER_COPY: m is cut into slabs of rows and the copy engines
+ *                            push slab i to the peers while slab i+1 is computed (best for large m).
+ *                            All ranks must make the same sequence of calls.  Reads of round k's
+ *                            result must be enqueued on the context's stream before round k+1 is
+ *                            called; the buffer is then safe until round k+2 is called.  A rank that
+ *                            does not show up makes the others' flag wait run out:
+ *                            rmi_check_status reports RMI_ERR_TIMEOUT.
+ *   rmi_shard_group_free     after a host-side barrier (no peer may still be writing). */
+typedef struct rmi_shard_group rmi_shard_group;
+enum { RMI_EXCHANGE_FUSED_STORES = 0, RMI_EXCHANGE_PEER_COPY = 1 };
+int32_t rmi_shard_group_create(rmi_ctx* ctx, int32_t world, int32_t rank, size_t n_out, size_t m_max,
+                               rmi_shard_group** out);
+int32_t rmi_shard_group_export(rmi_ctx* ctx, const rmi_shard_group* g, uint8_t* handles192);
+int32_t rmi_shard_group_connect(rmi_ctx* ctx, rmi_shard_group* g, const uint8_t* all_handles);
+int32_t rmi_shard_group_epoch(const rmi_shard_group* g, uint32_t* epoch);
+int32_t rmi_matmul_q8_0_sharded_dev(rmi_ctx* ctx, rmi_shard_group* g, const rmi_weight* w_shard, const float* x,
+                                    size_t m, int32_t exchange, float** result);
+int32_t rmi_shard_group_free(rmi_ctx* ctx, rmi_shard_group* g);
+
+/* The NCCL form of the same exchange: all-gather of every rank's y_local [m, n_per_rank] (device) with the
+ * caller's communicator (an ncclComm_t), then the un-shard into out [m, world * n_per_rank], enqueued on
+ * the context's stream.  `gathered` is a device staging buffer of world*m*n_per_rank floats (may be null
+ * for m == 1, where the shards are already contiguous pieces of the result).  NCCL is resolved at run
+ * time from the libnccl.so.2 the process has loaded.  No counterpart in the reference (its devices are
+ * planned, src/format/load_plan.rs:208-330, never executed). */
+int32_t rmi_allgather_cols_dev(rmi_ctx* ctx, void* nccl_comm, const float* y_local, size_t m, size_t n_per_rank,
+                               int32_t world, float* gathered, float* out);
+/* For hosts without a communicator of their own: rank 0 obtains a 128-byte id (ncclGetUniqueId), sends it
+ * to the other ranks by any means, and every rank creates its communicator (ncclCommInitRank on the
+ * context's device). */
+int32_t rmi_nccl_unique_id(uint8_t* id128);
+int32_t rmi_nccl_comm_create(rmi_ctx* ctx, const uint8_t* id128, int32_t world, int32_t rank, void** comm);
+int32_t rmi_nccl_comm_destroy(void* comm);
 
 #ifdef __cplusplus
 }

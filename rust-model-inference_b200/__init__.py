@@ -140,6 +140,14 @@ class Context:
     def d2h(self, dst: np.ndarray, src: int):
         _check(lib().rmi_d2h(self._h, _p(dst), C.c_void_p(src), _sz(dst.nbytes)))
 
+    def set_dependent_launch(self, on: bool):
+        """Programmatic dependent launch for chains of decode-shaped kernels (see rmi_set_dependent_launch)."""
+        _check(lib().rmi_set_dependent_launch(self._h, C.c_int32(1 if on else 0)))
+
+    def set_wait_limit_ms(self, ms: int):
+        """Time limit of the bounded device-side waits (flag rounds, GEMM barriers); default 2000 ms."""
+        _check(lib().rmi_set_wait_limit_ms(self._h, C.c_uint32(ms)))
+
     def check_status(self):
         """Synchronise and raise RMI_ERR_TIMEOUT if a device-side wait gave up."""
         _check(lib().rmi_check_status(self._h))
@@ -577,6 +585,74 @@ def peer_signal_wait_dev(ctx: Context, flag_ptrs, rank: int, epoch: int):
     arr = (C.c_void_p * len(flag_ptrs))(*[C.c_void_p(p) for p in flag_ptrs])
     _check(lib().rmi_peer_signal_wait_dev(ctx.handle, arr, C.c_int32(len(flag_ptrs)), C.c_int32(rank),
                                           C.c_uint32(epoch & 0xffffffff)))
+
+
+EXCHANGE_FUSED_STORES, EXCHANGE_PEER_COPY = 0, 1
+
+
+class ShardGroup:
+    """rmi_shard_group: one rank's result buffers and flags of a row-sharded matmul, and the peers' mappings."""
+
+    def __init__(self, ctx: Context, world: int, rank: int, n_out: int, m_max: int):
+        self._ctx, self.world, self.rank, self.n_out, self.m_max = ctx, world, rank, n_out, m_max
+        self._h = C.c_void_p()
+        _check(lib().rmi_shard_group_create(ctx.handle, C.c_int32(world), C.c_int32(rank), _sz(n_out), _sz(m_max),
+                                            C.byref(self._h)))
+
+    def export(self) -> bytes:
+        buf = (C.c_uint8 * 192)()
+        _check(lib().rmi_shard_group_export(self._ctx.handle, self._h, buf))
+        return bytes(buf)
+
+    def connect(self, handles_by_rank: list):
+        blob = b"".join(handles_by_rank)
+        if len(blob) != 192 * self.world:
+            raise ValueError("need one 192-byte handle block per rank")
+        buf = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        _check(lib().rmi_shard_group_connect(self._ctx.handle, self._h, buf))
+
+    @property
+    def epoch(self) -> int:
+        v = C.c_uint32()
+        _check(lib().rmi_shard_group_epoch(self._h, C.byref(v)))
+        return v.value
+
+    def matmul_dev(self, w_shard: "QuantizedTensor", x_ptr: int, m: int, exchange: int = EXCHANGE_FUSED_STORES) -> int:
+        """-> device pointer of this round's [m, n_out] result (complete once the enqueued work has run)."""
+        out = C.c_void_p()
+        _check(lib().rmi_matmul_q8_0_sharded_dev(self._ctx.handle, self._h, w_shard._h, C.c_void_p(x_ptr), _sz(m),
+                                                 C.c_int32(exchange), C.byref(out)))
+        return out.value
+
+    def free(self):
+        if self._h:
+            _check(lib().rmi_shard_group_free(self._ctx.handle, self._h))
+            self._h = C.c_void_p()
+
+
+class NcclComm:
+    """An NCCL communicator created through the library (rmi_nccl_*): rank 0 draws the id, `bcast(id_or_None)`
+    returns rank 0's id on every rank (e.g. a torch.distributed object broadcast)."""
+
+    def __init__(self, ctx: Context, world: int, rank: int, bcast):
+        buf = (C.c_uint8 * 128)()
+        if rank == 0:
+            _check(lib().rmi_nccl_unique_id(buf))
+        ident = bcast(bytes(buf) if rank == 0 else None)
+        buf = (C.c_uint8 * 128).from_buffer_copy(ident)
+        self._ctx, self.world, self.rank = ctx, world, rank
+        self._h = C.c_void_p()
+        _check(lib().rmi_nccl_comm_create(ctx.handle, buf, C.c_int32(world), C.c_int32(rank), C.byref(self._h)))
+
+    def allgather_cols_dev(self, y_local_ptr: int, m: int, n_per_rank: int, gathered_ptr: int, out_ptr: int):
+        _check(lib().rmi_allgather_cols_dev(self._ctx.handle, self._h, C.c_void_p(y_local_ptr), _sz(m), _sz(n_per_rank),
+                                            C.c_int32(self.world), C.c_void_p(gathered_ptr or 0), C.c_void_p(out_ptr)))
+
+    def destroy(self):
+        if self._h:
+            self._ctx.sync()
+            _check(lib().rmi_nccl_comm_destroy(self._h))
+            self._h = C.c_void_p()
 
 
 def quantize_row_q8_k(x, ctx: Context | None = None):

@@ -56,7 +56,7 @@ int32_t rmi_check_dev_status(rmi_ctx* ctx, const char* what) {
   if (ctx->h_status->code != 0) {
     rmi_set_error("%s: device-side wait gave up (site %d, detail %d)", what, ctx->h_status->where,
                   ctx->h_status->detail);
-    RMI_CUDA_CHECK(cudaMemsetAsync(ctx->d_status, 0, sizeof(rmi_dev_status), ctx->stream));
+    RMI_CUDA_CHECK(cudaMemsetAsync(ctx->d_status, 0, RMI_STATUS_CLEAR_BYTES, ctx->stream));
     return RMI_ERR_TIMEOUT;
   }
   return RMI_OK;
@@ -167,6 +167,7 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   c->smem_optin = prop.sharedMemPerBlockOptin;
   c->sem = RMI_SEM_AVX2;
   c->prefill_exact = false;
+  c->wait_limit_ns = 2000000000ull;
   c->launches = 0;
   c->prof_on = false;
   c->pdl = false;
@@ -179,7 +180,8 @@ extern "C" int32_t rmi_init(int32_t device, rmi_ctx** out) {
   if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&c->d_status, sizeof(rmi_dev_status)) != cudaSuccess ||
       cudaMallocHost(&c->h_status, sizeof(rmi_dev_status)) != cudaSuccess ||
-      cudaMemset(c->d_status, 0, sizeof(rmi_dev_status)) != cudaSuccess) {
+      cudaMemset(c->d_status, 0, sizeof(rmi_dev_status)) != cudaSuccess ||
+      cudaMemcpy(&c->d_status->limit_ns, &c->wait_limit_ns, 8, cudaMemcpyHostToDevice) != cudaSuccess) {
     rmi_set_error("context setup failed: %s", cudaGetErrorString(cudaGetLastError()));
     delete c;
     return RMI_ERR_CUDA;
@@ -222,6 +224,23 @@ extern "C" int32_t rmi_set_semantics(rmi_ctx* ctx, int32_t sem) {
 extern "C" int32_t rmi_set_prefill_exact(rmi_ctx* ctx, int32_t on) {
   RMI_TRY(rmi_check_ctx(ctx));
   ctx->prefill_exact = on != 0;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_set_dependent_launch(rmi_ctx* ctx, int32_t on) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->pdl = on != 0;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_set_wait_limit_ms(rmi_ctx* ctx, uint32_t ms) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_REQUIRE(ms >= 1 && ms <= 60000, RMI_ERR_BAD_SHAPE, "wait limit must be within 1..60000 ms, got %u", ms);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  ctx->wait_limit_ns = (uint64_t)ms * 1000000ull;
+  RMI_CUDA_CHECK(cudaMemcpy(&ctx->d_status->limit_ns, &ctx->wait_limit_ns, 8, cudaMemcpyHostToDevice));
   return RMI_OK;
 }
 
@@ -623,8 +642,8 @@ extern "C" int32_t rmi_matmul_q8_0_prequantized(rmi_ctx* ctx, const rmi_weight* 
 }
 
 // dout: [m][out_stride] f32, the weight's rows land in columns [0, n_rows); out_stride 0 = n_rows
-static int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float* dx, size_t m, float* dout,
-                                  size_t out_stride = 0) {
+int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float* dx, size_t m, float* dout,
+                           size_t out_stride) {
   const size_t blocks = w->n_in / 32;
   if (out_stride == 0) out_stride = w->n_rows;
   if (matmul_on_tensor_cores(ctx, m)) {
@@ -761,8 +780,8 @@ extern "C" int32_t rmi_q8_0_block_sums(rmi_ctx* ctx, const rmi_weight* w, const 
 
 // ---------------------------------------------------------------- fused SwiGLU FFN
 
-static int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight* wd, const float* dx, size_t m,
-                          float* dout) {
+int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight* wd, const float* dx, size_t m,
+                   float* dout) {
   const size_t n_embd = wgu->n_in, n_ff = wgu->n_rows / 2;
   RMI_REQUIRE(wgu->n_rows_a * 2 == wgu->n_rows && wgu->n_rows_a > 0, RMI_ERR_BAD_SHAPE,
               "w_gate_up must be rmi_weight_fuse_vstack(gate, up) of equal row counts");
@@ -937,5 +956,5 @@ extern "C" int32_t rmi_unshard_cols_dev(rmi_ctx* ctx, const float* gathered, siz
                                         float* out) {
   RMI_TRY(rmi_check_ctx(ctx));
   RMI_REQUIRE(gathered && out, RMI_ERR_BAD_HANDLE, "rmi_unshard_cols_dev: null buffer");
-  return launch_unshard_cols(ctx, gathered, g, m, npr, out);
+  return launch_unshard_cols_vec(ctx, gathered, g, m, npr, out);
 }

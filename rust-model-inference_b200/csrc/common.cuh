@@ -55,7 +55,9 @@ struct rmi_dev_status {
   int32_t where;   // site id of the wait that gave up
   int32_t detail;  // e.g. tile index
   int32_t pad;
+  unsigned long long limit_ns;  // time limit of a bounded wait; written by the host, kept across clears
 };
+static constexpr size_t RMI_STATUS_CLEAR_BYTES = 16;  // code, where, detail, pad
 
 struct rmi_prof_rec {
   const char* tag;
@@ -81,6 +83,7 @@ struct rmi_ctx {
   cudaStream_t stream;
   int sem;
   bool prefill_exact;  // AVX2 semantics: keep m > 32 on the bit-exact CUDA-core kernels
+  uint64_t wait_limit_ns;  // time limit of every bounded device-side wait (default 2 s)
   std::atomic<uint64_t> launches;
   std::mutex mu;
   rmi_dev_status* d_status;  // device

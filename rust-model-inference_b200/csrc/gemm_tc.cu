@@ -23,7 +23,7 @@
 // The kernel is persistent: one CTA per SM walks the output tiles, the barrier phases run on
 // across tiles, so the bulk copies and MMAs of the next tile overlap the tail of the current one.
 //
-// Every wait is bounded: after two seconds of failed polls a role records a site id in the
+// Every wait is bounded: after the context's wait limit (two seconds by default) of failed polls a role records a site id in the
 // context's status word, raises a shared abort flag that all other waits observe, and the
 // CTA falls through to the common teardown (TMEM is always deallocated).
 #include "common.cuh"
@@ -35,7 +35,6 @@ constexpr int STAGES = 4;
 constexpr int SLAB_BYTES_A = 128 * 128;  // 128 rows x 128 B of K
 constexpr int NBUF = 4;
 constexpr uint32_t WAIT_LIMIT = 1u << 26;
-constexpr uint64_t WAIT_NS = 2000000000ull;  // 2 s
 
 struct gemm_params {
   const uint8_t* a_img;
@@ -94,28 +93,6 @@ __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
-}
-
-// Bounded wait: gives up after WAIT_NS of wall time (or WAIT_LIMIT polls).  Returns false when
-// the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          rmi_dev_status* status, int site, int detail) {
-  uint64_t t0 = 0;
-  for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 15) == 15) {
-      if (*abort_flag) return false;
-      const uint64_t now = global_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_NS) break;
-    }
-  }
-  *abort_flag = 1;
-  if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
-    status->where = site;
-    status->detail = detail;
-  }
-  return false;
 }
 
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
@@ -271,6 +248,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t parity, 
   // The common case is a phase that completes during the first suspended tries: the global timer (a slow
   // read) and the abort flag are only consulted after every eighth failed try.
   uint64_t t0 = 0;
+  const uint64_t limit_ns = status->limit_ns;
   for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
     uint32_t ok;
     asm volatile(
@@ -285,7 +263,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar_addr, uint32_t parity, 
       if (*abort_flag) return false;
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_NS) break;
+      else if (now - t0 > limit_ns) break;
     }
   }
   *abort_flag = 1;

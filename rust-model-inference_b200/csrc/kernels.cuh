@@ -40,6 +40,17 @@ struct gemm_tc_args {
 int32_t launch_gemm_tc(rmi_ctx* ctx, const gemm_tc_args& a);
 int32_t ensure_umma_layout(rmi_ctx* ctx, const rmi_weight* w, bool gate_up_interleaved = false);
 
+// api.cu: quantize + matmul / fused FFN on device buffers (caller holds ctx->mu); dout [m][out_stride],
+// out_stride 0 = n_rows.  Uses the context's scratch slots 0..4.
+int32_t matmul_q8_0_device(rmi_ctx* ctx, const rmi_weight* w, const float* dx, size_t m, float* dout,
+                           size_t out_stride = 0);
+int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight* wd, const float* dx, size_t m, float* dout);
+
+// peer.cu: writes `epoch` into slot `rank` of every flag array, then waits (at most ctx->wait_limit_ns) until
+// all `world` slots of flags[rank] reached it; on `stream`
+int32_t launch_peer_signal_wait(rmi_ctx* ctx, cudaStream_t stream, uint32_t* const* flags, int world, int rank,
+                                uint32_t epoch);
+
 // embedding lookups (q8_0.cu, q4_0.cu, q6k.cu): ids and out on the device
 int32_t launch_q8_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out);
 int32_t launch_q4_0_embedding(rmi_ctx* ctx, const rmi_weight* w, const uint32_t* ids, size_t m, float* out);
@@ -64,6 +75,9 @@ int32_t launch_q4k_q8k_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* d8
                               size_t m, float* out, size_t row_begin, size_t row_end);
 int32_t launch_q4k_dequant_matmul(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* out);
 int32_t launch_q4k_dequantize(rmi_ctx* ctx, const rmi_weight* w, float* out);
+
+// sharded.cu: 16-byte vectorised variant (falls back to the scalar kernel for unaligned shapes)
+int32_t launch_unshard_cols_vec(rmi_ctx* ctx, const float* gathered, size_t g, size_t m, size_t npr, float* out);
 
 // decode.cu
 int32_t launch_unshard_cols(rmi_ctx* ctx, const float* gathered, size_t g, size_t m, size_t npr, float* out);

@@ -16,9 +16,8 @@ struct peer_flags {
   uint32_t* p[RMI_MAX_FANOUT];
 };
 
-constexpr uint64_t PEER_WAIT_NS = 2000000000ull;  // 2 s
-
-__global__ void peer_signal_wait_kernel(peer_flags flags, int world, int rank, uint32_t epoch, rmi_dev_status* status) {
+__global__ void peer_signal_wait_kernel(peer_flags flags, int world, int rank, uint32_t epoch, uint64_t limit_ns,
+                                        rmi_dev_status* status) {
   const int p = threadIdx.x;
   if (p >= world) return;
   // everything this GPU stored before this kernel (the matmul's peer stores) is ordered before the flag
@@ -33,7 +32,7 @@ __global__ void peer_signal_wait_kernel(peer_flags flags, int world, int rank, u
     if ((int32_t)(v - epoch) >= 0) break;
     uint64_t now;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    if (now - t0 > PEER_WAIT_NS) {  // give up: the host reads the status word
+    if (now - t0 > limit_ns) {  // give up: the host reads the status word
       if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
         status->where = 20;
         status->detail = p;
@@ -75,19 +74,24 @@ extern "C" int32_t rmi_ipc_close(rmi_ctx* ctx, void* ptr) {
   return RMI_OK;
 }
 
+int32_t launch_peer_signal_wait(rmi_ctx* ctx, cudaStream_t stream, uint32_t* const* flags, int world, int rank,
+                                uint32_t epoch) {
+  RMI_REQUIRE(flags && world >= 1 && world <= RMI_MAX_FANOUT && rank >= 0 && rank < world, RMI_ERR_BAD_SHAPE,
+              "peer flag round: world %d rank %d", world, rank);
+  peer_flags f = {};
+  for (int i = 0; i < world; i++) {
+    RMI_REQUIRE(flags[i] != nullptr, RMI_ERR_BAD_HANDLE, "peer flag round: flag array %d is null", i);
+    f.p[i] = flags[i];
+  }
+  peer_signal_wait_kernel<<<1, 32, 0, stream>>>(f, world, rank, epoch, ctx->wait_limit_ns, ctx->d_status);
+  return rmi_post_launch(ctx, "peer_signal_wait");
+}
+
 extern "C" int32_t rmi_peer_signal_wait_dev(rmi_ctx* ctx, uint32_t* const* flags, int32_t world, int32_t rank,
                                             uint32_t epoch) {
   RMI_TRY(rmi_check_ctx(ctx));
-  RMI_REQUIRE(flags && world >= 1 && world <= RMI_MAX_FANOUT && rank >= 0 && rank < world, RMI_ERR_BAD_SHAPE,
-              "rmi_peer_signal_wait_dev: world %d rank %d", world, rank);
-  peer_flags f = {};
-  for (int32_t i = 0; i < world; i++) {
-    RMI_REQUIRE(flags[i] != nullptr, RMI_ERR_BAD_HANDLE, "rmi_peer_signal_wait_dev: flag array %d is null", i);
-    f.p[i] = flags[i];
-  }
   std::lock_guard<std::mutex> lock(ctx->mu);
-  peer_signal_wait_kernel<<<1, 32, 0, ctx->stream>>>(f, world, rank, epoch, ctx->d_status);
-  return rmi_post_launch(ctx, "peer_signal_wait");
+  return launch_peer_signal_wait(ctx, ctx->stream, flags, world, rank, epoch);
 }
 
 extern "C" int32_t rmi_check_status(rmi_ctx* ctx) {

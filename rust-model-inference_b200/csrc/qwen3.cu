@@ -497,9 +497,10 @@ static int32_t build_graphs(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
     RMI_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     // programmatic dependent launch along the step's kernel chain: the next kernel's weight copy
     // overlaps the tail of the current one.  Measured gain for small batches only (large grids lose).
+    const bool pdl_before = ctx->pdl;
     ctx->pdl = s->d.batch <= 4;
     int32_t st = enqueue_step(ctx, s, n_prompt, n_gen, which == 1);
-    ctx->pdl = false;
+    ctx->pdl = pdl_before;
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
     if (st != RMI_OK) {

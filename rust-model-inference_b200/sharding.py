@@ -6,7 +6,8 @@ across devices (PlacementSlice::Rows, src/format/load_plan.rs:19-22).  The activ
 replicated and quantized locally (deterministic, so identical on every rank); the only exchange
 is an all-gather of the [M, N/g] results, after which a device kernel restores row-major [M, N]
 (ShardedLinear), or -- fused -- the matmul stores its column slice straight into every rank's
-[M, N] buffer through peer-mapped pointers and a flag round closes the step (PeerShardedLinear).
+[M, N] buffer through peer-mapped pointers, or the copy engines push it there slab by slab behind
+the next slab's matmul, and a flag round closes the step (PeerShardedLinear over rmi_shard_group).
 """
 from __future__ import annotations
 
@@ -38,10 +39,12 @@ def all_gather_cols_cpu(local: np.ndarray, group=None) -> np.ndarray:
 
 
 class ShardedLinear:
-    """One rank's shard of a Q8_0 weight plus the gather step (NCCL, device buffers)."""
+    """One rank's shard of a Q8_0 weight plus the NCCL gather step (device buffers).  With `comm` (an
+    NcclComm of the package) the gather and the un-shard run inside the library (rmi_allgather_cols_dev);
+    without it torch.distributed's all-gather is used and only the un-shard is the library's."""
 
-    def __init__(self, pkg, weight_bytes_of_shard, n_in: int, n_out: int, rank: int, world: int, group=None):
-        self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
+    def __init__(self, pkg, weight_bytes_of_shard, n_in: int, n_out: int, rank: int, world: int, group=None, comm=None):
+        self.pkg, self.rank, self.world, self.group, self.comm = pkg, rank, world, group, comm
         self.n_in, self.n_out = n_in, n_out
         self.row_begin, self.row_end = shard_rows(n_out, world, rank)
         if n_out % world != 0:
@@ -51,12 +54,16 @@ class ShardedLinear:
 
     def forward_dev(self, x, out_local, gathered=None, out_full=None):
         """x [M, n_in] f32 cuda tensor; out_local [M, n_out/g]; optional gather into out_full [M, n_out]."""
-        import torch.distributed as dist
         m = x.shape[0]
         self.pkg.matmul_q8_0_dev(self.weight, x.data_ptr(), m, out_local.data_ptr())
         if gathered is None:
             return out_local
+        if self.comm is not None:
+            self.comm.allgather_cols_dev(out_local.data_ptr(), m, self.n_out // self.world, gathered.data_ptr(),
+                                         out_full.data_ptr())
+            return out_full
         if self.world > 1:
+            import torch.distributed as dist
             dist.all_gather_into_tensor(gathered, out_local, group=self.group)
         else:
             gathered.copy_(out_local.reshape(gathered.shape))
@@ -92,11 +99,12 @@ def rotate_own_first(ptrs: list, rank: int) -> list:
 
 
 class PeerShardedLinear:
-    """Row-sharded Q8_0 linear whose result lands complete on every rank without a collective call:
-    the matmul's epilogue stores this rank's columns into all ranks' [m_max, n_out] buffers."""
+    """Row-sharded Q8_0 linear whose result lands complete on every rank without a collective call
+    (rmi_shard_group): either the matmul's epilogue stores this rank's columns into all ranks' result
+    buffers (EXCHANGE_FUSED_STORES), or the copy engines push them slab by slab while the next slab is
+    computed (EXCHANGE_PEER_COPY).  Result buffers alternate by round."""
 
     def __init__(self, pkg, weight_bytes_of_shard, n_in: int, n_out: int, rank: int, world: int, m_max: int, group=None):
-        import torch.distributed as dist
         if n_out % world != 0:
             raise ValueError("equal shards: n_out must be a multiple of the world size")
         if world > 8:
@@ -107,31 +115,25 @@ class PeerShardedLinear:
         self.ctx = pkg.context()
         self.weight = pkg.QuantizedTensor.from_bytes(weight_bytes_of_shard, pkg.GGML_Q8_0, n_in,
                                                      self.row_end - self.row_begin)
-        self.out_ptr = self.ctx.dev_alloc(m_max * n_out * 4)
-        self.flag_ptr = self.ctx.dev_alloc(256)
-        self.ctx.h2d(self.flag_ptr, np.zeros(64, np.uint32))
-        self.ctx.sync()
+        self.shard_group = pkg.ShardGroup(self.ctx, world, rank, n_out, m_max)
         if world > 1:
+            import torch.distributed as dist
             gather = lambda out, obj: dist.all_gather_object(out, obj, group=group)
-            outs = exchange_handles(self.ctx.ipc_export(self.out_ptr), rank, world, gather)
-            flags = exchange_handles(self.ctx.ipc_export(self.flag_ptr), rank, world, gather)
-            self._out_all = peer_pointer_table(outs, rank, self.out_ptr, self.ctx.ipc_open)
-            self._flag_all = peer_pointer_table(flags, rank, self.flag_ptr, self.ctx.ipc_open)
+            self.shard_group.connect(exchange_handles(self.shard_group.export(), rank, world, gather))
             dist.barrier(group=group)  # every rank has mapped every buffer before the first store
-        else:
-            self._out_all, self._flag_all = [self.out_ptr], [self.flag_ptr]
-        self._fan = rotate_own_first(self._out_all, rank)
-        self.epoch = 0
+        self.out_ptr = None
 
-    def forward_dev(self, x_ptr: int, m: int) -> int:
-        """x [m, n_in] f32 on the device -> pointer of this rank's [m, n_out] buffer, complete (all
-        ranks' columns) once the enqueued work has run.  A consumer must finish reading the buffer
-        before the next call's stores arrive: call forward_dev again only after that."""
+    @property
+    def epoch(self) -> int:
+        return self.shard_group.epoch
+
+    def forward_dev(self, x_ptr: int, m: int, exchange: int = 0) -> int:
+        """x [m, n_in] f32 on the device -> pointer of this round's [m, n_out] buffer, complete (all ranks'
+        columns) once the enqueued work has run.  Reads of a round's result must be enqueued on the context's
+        stream before the next call; the buffer then stays intact until the call after that."""
         if m > self.m_max:
             raise ValueError("m exceeds m_max")
-        self.pkg.matmul_q8_0_fanout_dev(self.weight, x_ptr, m, self._fan, self.n_out, self.row_begin)
-        self.epoch += 1
-        self.pkg.peer_signal_wait_dev(self.ctx, self._flag_all, self.rank, self.epoch)
+        self.out_ptr = self.shard_group.matmul_dev(self.weight, x_ptr, m, exchange)
         return self.out_ptr
 
     def close(self):
@@ -139,10 +141,5 @@ class PeerShardedLinear:
         if self.world > 1:
             import torch.distributed as dist
             dist.barrier(group=self.group)  # no peer is still storing into a buffer that is about to go
-        for r, (o, f) in enumerate(zip(self._out_all, self._flag_all)):
-            if r != self.rank:
-                self.ctx.ipc_close(o)
-                self.ctx.ipc_close(f)
-        self.ctx.dev_free(self.out_ptr)
-        self.ctx.dev_free(self.flag_ptr)
+        self.shard_group.free()
         self.weight.free()

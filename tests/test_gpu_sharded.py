@@ -97,27 +97,76 @@ def test_fanout_rejects_bad_arguments(rmi):
     w.free()
 
 
-def test_peer_sharded_linear_single_rank_and_flag_round(rmi):
-    """world = 1: the fan-out is this rank's own buffer and the flag round completes on its own flag."""
+@pytest.mark.parametrize("m", [7, 1300])
+def test_peer_sharded_linear_single_rank_and_flag_round(rmi, m):
+    """world = 1: the fan-out is this rank's own buffer and the flag round completes on its own flag; both
+    exchanges, alternating result buffers, a different x every round (m = 1300 runs two slabs of the
+    peer-copy exchange)."""
     torch = pytest.importorskip("torch")
     ctx = rmi.context(0)
     ctx.set_semantics(rmi.SEM_NEON)
-    n, k, m = 512, 128, 7
+    n, k = 512, 128
     wb = rmi.synth.q8_0_weight_rows(n, k, seed=8, row_begin=0, row_end=n)
-    lin = rmi.sharding.PeerShardedLinear(rmi, wb, k, n, rank=0, world=1, m_max=8)
-    x = torch.from_numpy(rmi.synth.normal((m, k), seed=9)).cuda()
-    ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
-    rmi.matmul_q8_0_dev(lin.weight, x.data_ptr(), m, ref.data_ptr())
-    torch.cuda.synchronize()
-    for _ in range(3):
-        ptr = lin.forward_dev(x.data_ptr(), m)
-    ctx.check_status()
-    got = np.empty((m, n), np.float32)
-    ctx.d2h(got, ptr)
-    assert np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
-    assert lin.epoch == 3
+    lin = rmi.sharding.PeerShardedLinear(rmi, wb, k, n, rank=0, world=1, m_max=m)
+    seen = set()
+    for rnd in range(4):
+        x = torch.from_numpy(rmi.synth.normal((m, k), seed=9 + rnd)).cuda()
+        ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        rmi.matmul_q8_0_dev(lin.weight, x.data_ptr(), m, ref.data_ptr())
+        ptr = lin.forward_dev(x.data_ptr(), m, rmi.EXCHANGE_PEER_COPY if rnd % 2 else rmi.EXCHANGE_FUSED_STORES)
+        ctx.check_status()
+        got = np.empty((m, n), np.float32)
+        ctx.d2h(got, ptr)
+        assert np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32)), rnd
+        seen.add(ptr)
+    assert lin.epoch == 4 and len(seen) == 2
+    with pytest.raises(ValueError):
+        lin.forward_dev(0, m + 1)
     lin.close()
     ctx.set_semantics(rmi.SEM_AVX2)
+
+
+def test_flag_wait_runs_out_and_reports_timeout(rmi):
+    """A rank that never signals: world = 2 with both flag arrays local and slot 1 never written.  The wait
+    kernel returns after the context's limit (20 ms here), the status call reports RMI_ERR_TIMEOUT once and
+    clears the word, and the context stays usable.  Nothing hangs or faults: the wait is a bounded poll."""
+    ctx = rmi.context(0)
+    f0, f1 = ctx.dev_alloc(256), ctx.dev_alloc(256)
+    zeros = np.zeros(64, np.uint32)
+    ctx.h2d(f0, zeros)
+    ctx.h2d(f1, zeros)
+    ctx.set_wait_limit_ms(20)
+    try:
+        rmi.peer_signal_wait_dev(ctx, [f0, f1], rank=0, epoch=1)
+        with pytest.raises(rmi.RmiError) as e:
+            ctx.check_status()
+        assert e.value.status == 5 and "site 20" in e.value.message
+        ctx.check_status()                      # cleared: the next check is clean
+        got = np.zeros(64, np.uint32)
+        ctx.d2h(got, f1)
+        assert got[0] == 1                      # this rank's own signal did go out
+        # the slot gets written: the same round now completes
+        ctx.h2d(f0, np.array([1, 1] + [0] * 62, np.uint32))
+        rmi.peer_signal_wait_dev(ctx, [f0, f1], rank=0, epoch=1)
+        ctx.check_status()
+        with pytest.raises(rmi.RmiError):
+            ctx.set_wait_limit_ms(0)
+    finally:
+        ctx.set_wait_limit_ms(2000)
+        ctx.dev_free(f0)
+        ctx.dev_free(f1)
+
+
+def test_unshard_vectorised_and_ragged(rmi):
+    torch = pytest.importorskip("torch")
+    ctx = rmi.context(0)
+    for g, m, npr in [(4, 9, 1024), (3, 5, 30), (2, 1, 8)]:
+        gathered = torch.arange(g * m * npr, dtype=torch.float32, device="cuda").reshape(g, m, npr)
+        out = torch.empty((m, g * npr), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        rmi.unshard_cols_dev(ctx, gathered.data_ptr(), g, m, npr, out.data_ptr())
+        ctx.sync()
+        assert np.array_equal(out.cpu().numpy(), rmi.sharding.unshard_numpy(gathered.cpu().numpy()))
 
 
 def test_ipc_export_gives_a_64_byte_handle(rmi):
@@ -141,21 +190,43 @@ ctx = pkg.context(rank)
 ctx.set_semantics(pkg.SEM_NEON)
 n, k = 2048, 512
 s, e = pkg.sharding.shard_rows(n, world, rank)
-lin = pkg.sharding.PeerShardedLinear(pkg, pkg.synth.q8_0_weight_rows(n, k, seed=3, row_begin=s, row_end=e), k, n, rank, world, m_max=160)
+shard = pkg.synth.q8_0_weight_rows(n, k, seed=3, row_begin=s, row_end=e)
+lin = pkg.sharding.PeerShardedLinear(pkg, shard, k, n, rank, world, m_max=1200)
 full = pkg.QuantizedTensor.from_bytes(pkg.synth.q8_0_weight_rows(n, k, seed=3, row_begin=0, row_end=n), pkg.GGML_Q8_0, k, n)
+def bcast(obj):
+    box = [obj]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+comm = pkg.NcclComm(ctx, world, rank, bcast)
+nccl_lin = pkg.sharding.ShardedLinear(pkg, shard, k, n, rank, world, comm=comm)
 ok = True
-for m in (1, 16, 160):
-    x = torch.from_numpy(pkg.synth.normal((m, k), seed=4)).cuda()
-    ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
-    pkg.matmul_q8_0_dev(full, x.data_ptr(), m, ref.data_ptr())
-    for _ in range(2):
-        ptr = lin.forward_dev(x.data_ptr(), m)
-        ctx.check_status()
-        dist.barrier()          # both ranks have read nothing yet; keeps the rounds apart
-    got = np.empty((m, n), np.float32)
-    ctx.d2h(got, ptr)
-    ok = ok and np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
+for m in (1, 16, 160, 1200):
+    # three rounds back to back, a different x each, no host barrier in between: a stale or overwritten
+    # result buffer shows up as a bit mismatch.  Each round's result is read back (enqueued on the
+    # context's stream) before the next round is called, which is the documented contract.
+    xs = [torch.from_numpy(pkg.synth.normal((m, k), seed=4 + 10 * r)).cuda() for r in range(3)]
+    refs = []
+    for x in xs:
+        ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        pkg.matmul_q8_0_dev(full, x.data_ptr(), m, ref.data_ptr())
+        refs.append(ref)
+    ctx.sync()
+    for exchange in (pkg.EXCHANGE_FUSED_STORES, pkg.EXCHANGE_PEER_COPY):
+        for x, ref in zip(xs, refs):
+            ptr = lin.forward_dev(x.data_ptr(), m, exchange)
+            got = np.empty((m, n), np.float32)
+            ctx.d2h(got, ptr)
+            ctx.check_status()
+            ok = ok and np.array_equal(got.view(np.uint32), ref.cpu().numpy().view(np.uint32))
+    out_local = torch.empty((m, n // world), dtype=torch.float32, device="cuda")
+    gathered = torch.empty((world, m, n // world), dtype=torch.float32, device="cuda")
+    out_full = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    nccl_lin.forward_dev(xs[0], out_local, gathered, out_full)
+    ctx.sync()
+    ok = ok and torch.equal(out_full.view(torch.int32), refs[0].view(torch.int32))
     dist.barrier()
+comm.destroy()
 lin.close()
 dist.destroy_process_group()
 print("RANK_OK" if ok else "RANK_MISMATCH", flush=True)
