@@ -307,7 +307,18 @@ def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="sess
     prompts = np.stack([pkg.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=1000 + b) for b in range(batch)])
     toks = s.generate(prompts, n_gen)
     res = {"batch": batch, "prompt": n_prompt, "gen": n_gen, "tok_s": batch * n_gen / (s.gen_ms / 1e3),
-           "gen_ms": s.gen_ms, "prefill_ms": s.prefill_ms, "first_tokens": [int(t) for t in toks[0, :4]]}
+           "gen_ms": s.gen_ms, "prefill_ms": s.prefill_ms, "first_tokens": [int(t) for t in toks[0, :4]],
+           "prefill": "prompt positions as rows through every operator; cache rows bit-identical to the reference's "
+                      "token loop (AVX2: eight-lane order on CUDA cores)"}
+    if forward == "session":
+        s.set_prefill(pkg.PREFILL_TOKEN_LOOP)
+        s.generate(prompts, 1)
+        res["prefill_ms_token_loop"] = s.prefill_ms
+        if sem == pkg.SEM_AVX2:
+            s.set_prefill(pkg.PREFILL_BATCHED_TENSOR)
+            t2 = s.generate(prompts, n_gen)
+            res["prefill_ms_tensor_cores"] = s.prefill_ms
+            res["tensor_core_prefill_same_tokens"] = bool(np.array_equal(t2, toks))
     s.free()
     model.free()
     return res, toks

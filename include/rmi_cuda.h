@@ -300,8 +300,20 @@ enum {
   RMI_FORWARD_APP_LOGITS_F32KV = 4
 };
 int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t forward);
-/* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): feeds the prompts one
- * position at a time, then generates n_gen tokens per sequence; the whole step runs on the
+/* How the prompt positions before the last one are processed (their logits are never read):
+ *   RMI_PREFILL_BATCHED (default)  all positions of a sequence as rows through every operator of a layer
+ *     (matmuls with M = positions, causal attention per position over the cache rows written on the way).
+ *     Every operator of the reference's step works on one row and positions only meet in the K/V cache, so
+ *     every cache row carries the bits of the reference's token loop (src/models/qwen3.rs:657-689): under
+ *     NEON/SCALAR semantics the matmuls run on the tensor cores, under AVX2 on the bit-exact CUDA-core
+ *     kernels.  Used for the default forward and prompts of 17 positions or more; otherwise the token loop.
+ *   RMI_PREFILL_TOKEN_LOOP         one position per step, as the reference does.
+ *   RMI_PREFILL_BATCHED_TENSOR     as BATCHED, but AVX2 semantics also take the tensor cores: cache rows are
+ *     then within the 1e-5 matmul contract of the eight-lane order instead of bit-equal to it. */
+enum { RMI_PREFILL_BATCHED = 0, RMI_PREFILL_TOKEN_LOOP = 1, RMI_PREFILL_BATCHED_TENSOR = 2 };
+int32_t rmi_session_set_prefill(rmi_ctx* ctx, rmi_session* s, int32_t mode);
+/* Qwen3Session::generate greedy path (src/models/qwen3.rs:581-1158): processes the prompts (see
+ * rmi_session_set_prefill), then generates n_gen tokens per sequence; the whole step runs on the
  * device.  prompts [batch, n_prompt] u32, out_tokens [batch, n_gen] u32.  EOS handling is
  * the caller's (there is no tokenizer here).  gen_ms (optional) receives the device time of
  * the n_gen generation steps, prefill_ms that of the prompt steps. */

@@ -31,6 +31,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "librmi_cuda.so")
 SEM_AVX2, SEM_NEON, SEM_SCALAR = 0, 1, 2
 GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
 FORWARD_QWEN3_SESSION, FORWARD_APP_TEXT, FORWARD_APP_TEXT_F32KV, FORWARD_APP_LOGITS, FORWARD_APP_LOGITS_F32KV = 0, 1, 2, 3, 4
+PREFILL_BATCHED, PREFILL_TOKEN_LOOP, PREFILL_BATCHED_TENSOR = 0, 1, 2
 STATUS = {0: "RMI_OK", 1: "RMI_ERR_BAD_HANDLE", 2: "RMI_ERR_BAD_SHAPE", 3: "RMI_ERR_OOM", 4: "RMI_ERR_CUDA",
           5: "RMI_ERR_TIMEOUT", 6: "RMI_ERR_UNSUPPORTED", 7: "RMI_ERR_IO", 8: "RMI_ERR_FORMAT",
           9: "RMI_ERR_NONFINITE"}
@@ -831,6 +832,12 @@ class Qwen3Session:
         FORWARD_APP_TEXT_F32KV (that loop with `--kv-cache f32`; at most 512 positions), FORWARD_APP_LOGITS /
         FORWARD_APP_LOGITS_F32KV (the logits tool's loop, src/app/logits.rs, over the F16 / F32 cache)."""
         _check(lib().rmi_session_set_forward(self._ctx.handle, self._h, C.c_int32(forward)))
+
+    def set_prefill(self, mode: int):
+        """PREFILL_BATCHED (default: prompt positions as rows through every operator, bit-identical to the token
+        loop), PREFILL_TOKEN_LOOP (one position per step, the reference's order) or PREFILL_BATCHED_TENSOR (AVX2
+        semantics also on the tensor cores: cache rows within the 1e-5 matmul contract instead of bit-equal)."""
+        _check(lib().rmi_session_set_prefill(self._ctx.handle, self._h, C.c_int32(mode)))
 
     def generate(self, prompts, max_new_tokens: int) -> np.ndarray:
         prompts = np.ascontiguousarray(prompts, np.uint32).reshape(self.batch, -1)

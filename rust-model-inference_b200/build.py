@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "librmi_cuda.so")
-SOURCES = ["api.cu", "api_q4k.cu", "q8_0.cu", "gemm_tc.cu", "q4k.cu", "q6k.cu", "q4_0.cu", "decode.cu", "qwen3.cu", "gguf.cpp", "no_alloc.cu", "peer.cu", "sharded.cu"]
+SOURCES = ["api.cu", "api_q4k.cu", "q8_0.cu", "gemm_tc.cu", "q4k.cu", "q6k.cu", "q4_0.cu", "decode.cu", "prefill.cu", "qwen3.cu", "gguf.cpp", "no_alloc.cu", "peer.cu", "sharded.cu"]
 # -fmad=false: the reference never fuses a*b+c unless it says mul_add; fused ops are explicit.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-fmad=false",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr"]

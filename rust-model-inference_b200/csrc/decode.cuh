@@ -38,3 +38,16 @@ size_t argmax_scratch_floats(size_t batch);
 int32_t launch_argmax(rmi_ctx* ctx, const float* logits, size_t vocab, const int* d_step, size_t n_prompt, uint32_t* gen,
                       size_t n_gen, int* flag, size_t batch, float* part_v, uint32_t* part_i, bool last_index = false);
 int32_t launch_step_inc(rmi_ctx* ctx, int* d_step);
+
+// prefill.cu: batched prompt processing (rows r = b_local * P + p for sequences b0.. and positions p < P)
+bool prefill_supported(const rmi_ctx* ctx, const decode_dims& d, size_t P);
+int32_t launch_embed_rows(rmi_ctx* ctx, const rmi_weight* emb, const uint32_t* prompts, size_t n_prompt, size_t P, size_t b0,
+                          size_t rows, float* x);
+int32_t launch_rmsnorm_rows(rmi_ctx* ctx, float* x, const float* add, const float* weight, size_t n, float eps, float* out,
+                            size_t rows);
+int32_t launch_qk_norm_rope_kv_rows(rmi_ctx* ctx, const decode_dims& d, const float* qkv, const float* q_norm,
+                                    const float* k_norm, const float* rope, size_t P, size_t b0, size_t rows, uint16_t* q16,
+                                    uint16_t* k_cache, uint16_t* v_cache, size_t layer);
+int32_t launch_attention_prefill(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
+                                 const uint16_t* v_cache, size_t layer, size_t P, size_t b0, size_t n_seq, float* attn_out);
+int32_t launch_set_step(rmi_ctx* ctx, int* d_step, int value);

@@ -58,6 +58,11 @@ struct rmi_session {
   int *d_step, *d_flag;
   float* argmax_v;
   uint32_t* argmax_i;
+  // batched prompt processing (rows = sequences of a group x prompt positions); buffers allocated on first use
+  int prefill_mode;  // RMI_PREFILL_*
+  size_t pf_rows;
+  float *pf_x, *pf_xn, *pf_qkv, *pf_attn, *pf_proj;
+  uint16_t* pf_q16;
   cudaGraph_t graph_body, graph_full;
   cudaGraphExec_t exec_body, exec_full;
   size_t graph_n_prompt, graph_n_gen;
@@ -279,6 +284,7 @@ static void free_session(rmi_session* s) {
   cudaFree(s->v32_cache);
   cudaFree(s->argmax_v);
   cudaFree(s->argmax_i);
+  cudaFree(s->pf_x); cudaFree(s->pf_xn); cudaFree(s->pf_qkv); cudaFree(s->pf_attn); cudaFree(s->pf_proj); cudaFree(s->pf_q16);
   s->magic = 0;
   delete s;
 }
@@ -533,6 +539,122 @@ static int32_t build_graphs(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
   return RMI_OK;
 }
 
+extern "C" int32_t rmi_session_set_prefill(rmi_ctx* ctx, rmi_session* s, int32_t mode) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  RMI_REQUIRE(mode >= RMI_PREFILL_BATCHED && mode <= RMI_PREFILL_BATCHED_TENSOR, RMI_ERR_UNSUPPORTED, "unknown prefill mode %d",
+              mode);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  s->prefill_mode = mode;
+  return RMI_OK;
+}
+
+// Prompt positions 0..P-1 of every sequence as rows through each operator (see prefill.cu).  Only the default
+// forward is batched; the app-loop variants keep the token loop.
+static const size_t PREFILL_MIN_POSITIONS = 16;
+static const size_t PREFILL_MAX_ROWS = 8192;
+
+static bool prefill_batched(const rmi_ctx* ctx, const rmi_session* s, size_t P) {
+  return s->prefill_mode != RMI_PREFILL_TOKEN_LOOP && s->forward == RMI_FORWARD_QWEN3_SESSION && P >= PREFILL_MIN_POSITIONS &&
+         prefill_supported(ctx, s->d, P);
+}
+
+static int32_t ensure_prefill_buffers(rmi_session* s, size_t rows) {
+  if (s->pf_rows >= rows) return RMI_OK;
+  const decode_dims& d = s->d;
+  const size_t nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
+  cudaFree(s->pf_x); cudaFree(s->pf_xn); cudaFree(s->pf_qkv); cudaFree(s->pf_attn); cudaFree(s->pf_proj); cudaFree(s->pf_q16);
+  s->pf_x = s->pf_xn = s->pf_qkv = s->pf_attn = s->pf_proj = nullptr;
+  s->pf_q16 = nullptr;
+  s->pf_rows = 0;
+  cudaError_t e = cudaMalloc((void**)&s->pf_x, rows * d.n_embd * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->pf_xn, rows * d.n_embd * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->pf_qkv, rows * (nq + 2 * nk) * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->pf_attn, rows * nq * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->pf_proj, rows * d.n_embd * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->pf_q16, rows * nq * 2);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    rmi_set_error("allocation of the prefill buffers (%zu rows) failed: %s", rows, cudaGetErrorString(e));
+    return RMI_ERR_OOM;
+  }
+  s->pf_rows = rows;
+  return RMI_OK;
+}
+
+static size_t prefill_group_seqs(const rmi_session* s, size_t P) {
+  const size_t per_group = P >= PREFILL_MAX_ROWS ? 1 : PREFILL_MAX_ROWS / P;
+  return s->d.batch < per_group ? s->d.batch : per_group;
+}
+
+static bool prefill_on_tensor_cores(const rmi_ctx* ctx, const rmi_session* s) {
+  return ctx->sem != RMI_SEM_AVX2 || s->prefill_mode == RMI_PREFILL_BATCHED_TENSOR;
+}
+
+// Everything that allocates (row buffers, the context's matmul scratch, tcgen05 weight layouts), done before the
+// timed region of a generate call.
+static int32_t prepare_prefill(rmi_ctx* ctx, rmi_session* s, size_t P) {
+  const rmi_qwen3* m = s->model;
+  const decode_dims& d = s->d;
+  const size_t rows = prefill_group_seqs(s, P) * P;
+  RMI_TRY(ensure_prefill_buffers(s, rows));
+  const size_t nq = d.n_head * d.hd;
+  const size_t widest = nq > d.n_ff ? (nq > d.n_embd ? nq : d.n_embd) : (d.n_ff > d.n_embd ? d.n_ff : d.n_embd);
+  const size_t rows_pad = (rows + 127) / 128 * 128, wide_pad = (widest + 127) / 128 * 128;
+  void* unused;
+  RMI_TRY(rmi_scratch(ctx, 0, rows_pad * wide_pad, &unused));                 // quantized rows (row-major or images)
+  RMI_TRY(rmi_scratch(ctx, 1, rows_pad * (wide_pad / 32) * 4, &unused));      // their scales
+  RMI_TRY(rmi_scratch(ctx, 3, rows_pad * wide_pad, &unused));
+  RMI_TRY(rmi_scratch(ctx, 4, rows_pad * (wide_pad / 32) * 4, &unused));
+  if (prefill_on_tensor_cores(ctx, s)) {
+    for (const auto& l : m->layers) {
+      RMI_TRY(ensure_umma_layout(ctx, l.wqkv));
+      RMI_TRY(ensure_umma_layout(ctx, l.wo));
+      RMI_TRY(ensure_umma_layout(ctx, l.wgu, true));
+      RMI_TRY(ensure_umma_layout(ctx, l.wdown));
+    }
+  } else {
+    RMI_TRY(rmi_scratch(ctx, 2, rows * 2 * d.n_ff * 4, &unused));             // gate | up rows of the CUDA-core FFN
+  }
+  return RMI_OK;
+}
+
+static int32_t enqueue_prefill(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_t P) {
+  const rmi_qwen3* m = s->model;
+  const decode_dims& d = s->d;
+  const size_t nq = d.n_head * d.hd;
+  const size_t group_seqs = prefill_group_seqs(s, P);
+  RMI_TRY(ensure_prefill_buffers(s, group_seqs * P));
+  // AVX2 semantics: the eight-lane accumulation order is reproduced bit for bit by the CUDA-core kernels, which
+  // keeps every cache row identical to the token loop's; RMI_PREFILL_BATCHED_TENSOR trades that for the tensor cores
+  const bool exact_before = ctx->prefill_exact;
+  if (ctx->sem == RMI_SEM_AVX2) ctx->prefill_exact = s->prefill_mode != RMI_PREFILL_BATCHED_TENSOR;
+  int32_t st = RMI_OK;
+  for (size_t b0 = 0; b0 < d.batch && st == RMI_OK; b0 += group_seqs) {
+    const size_t nb = d.batch - b0 < group_seqs ? d.batch - b0 : group_seqs, rows = nb * P;
+    st = launch_embed_rows(ctx, m->token_embd, s->prompts, n_prompt, P, b0, rows, s->pf_x);
+    const float* pending = nullptr;
+    for (size_t l = 0; l < d.n_layer && st == RMI_OK; l++) {
+      const layer_weights& w = m->layers[l];
+      st = launch_rmsnorm_rows(ctx, s->pf_x, pending, w.attn_norm, d.n_embd, d.eps, s->pf_xn, rows);
+      if (st == RMI_OK) st = matmul_q8_0_device(ctx, w.wqkv, s->pf_xn, rows, s->pf_qkv);
+      if (st == RMI_OK)
+        st = launch_qk_norm_rope_kv_rows(ctx, d, s->pf_qkv, w.q_norm, w.k_norm, s->rope, P, b0, rows, s->pf_q16, s->k_cache,
+                                         s->v_cache, l);
+      if (l + 1 == d.n_layer) break;  // the last layer only has to fill its cache rows: nobody reads these positions' output
+      if (st == RMI_OK) st = launch_attention_prefill(ctx, d, s->pf_q16, s->k_cache, s->v_cache, l, P, b0, nb, s->pf_attn);
+      if (st == RMI_OK) st = matmul_q8_0_device(ctx, w.wo, s->pf_attn, rows, s->pf_proj);
+      if (st == RMI_OK) st = launch_rmsnorm_rows(ctx, s->pf_x, s->pf_proj, w.ffn_norm, d.n_embd, d.eps, s->pf_xn, rows);
+      if (st == RMI_OK) st = ffn_device(ctx, w.wgu, w.wdown, s->pf_xn, rows, s->pf_proj);
+      pending = s->pf_proj;
+    }
+  }
+  ctx->prefill_exact = exact_before;
+  RMI_TRY(st);
+  (void)nq;
+  return launch_set_step(ctx, s->d_step, (int)P);
+}
+
 extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint32_t* prompts, size_t n_prompt,
                                         size_t n_gen, uint32_t* out_tokens, float* prefill_ms, float* gen_ms) {
   RMI_TRY(rmi_check_ctx(ctx));
@@ -566,6 +688,11 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
   RMI_CUDA_CHECK(cudaMemsetAsync(s->d_flag, 0, 4, ctx->stream));
   RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
   RMI_TRY(build_graphs(ctx, s, n_prompt, n_gen));
+  const bool batched = n_prompt >= 2 && prefill_batched(ctx, s, n_prompt - 1);
+  if (batched) {
+    RMI_TRY(prepare_prefill(ctx, s, n_prompt - 1));
+    RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  }
   cudaEvent_t e0, e1, e2;
   RMI_CUDA_CHECK(cudaEventCreate(&e0));
   RMI_CUDA_CHECK(cudaEventCreate(&e1));
@@ -583,7 +710,19 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
   const uint64_t launches_per_body = 3 + d.n_layer * per_layer, launches_full = launches_per_body + passes + 2;
   RMI_CUDA_CHECK(cudaEventRecord(e0, ctx->stream));
   cudaError_t ce = cudaSuccess;
-  for (size_t st = 0; st < steps && ce == cudaSuccess; st++) {
+  size_t first_step = 0;
+  if (batched) {
+    const int32_t pst = enqueue_prefill(ctx, s, n_prompt, n_prompt - 1);
+    if (pst != RMI_OK) {
+      cudaStreamSynchronize(ctx->stream);
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      cudaEventDestroy(e2);
+      return pst;
+    }
+    first_step = n_prompt - 1;
+  }
+  for (size_t st = first_step; st < steps && ce == cudaSuccess; st++) {
     if (st == n_prompt - 1) ce = cudaEventRecord(e1, ctx->stream);
     const bool full = st + 1 >= n_prompt && n_gen > 0;
     if (ce == cudaSuccess) ce = cudaGraphLaunch(full ? s->exec_full : s->exec_body, ctx->stream);

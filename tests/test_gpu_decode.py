@@ -294,3 +294,53 @@ def test_config4_full_size_greedy_tokens_identical_over_128_steps(rmi, ctx):
     assert np.array_equal(got[1], ref1)
     s.free()
     model.free()
+
+
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
+@pytest.mark.parametrize("batch,n_prompt", [(1, 70), (3, 33), (40, 300)])
+def test_batched_prefill_equals_the_token_loop(rmi, ctx, tmp_path_factory, sem, batch, n_prompt):
+    """Prompt positions as rows through every operator (matmuls with M = positions, causal attention per position)
+    against the reference's one-position-per-step loop on the same session: tokens identical, hidden state and
+    logits of the last step bit-identical; sequence 0 also against the oracle.  (40, 300) makes the prefill run
+    in two groups of sequences (more than 8192 rows) and uses attention tiles of several key blocks."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=5)
+    model = rmi.Qwen3Model.from_file(path)
+    n_gen = 12
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=40 + b) for b in range(batch)])
+    s = rmi.Qwen3Session(model, n_prompt + n_gen, batch=batch)
+    s.set_prefill(rmi.PREFILL_TOKEN_LOOP)
+    loop_tok = s.generate(prompts, n_gen)
+    loop_hidden, loop_logits, loop_ms = s.hidden(), s.logits(), s.prefill_ms
+    s.set_prefill(rmi.PREFILL_BATCHED)
+    tok = s.generate(prompts, n_gen)
+    assert np.array_equal(tok, loop_tok)
+    assert np.array_equal(bits(s.hidden()), bits(loop_hidden))
+    assert np.array_equal(bits(s.logits()), bits(loop_logits))
+    ref = orc.Qwen3(cfg, tensors).generate(prompts[0], n_gen, sem=sem)
+    assert np.array_equal(tok[0], ref)
+    print(f"prefill {n_prompt - 1} positions x {batch}: token loop {loop_ms:.2f} ms, batched {s.prefill_ms:.2f} ms")
+    s.free()
+    model.free()
+
+
+def test_batched_prefill_on_tensor_cores_under_avx2_semantics(rmi, ctx, tmp_path_factory):
+    """RMI_PREFILL_BATCHED_TENSOR: AVX2 quantizer, whole-block accumulation on tcgen05 for the prompt rows.  The cache
+    rows are then not bit-equal to the eight-lane order; the hidden state of the last step stays within a small
+    relative distance and, on this model, the greedy tokens are the same."""
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=6)
+    model = rmi.Qwen3Model.from_file(path)
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], 130, seed=60 + b) for b in range(2)])
+    s = rmi.Qwen3Session(model, 130 + 8, batch=2)
+    exact = s.generate(prompts, 8)
+    h_exact = s.hidden()
+    s.set_prefill(rmi.PREFILL_BATCHED_TENSOR)
+    tens = s.generate(prompts, 8)
+    h_tens = s.hidden()
+    assert np.array_equal(tens, exact)
+    assert float(np.max(np.abs(h_tens - h_exact))) <= 2e-2 * float(np.max(np.abs(h_exact)))
+    s.free()
+    model.free()
