@@ -554,7 +554,8 @@ __global__ void __launch_bounds__(128)
   }
   __syncthreads();  // barrier initialised and activations staged
   {
-    // bounded wait for the bulk copy (two seconds), all threads observe the phase themselves
+    // bounded wait for the bulk copy (the context's wait limit), all threads observe the phase themselves
+    const uint64_t limit_ns = status->limit_ns;
     uint64_t t0 = 0;
     bool done = false;
     for (uint32_t i = 0; i < (1u << 26) && !done; i++) {
@@ -571,7 +572,7 @@ __global__ void __launch_bounds__(128)
         uint64_t now;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
         if (t0 == 0) t0 = now;
-        else if (now - t0 > 2000000000ull) break;
+        else if (now - t0 > limit_ns) break;
       }
     }
     if (!done) {
@@ -621,6 +622,161 @@ __global__ void __launch_bounds__(128)
       r = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
     }
     if (l == 0 && row >= row_begin && row < row_end) store_fanout(out + m * out_stride + row, r, fo);
+  }
+}
+
+// ---------------------------------------------------------------- GEMV, long streams
+
+// Bandwidth-bound shapes with one or two activation rows and more 16-row tiles than the staged kernel takes
+// (the config-5 shard at M = 1, the logits projection): persistent CTAs walk the tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ...  A tile's record stream (blocks * 544 contiguous bytes) is cut into
+// chunks of STREAM_CB blocks that travel through a ring of STREAM_S shared-memory stages as bulk async copies
+// (one elected thread, mbarrier transaction counts), so a CTA keeps STREAM_S * 17 KiB of reads in flight with
+// no register staging, across tile boundaries.  64 threads per CTA: thread (row r, part p) owns bytes 8p..8p+7
+// of every block of row r, i.e. two of the reference's eight per-lane chains, and runs them over the blocks in
+// order out of shared memory.
+// Measured on W [32768, 8192], M = 1 (fractions of the copy bandwidth): chunks of 8 / 16 / 32 / 48 / 64 blocks with
+// 6 / 4 / 2 / 2 / 2 stages reach 0.50 / 0.77 / 0.88 / 0.83 / 0.64: large copies stream better as long as five CTAs
+// still fit on an SM.
+constexpr int STREAM_CB = 32;  // blocks per chunk: 32 * 544 = 17408 bytes
+constexpr int STREAM_S = 2;    // stages
+constexpr int STREAM_THREADS = 64;  // 16 rows x 4 lanes, 8 bytes of every block per lane
+
+template <int SEM, int MP>
+__global__ void __launch_bounds__(STREAM_THREADS)
+    q8_gemv_stream_kernel(const uint8_t* __restrict__ w, size_t blocks, const uint8_t* __restrict__ xq,
+                          const float* __restrict__ xs, float* __restrict__ out, size_t out_stride, size_t row_begin,
+                          size_t row_end, size_t first_tile, size_t n_tiles, rmi_dev_status* status, const out_fanout fo) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const size_t K = blocks * 32;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);                    // [STREAM_S]
+  uint8_t* ring = smem + 128;                                           // [STREAM_S][STREAM_CB * 544]
+  int8_t* xq_s = reinterpret_cast<int8_t*>(ring + STREAM_S * STREAM_CB * Q8_REC_BYTES);  // [MP][K]
+  float* xs_s = reinterpret_cast<float*>(xq_s + MP * K);                // [MP][blocks]
+  const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bar);
+  const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(ring);
+  const int n_chunks = (int)((blocks + STREAM_CB - 1) / STREAM_CB);
+  const size_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const size_t n_items = my_tiles * (size_t)n_chunks;                   // (tile, chunk) pairs of this CTA, in order
+
+  // item j -> stage j % STREAM_S; issued by thread 0 only
+  auto issue = [&](size_t j) {
+    const size_t tile = first_tile + blockIdx.x + (j / n_chunks) * gridDim.x;
+    const int c = (int)(j % n_chunks);
+    const size_t b0 = (size_t)c * STREAM_CB;
+    const uint32_t nb = (uint32_t)(blocks - b0 < (size_t)STREAM_CB ? blocks - b0 : (size_t)STREAM_CB);
+    const uint32_t bytes = nb * Q8_REC_BYTES;
+    const uint32_t st = (uint32_t)(j % STREAM_S);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a + 8 * st), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     ring_a + st * (uint32_t)(STREAM_CB * Q8_REC_BYTES)),
+                 "l"(w + (tile * blocks + b0) * Q8_REC_BYTES), "r"(bytes), "r"(bar_a + 8 * st)
+                 : "memory");
+  };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STREAM_S; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a + 8 * i));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (size_t j = 0; j < n_items && j < (size_t)STREAM_S; j++) issue(j);   // weights: nobody in the chain writes them
+  }
+  pdl_wait();  // everything below depends on the previous kernel
+  pdl_launch_dependents();
+  {
+    const int4* src = reinterpret_cast<const int4*>(xq);
+    int4* dst = reinterpret_cast<int4*>(xq_s);
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+  }
+  __syncthreads();  // barriers initialised, activations staged
+
+  const int rit = threadIdx.x >> 2, part = threadIdx.x & 3;   // row in tile, which 8 bytes of the block
+  const uint64_t limit_ns = status->limit_ns;
+  float acc[MP][SEM == RMI_SEM_AVX2 ? 2 : 1];
+  for (size_t j = 0; j < n_items; j++) {
+    const int c = (int)(j % n_chunks);
+    const uint32_t st = (uint32_t)(j % STREAM_S), parity = (uint32_t)((j / STREAM_S) & 1);
+    if (c == 0) {
+#pragma unroll
+      for (int m = 0; m < MP; m++)
+#pragma unroll
+        for (int q = 0; q < (SEM == RMI_SEM_AVX2 ? 2 : 1); q++) acc[m][q] = 0.0f;
+    }
+    {
+      // bounded wait for the chunk; every thread observes the phase itself
+      uint64_t t0 = 0;
+      bool done = false;
+      for (uint32_t i = 0; i < (1u << 26) && !done; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar_a + 8 * st), "r"(parity), "r"(20000u)
+            : "memory");
+        done = ok != 0;
+        if (!done && (i & 15) == 15) {
+          uint64_t now;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > limit_ns) break;
+        }
+      }
+      if (!done) {  // the copies in flight target this CTA's own shared memory and are dropped with it
+        if (atomicCAS(&status->code, 0, RMI_ERR_TIMEOUT) == 0) {
+          status->where = 11;
+          status->detail = (int)j;
+        }
+        return;
+      }
+    }
+    const size_t b0 = (size_t)c * STREAM_CB;
+    const int nb = (int)(blocks - b0 < (size_t)STREAM_CB ? blocks - b0 : (size_t)STREAM_CB);
+    const uint8_t* wt = ring + st * (STREAM_CB * Q8_REC_BYTES);
+    const uint8_t* qp = wt + 32 + rit * 32 + part * 8;
+    const uint8_t* sp = wt + 2 * rit;
+#pragma unroll 4
+    for (int bi = 0; bi < nb; bi++) {
+      const size_t b = b0 + bi;
+      const int2 wq = *reinterpret_cast<const int2*>(qp + bi * Q8_REC_BYTES);
+      const float wd = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(sp + bi * Q8_REC_BYTES));
+#pragma unroll
+      for (int m = 0; m < MP; m++) {
+        const int2 xv = *reinterpret_cast<const int2*>(xq_s + m * K + b * 32 + part * 8);
+        const float da = __fmul_rn(wd, xs_s[m * blocks + b]);
+        if (SEM == RMI_SEM_AVX2) {
+          // avx2.rs:96-148: lanes 2*part and 2*part+1 of the eight partial sums
+          const float f0 = __fsub_rn(__int_as_float(dp4a_s8(wq.x, xv.x, 0x4B400000)), 12582912.0f);
+          const float f1 = __fsub_rn(__int_as_float(dp4a_s8(wq.y, xv.y, 0x4B400000)), 12582912.0f);
+          acc[m][0] = __fmaf_rn(da, f0, acc[m][0]);
+          acc[m][SEM == RMI_SEM_AVX2 ? 1 : 0] = __fmaf_rn(da, f1, acc[m][SEM == RMI_SEM_AVX2 ? 1 : 0]);
+        } else {
+          int dot = dp4a_s8(wq.y, xv.y, dp4a_s8(wq.x, xv.x, 0));
+          dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+          dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+          const float f = small_int_to_f32(dot);
+          if (SEM == RMI_SEM_NEON) acc[m][0] = __fmaf_rn(f, da, acc[m][0]);   // neon.rs:69
+          else acc[m][0] = __fadd_rn(acc[m][0], __fmul_rn(da, f));            // scalar.rs:55
+        }
+      }
+    }
+    __syncthreads();  // every thread is done with the stage
+    if (threadIdx.x == 0 && j + STREAM_S < n_items) issue(j + STREAM_S);
+    if (c == n_chunks - 1) {
+      const size_t tile = first_tile + blockIdx.x + (j / n_chunks) * gridDim.x;
+      const size_t row = tile * 16 + rit;
+#pragma unroll
+      for (int m = 0; m < MP; m++) {
+        float r = acc[m][0];
+        if (SEM == RMI_SEM_AVX2) {  // dot.rs:447-456: s_i = a[i+4] + a[i]; (s0 + s1) + (s2 + s3)
+          const float a0 = acc[m][0], a1 = acc[m][SEM == RMI_SEM_AVX2 ? 1 : 0];
+          const float s0 = __fadd_rn(__shfl_xor_sync(0xffffffffu, a0, 2), a0);
+          const float s1 = __fadd_rn(__shfl_xor_sync(0xffffffffu, a1, 2), a1);
+          const float t = __fadd_rn(s0, s1);  // part 0: s0+s1, part 1: s2+s3
+          r = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
+        }
+        if (part == 0 && row >= row_begin && row < row_end) store_fanout(out + m * out_stride + row, r, fo);
+      }
+    }
   }
 }
 
@@ -748,6 +904,10 @@ static int32_t gemv_launch_one(rmi_ctx* ctx, const rmi_weight* w, const uint8_t*
   return rmi_post_launch(ctx, "q8_gemv");
 }
 
+#ifndef RMI_STREAM_MIN_BLOCKS
+#define RMI_STREAM_MIN_BLOCKS 64
+#endif
+
 template <int SEM, int MP>
 static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, const float* xs, float* out,
                                 size_t out_stride, size_t row_begin, size_t row_end, size_t n_groups) {
@@ -774,6 +934,36 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
         return RMI_ERR_CUDA;
       }
       return rmi_post_launch(ctx, "q8_gemv_staged");
+    }
+  }
+  {
+    // many tiles, one or two activation rows: persistent CTAs stream the records through a ring of bulk copies
+    const size_t t1 = (row_end + 15) / 16 - row_begin / 16, blocks = w->n_in / 32;
+    const size_t smem = 128 + (size_t)STREAM_S * STREAM_CB * Q8_REC_BYTES + (size_t)MP * (w->n_in + blocks * 4);
+    if (MP <= 2 && n_groups == 1 && blocks >= RMI_STREAM_MIN_BLOCKS && smem <= ctx->smem_optin - 1024) {
+      auto kern = q8_gemv_stream_kernel<SEM, MP>;
+      if (smem > 48 * 1024 &&
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed", smem);
+        return RMI_ERR_CUDA;
+      }
+      size_t per_sm = (ctx->smem_optin + 1024) / (smem + 1024);   // resident CTAs by shared memory
+      if (per_sm > 8) per_sm = 8;
+      if (per_sm < 1) per_sm = 1;
+      // as many CTAs as can be resident, then trimmed so that every CTA walks the same number of tiles
+      size_t grid = (size_t)ctx->sm_count * per_sm;
+      if (grid > t1) grid = t1;
+      const size_t tiles_per_cta = (t1 + grid - 1) / grid;
+      grid = (t1 + tiles_per_cta - 1) / tiles_per_cta;
+      const int pr = rmi_prof_begin(ctx, "q8_gemv");
+      cudaError_t le = rmi_launch(ctx, kern, dim3((unsigned)grid), dim3(STREAM_THREADS), smem, w->d_tile16, blocks, xq, xs, out,
+                                  out_stride, row_begin, row_end, row_begin / 16, t1, ctx->d_status, ctx->fanout);
+      rmi_prof_end(ctx, pr);
+      if (le != cudaSuccess) {
+        rmi_set_error("launch of q8_gemv_stream failed: %s", cudaGetErrorString(le));
+        return RMI_ERR_CUDA;
+      }
+      return rmi_post_launch(ctx, "q8_gemv_stream");
     }
   }
   const size_t tiles = ((row_end + 15) / 16 - row_begin / 16) * n_groups;

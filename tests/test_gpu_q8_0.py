@@ -267,3 +267,23 @@ def test_row_sharded_upload_equals_slices_of_the_full_result(rmi, ctx):
     for r in range(g):
         shard = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q8_0, k, n, row_begin=r * n // g, row_end=(r + 1) * n // g)
         assert np.array_equal(bits(rmi.matmul_q8_0(shard, x)), bits(full[:, r * n // g:(r + 1) * n // g]))
+
+
+@pytest.mark.parametrize("sem", SEMS)
+@pytest.mark.parametrize("n,k,m", [(16389, 2048, 1), (15000, 2080, 2), (20000, 8192, 1)])
+def test_streaming_gemv_many_long_rows_bit_exact(rmi, ctx, sem, n, k, m):
+    """More 16-row tiles than the one-copy-per-tile kernel takes and rows of 64 blocks or more: persistent CTAs
+    stream the records through a ring of bulk copies.  Ragged last tile, a chunk count that does not divide the
+    row (2080 = 65 blocks), a row range, and run-twice equality."""
+    ctx.set_semantics(sem)
+    wb = rmi.synth.q8_0_weight(n, k, seed=n % 97)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q8_0, k, n)
+    x = rmi.synth.normal((m, k), seed=3)
+    got = rmi.matmul_q8_0(w, x)
+    ref = orc.q8_forward_batched(wb, x, k, n, sem, threads=8)
+    assert np.array_equal(bits(got), bits(ref))
+    assert np.array_equal(bits(rmi.matmul_q8_0(w, x)), bits(got))
+    q8, sc = orc.quantize_q8_0(x, sem)
+    part = rmi.matmul_q8_0_prequantized_rows(w, q8, sc, m, row_begin=17, row_end=n - 33)
+    assert np.array_equal(bits(part[:, 17:n - 33]), bits(ref[:, 17:n - 33]))
+    w.free()
