@@ -320,6 +320,22 @@ int32_t rmi_session_set_prefill(rmi_ctx* ctx, rmi_session* s, int32_t mode);
 int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint32_t* prompts,
                              size_t n_prompt, size_t n_gen, uint32_t* out_tokens, float* prefill_ms,
                              float* gen_ms);
+/* The same step for hosts that sample themselves -- one iteration of the loop in Qwen3Session::generate_inner
+ * (src/models/qwen3.rs:657-1158; the reference hands the logits to its sampler, src/ops/sampler.rs) per call:
+ *   rmi_session_reset     position 0 (required before the calls below, and after rmi_session_generate)
+ *   rmi_session_prefill   tokens [batch, n_tokens] for positions 0..n_tokens-1 whose logits nobody needs (a
+ *                         prompt without its last token); batched or token loop per rmi_session_set_prefill
+ *   rmi_session_step      tokens [batch] at the current position; returns the greedy choice per sequence
+ *                         (next_tokens [batch], may be NULL) and, if logits_opt is not NULL, the logits
+ *                         [batch, vocab] for the host's own sampler.  Synchronous.  RMI_ERR_NONFINITE as in
+ *                         the reference ("Cannot sample non-finite logits").
+ *   rmi_session_position  the next position to be computed
+ * All pointers are host pointers. */
+int32_t rmi_session_reset(rmi_ctx* ctx, rmi_session* s);
+int32_t rmi_session_prefill(rmi_ctx* ctx, rmi_session* s, const uint32_t* tokens, size_t n_tokens);
+int32_t rmi_session_step(rmi_ctx* ctx, rmi_session* s, const uint32_t* tokens, uint32_t* next_tokens,
+                         float* logits_opt);
+int32_t rmi_session_position(const rmi_session* s, size_t* position);
 /* Debug/parity reads after a generate call: hidden state of the last step [batch, n_embd]
  * and logits of the last step [batch, vocab]. */
 int32_t rmi_session_read_hidden(rmi_ctx* ctx, rmi_session* s, float* hidden);

@@ -848,6 +848,29 @@ class Qwen3Session:
         self.prefill_ms, self.gen_ms = pre.value, gen.value
         return out[:, :max_new_tokens]
 
+    # per-step interface: the host feeds tokens and samples itself
+    def reset(self):
+        _check(lib().rmi_session_reset(self._ctx.handle, self._h))
+
+    def prefill(self, tokens):
+        """tokens [batch, n]: positions 0..n-1 whose logits nobody needs (a prompt without its last token)."""
+        tokens = np.ascontiguousarray(tokens, np.uint32).reshape(self.batch, -1)
+        _check(lib().rmi_session_prefill(self._ctx.handle, self._h, _p(tokens), _sz(tokens.shape[1])))
+
+    def step(self, tokens, want_logits: bool = False):
+        """tokens [batch] at the current position -> greedy next tokens [batch] (and the logits [batch, vocab])."""
+        tokens = np.ascontiguousarray(tokens, np.uint32).reshape(self.batch)
+        nxt = np.zeros(self.batch, np.uint32)
+        logits = np.zeros((self.batch, self.model.config["vocab"]), np.float32) if want_logits else None
+        _check(lib().rmi_session_step(self._ctx.handle, self._h, _p(tokens), _p(nxt), _p(logits)))
+        return (nxt, logits) if want_logits else nxt
+
+    @property
+    def position(self) -> int:
+        v = C.c_size_t()
+        _check(lib().rmi_session_position(self._h, C.byref(v)))
+        return v.value
+
     def hidden(self) -> np.ndarray:
         out = np.zeros((self.batch, self.model.config["n_embd"]), np.float32)
         _check(lib().rmi_session_read_hidden(self._ctx.handle, self._h, _p(out)))

@@ -59,6 +59,9 @@ struct rmi_session {
   float* argmax_v;
   uint32_t* argmax_i;
   // batched prompt processing (rows = sequences of a group x prompt positions); buffers allocated on first use
+  // per-step interface (rmi_session_reset / _prefill / _step): tokens live in the ring gen[batch][capacity + 1]
+  bool step_mode;
+  size_t pos;        // next position to be computed
   int prefill_mode;  // RMI_PREFILL_*
   size_t pf_rows;
   float *pf_x, *pf_xn, *pf_qkv, *pf_attn, *pf_proj;
@@ -668,6 +671,7 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
   for (size_t i = 0; i < d.batch * n_prompt; i++)
     RMI_REQUIRE(prompts[i] < d.vocab, RMI_ERR_BAD_SHAPE, "token id %u outside the vocabulary (%zu)", prompts[i], d.vocab);
   std::lock_guard<std::mutex> lock(ctx->mu);
+  s->step_mode = false;
   if (s->prompts_cap < d.batch * n_prompt) {
     cudaFree(s->prompts);
     s->prompts = nullptr;
@@ -748,6 +752,108 @@ extern "C" int32_t rmi_session_generate(rmi_ctx* ctx, rmi_session* s, const uint
   int flag = 0;
   RMI_CUDA_CHECK(cudaMemcpy(&flag, s->d_flag, 4, cudaMemcpyDeviceToHost));
   if (n_gen) RMI_CUDA_CHECK(cudaMemcpy(out_tokens, s->gen, d.batch * n_gen * 4, cudaMemcpyDeviceToHost));
+  RMI_REQUIRE(flag == 0, RMI_ERR_NONFINITE, "Cannot sample non-finite logits");
+  return RMI_OK;
+}
+
+// ---------------------------------------------------------------- per-step interface
+//
+// The host feeds one token per sequence and position and samples itself.  Tokens are kept in a device ring
+// gen[batch][capacity + 1]: the step at position p reads column p and its greedy choice lands in column p + 1
+// (where the next step reads it unless the host writes its own token there first).
+
+static int32_t ensure_step_mode(rmi_ctx* ctx, rmi_session* s) {
+  const decode_dims& d = s->d;
+  const size_t n_gen = d.capacity + 1;
+  if (s->gen_cap < d.batch * n_gen) {
+    RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+    cudaFree(s->gen);
+    s->gen = nullptr;
+    s->gen_cap = 0;
+    RMI_CUDA_CHECK(cudaMalloc(&s->gen, d.batch * n_gen * 4));
+    s->gen_cap = d.batch * n_gen;
+    drop_graphs(s);
+  }
+  return build_graphs(ctx, s, 0, n_gen);
+}
+
+extern "C" int32_t rmi_session_reset(rmi_ctx* ctx, rmi_session* s) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  RMI_TRY(ensure_step_mode(ctx, s));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->gen, 0, s->gen_cap * 4, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->d_step, 0, 4, ctx->stream));
+  RMI_CUDA_CHECK(cudaMemsetAsync(s->d_flag, 0, 4, ctx->stream));
+  s->pos = 0;
+  s->step_mode = true;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_position(const rmi_session* s, size_t* position) {
+  RMI_TRY(check_session(s));
+  RMI_REQUIRE(position != nullptr, RMI_ERR_BAD_HANDLE, "rmi_session_position: null argument");
+  *position = s->step_mode ? s->pos : 0;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_prefill(rmi_ctx* ctx, rmi_session* s, const uint32_t* tokens, size_t n_tokens) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  const decode_dims& d = s->d;
+  RMI_REQUIRE(s->step_mode, RMI_ERR_BAD_HANDLE, "call rmi_session_reset before the per-step interface");
+  RMI_REQUIRE(s->pos == 0, RMI_ERR_BAD_SHAPE, "rmi_session_prefill starts at position 0; the session is at %zu", s->pos);
+  RMI_REQUIRE(tokens != nullptr || n_tokens == 0, RMI_ERR_BAD_HANDLE, "rmi_session_prefill: null tokens");
+  RMI_REQUIRE(n_tokens <= d.capacity, RMI_ERR_BAD_SHAPE, "%zu positions exceed the session capacity %zu", n_tokens, d.capacity);
+  for (size_t i = 0; i < d.batch * n_tokens; i++)
+    RMI_REQUIRE(tokens[i] < d.vocab, RMI_ERR_BAD_SHAPE, "token id %u outside the vocabulary (%zu)", tokens[i], d.vocab);
+  if (n_tokens == 0) return RMI_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n_gen = d.capacity + 1;
+  RMI_CUDA_CHECK(cudaMemcpy2DAsync(s->gen, n_gen * 4, tokens, n_tokens * 4, n_tokens * 4, d.batch, cudaMemcpyHostToDevice,
+                                   ctx->stream));
+  if (prefill_batched(ctx, s, n_tokens)) {
+    RMI_TRY(prepare_prefill(ctx, s, n_tokens));
+    // the rows kernels read token (b, p) at prompts[b * stride + p]: the ring with its row stride
+    uint32_t* saved = s->prompts;
+    s->prompts = s->gen;
+    const int32_t st = enqueue_prefill(ctx, s, n_gen, n_tokens);
+    s->prompts = saved;
+    RMI_TRY(st);
+  } else {
+    for (size_t p = 0; p < n_tokens; p++) {
+      RMI_CUDA_CHECK(cudaGraphLaunch(s->exec_body, ctx->stream));
+      ctx->launches.fetch_add(1, std::memory_order_relaxed);
+    }
+  }
+  s->pos = n_tokens;
+  return RMI_OK;
+}
+
+extern "C" int32_t rmi_session_step(rmi_ctx* ctx, rmi_session* s, const uint32_t* tokens, uint32_t* next_tokens,
+                                    float* logits_opt) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(check_session(s));
+  const decode_dims& d = s->d;
+  RMI_REQUIRE(s->step_mode, RMI_ERR_BAD_HANDLE, "call rmi_session_reset before the per-step interface");
+  RMI_REQUIRE(s->pos < d.capacity, RMI_ERR_BAD_SHAPE, "session is full (%zu positions)", d.capacity);
+  RMI_REQUIRE(tokens != nullptr, RMI_ERR_BAD_HANDLE, "rmi_session_step: null tokens");
+  for (size_t b = 0; b < d.batch; b++)
+    RMI_REQUIRE(tokens[b] < d.vocab, RMI_ERR_BAD_SHAPE, "token id %u outside the vocabulary (%zu)", tokens[b], d.vocab);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const size_t n_gen = d.capacity + 1;
+  RMI_CUDA_CHECK(cudaMemcpy2DAsync(s->gen + s->pos, n_gen * 4, tokens, 4, 4, d.batch, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_CUDA_CHECK(cudaGraphLaunch(s->exec_full, ctx->stream));
+  ctx->launches.fetch_add(1, std::memory_order_relaxed);
+  if (next_tokens)
+    RMI_CUDA_CHECK(cudaMemcpy2DAsync(next_tokens, 4, s->gen + s->pos + 1, n_gen * 4, 4, d.batch, cudaMemcpyDeviceToHost,
+                                     ctx->stream));
+  if (logits_opt)
+    RMI_CUDA_CHECK(cudaMemcpyAsync(logits_opt, s->logits, d.batch * d.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  int flag = 0;
+  RMI_CUDA_CHECK(cudaMemcpyAsync(&flag, s->d_flag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  s->pos += 1;
   RMI_REQUIRE(flag == 0, RMI_ERR_NONFINITE, "Cannot sample non-finite logits");
   return RMI_OK;
 }

@@ -30,7 +30,95 @@ static std::vector<uint8_t> q8_0_uniform_row(int8_t value, float scale) {
   return row;
 }
 
-int main() {
+// The session's per-step interface from a compiled host: the host samples (first maximal index) from the logits
+// the library returns and must agree with the library's own greedy choice.
+static void session_checks(const char* gguf_path) {
+  rmi_ctx* ctx = rmi::context();
+  rmi_qwen3* model = nullptr;
+  rmi::check(rmi_qwen3_load(ctx, gguf_path, &model));
+  size_t vocab = 0;
+  rmi::check(rmi_qwen3_config(model, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &vocab));
+  rmi_session* s = nullptr;
+  const size_t batch = 2;
+  rmi::check(rmi_session_create(ctx, model, batch, 32, &s));
+  rmi::check(rmi_session_reset(ctx, s));
+  const uint32_t prompt[2][3] = {{1, 2, 3}, {7, 5, 3}};
+  rmi::check(rmi_session_prefill(ctx, s, &prompt[0][0], 3));
+  size_t pos = 99;
+  rmi::check(rmi_session_position(s, &pos));
+  EXPECT(pos == 3);
+  std::vector<uint32_t> tok = {4, 9}, next(batch);
+  std::vector<float> logits(batch * vocab);
+  for (int step = 0; step < 4; step++) {
+    rmi::check(rmi_session_step(ctx, s, tok.data(), next.data(), logits.data()));
+    for (size_t b = 0; b < batch; b++) {
+      size_t best = 0;
+      for (size_t i = 1; i < vocab; i++)
+        if (logits[b * vocab + i] > logits[b * vocab + best]) best = i;
+      EXPECT(best == next[b]);
+    }
+    tok = next;
+  }
+  rmi::check(rmi_session_position(s, &pos));
+  EXPECT(pos == 7);
+  rmi::check(rmi_session_free(ctx, s));
+  rmi::check(rmi_qwen3_free(ctx, model));
+}
+
+// One rank of the row-sharded matmul (world = 1): both exchanges of the shard group and the NCCL entry point must
+// reproduce the plain matmul bit for bit.
+static void sharded_checks() {
+  rmi_ctx* ctx = rmi::context();
+  const size_t n = 64, k = 64, m = 5;
+  std::vector<uint8_t> w;
+  for (size_t r = 0; r < n; r++)
+    for (size_t b = 0; b < k / 32; b++) {
+      auto blk = q8_0_uniform_row((int8_t)(1 + (r + b) % 5), 0.5f);
+      w.insert(w.end(), blk.begin(), blk.end());
+    }
+  rmi_weight* wt = nullptr;
+  rmi::check(rmi_weight_upload(ctx, RMI_GGML_Q8_0, w.data(), w.size(), k, n, 0, n, &wt));
+  std::vector<float> x(m * k), ref(m * n), got(m * n);
+  for (size_t i = 0; i < x.size(); i++) x[i] = 0.01f * (float)(i % 37) - 0.2f;
+  rmi::check(rmi_matmul_q8_0(ctx, wt, x.data(), m, ref.data()));
+  void* dx = nullptr;
+  rmi::check(rmi_dev_alloc(ctx, x.size() * 4, &dx));
+  rmi::check(rmi_h2d(ctx, dx, x.data(), x.size() * 4));
+  rmi_shard_group* g = nullptr;
+  rmi::check(rmi_shard_group_create(ctx, 1, 0, n, 8, &g));
+  uint8_t handles[192];
+  rmi::check(rmi_shard_group_export(ctx, g, handles));
+  rmi::check(rmi_shard_group_connect(ctx, g, handles));
+  for (int exchange : {RMI_EXCHANGE_FUSED_STORES, RMI_EXCHANGE_PEER_COPY}) {
+    float* result = nullptr;
+    rmi::check(rmi_matmul_q8_0_sharded_dev(ctx, g, wt, (const float*)dx, m, exchange, &result));
+    rmi::check(rmi_check_status(ctx));
+    rmi::check(rmi_d2h(ctx, got.data(), result, got.size() * 4));
+    EXPECT(std::memcmp(got.data(), ref.data(), got.size() * 4) == 0);
+  }
+  uint32_t epoch = 0;
+  rmi::check(rmi_shard_group_epoch(g, &epoch));
+  EXPECT(epoch == 2);
+  rmi::check(rmi_shard_group_free(ctx, g));
+  // NCCL entry point with a one-rank communicator created through the library
+  uint8_t id[128];
+  void* comm = nullptr;
+  rmi::check(rmi_nccl_unique_id(id));
+  rmi::check(rmi_nccl_comm_create(ctx, id, 1, 0, &comm));
+  void *dy = nullptr, *dgath = nullptr, *dout = nullptr;
+  rmi::check(rmi_dev_alloc(ctx, got.size() * 4, &dy));
+  rmi::check(rmi_dev_alloc(ctx, got.size() * 4, &dgath));
+  rmi::check(rmi_dev_alloc(ctx, got.size() * 4, &dout));
+  rmi::check(rmi_matmul_q8_0_dev(ctx, wt, (const float*)dx, m, (float*)dy));
+  rmi::check(rmi_allgather_cols_dev(ctx, comm, (const float*)dy, m, n, 1, (float*)dgath, (float*)dout));
+  rmi::check(rmi_d2h(ctx, got.data(), dout, got.size() * 4));
+  EXPECT(std::memcmp(got.data(), ref.data(), got.size() * 4) == 0);
+  rmi::check(rmi_nccl_comm_destroy(comm));
+  for (void* p : {dx, dy, dgath, dout}) rmi::check(rmi_dev_free(ctx, p));
+  rmi::check(rmi_weight_free(ctx, wt));
+}
+
+int main(int argc, char** argv) {
   try {
     std::vector<uint8_t> q8(32, 1);
     std::vector<float> sc(1, 1.0f);
@@ -102,6 +190,8 @@ int main() {
       }
       EXPECT(threw);
     }
+    sharded_checks();
+    if (argc > 1) session_checks(argv[1]);
   } catch (const std::exception& e) {
     std::printf("FAIL exception: %s\n", e.what());
     failures++;

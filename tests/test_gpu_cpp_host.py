@@ -23,6 +23,11 @@ def test_cpp_host_mirror_compiles_and_links(rmi, tmp_path):
 @pytest.mark.gpu
 def test_cpp_host_mirror_runs_the_reference_unit_tests(rmi, tmp_path):
     rmi.lib()
-    out = subprocess.run([_build(tmp_path)], capture_output=True, text=True, timeout=120)
+    # a two-layer model file for the per-step session interface
+    from tests.synth_model import tiny_cfg
+    cfg = tiny_cfg()
+    path = str(tmp_path / "tiny.gguf")
+    rmi.synth.write_qwen3_gguf(path, cfg, rmi.synth.qwen3_tensors(cfg, 3))
+    out = subprocess.run([_build(tmp_path), path], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "all kernel-trait checks passed" in out.stdout

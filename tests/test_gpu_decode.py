@@ -344,3 +344,51 @@ def test_batched_prefill_on_tensor_cores_under_avx2_semantics(rmi, ctx, tmp_path
     assert float(np.max(np.abs(h_tens - h_exact))) <= 2e-2 * float(np.max(np.abs(h_exact)))
     s.free()
     model.free()
+
+
+@pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON])
+@pytest.mark.parametrize("n_prompt", [5, 40])
+def test_per_step_interface_reproduces_generate(rmi, ctx, tmp_path_factory, sem, n_prompt):
+    """reset / prefill / step with host-side greedy sampling from the returned logits: the same tokens, hidden state
+    and logits as rmi_session_generate and the oracle (n_prompt = 40 takes the batched prefill, 5 the token loop)."""
+    ctx.set_semantics(sem)
+    cfg = tiny_cfg()
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=8)
+    model = rmi.Qwen3Model.from_file(path)
+    batch, n_gen = 2, 10
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], n_prompt, seed=80 + b) for b in range(batch)])
+    s = rmi.Qwen3Session(model, n_prompt + n_gen, batch=batch)
+    want = s.generate(prompts, n_gen)
+    want_hidden, want_logits = s.hidden(), s.logits()
+    s.reset()
+    assert s.position == 0
+    s.prefill(prompts[:, :-1])
+    assert s.position == n_prompt - 1
+    tok = prompts[:, -1].copy()
+    got = np.zeros((batch, n_gen), np.uint32)
+    for i in range(n_gen):
+        greedy, logits = s.step(tok, want_logits=True)
+        mine = np.array([orc.greedy_token(logits[b]) for b in range(batch)], np.uint32)   # the host's own sampler
+        assert np.array_equal(mine, greedy)
+        got[:, i] = mine
+        tok = mine
+        if i == n_gen - 2:   # generate() stops one step earlier: its last step produced token n_gen-1
+            pass
+    assert np.array_equal(got, want)
+    assert s.position == n_prompt - 1 + n_gen
+    ref = orc.Qwen3(cfg, tensors).generate(prompts[0], n_gen, sem=sem)
+    assert np.array_equal(got[0], ref)
+    # a session that is full refuses another step; generate() leaves step mode
+    s2 = rmi.Qwen3Session(model, 3, batch=batch)
+    s2.reset()
+    for _ in range(3):
+        s2.step(prompts[:, 0])
+    with pytest.raises(rmi.RmiError):
+        s2.step(prompts[:, 0])
+    s2.generate(prompts[:, :2], 1)
+    with pytest.raises(rmi.RmiError):
+        s2.step(prompts[:, 0])
+    s2.free()
+    del want_hidden, want_logits
+    s.free()
+    model.free()
