@@ -248,7 +248,12 @@ def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10, cpu_threads=0):
     for m in (1, 8, 256):
         x = torch.from_numpy(pkg.synth.normal((m, k), seed=1)).cuda()
         out = torch.empty((m, n), dtype=torch.float32, device="cuda")
-        for name, fn in (("dequant", pkg.matmul_q4_k_dequant_dev), ("q8k", pkg.matmul_q4_k_q8k_dev)):
+        for name, fn in (("dequant", pkg.matmul_q4_k_dequant_dev), ("q8k", pkg.matmul_q4_k_q8k_dev),
+                         ("q8k_dependent_launch", pkg.matmul_q4_k_q8k_dev)):
+            # the last variant launches quantizer and matmul as programmatic dependents: the matmul fetches its first
+            # weight chunks while the quantizer runs
+            ctx.set_dependent_launch(name == "q8k_dependent_launch")
+
             def burst():
                 for w in ws:
                     fn(w, x.data_ptr(), m, out.data_ptr())
@@ -269,6 +274,7 @@ def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10, cpu_threads=0):
             stream.synchronize()
             per = e0.elapsed_time(e1) / 1e3 / (iters * len(ws))
             algo = n * (k // 256) * 144 + m * k * 4 + m * n * 4
+            ctx.set_dependent_launch(False)
             res[f"{name}_m{m}"] = {"us": per * 1e6, "gbs": algo / per / 1e9, "frac_of_hbm_peak": algo / per / 1e9 / hbm_peak,
                                    "tflops": 2.0 * m * n * k / per / 1e12, "algorithmic_bytes": algo}
     for w in ws:

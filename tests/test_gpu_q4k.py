@@ -161,3 +161,30 @@ def test_q4_k_q8k_device_entry_point_matches_host_entry_point(rmi, ctx, sem, m):
     assert np.array_equal(bits(od.cpu().numpy()), bits(ref))
     w.free()
     ctx.set_semantics(rmi.SEM_AVX2)
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 64, 512), (70, 100, 1024), (256, 256, 4096)])
+def test_q4k_q8k_many_rows_tiled_kernel_bit_exact(rmi, ctx, m, n, k):
+    """m >= 32 under AVX2 semantics takes the tiled kernel (32 weight rows x 16 activation rows per CTA): every
+    output carries the bits of the per-row reference order; ragged tiles in both directions and a row range."""
+    ctx.set_semantics(rmi.SEM_AVX2)
+    wb = rmi.synth.q4_k_weight(n, k, seed=m + n)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q4_K, k, n)
+    x = rmi.synth.normal((m, k), seed=7)
+    import ctypes as C
+
+    def run(out, row_begin, row_end):
+        st = rmi.lib().rmi_matmul_q4_k_q8k(ctx.handle, w._h, C.c_void_p(x.ctypes.data), C.c_size_t(m),
+                                           C.c_void_p(out.ctypes.data), C.c_size_t(row_begin), C.c_size_t(row_end))
+        assert st == 0, rmi.lib().rmi_last_error()
+
+    got = np.zeros((m, n), np.float32)
+    run(got, 0, n)
+    for t in (0, 1, m // 2, m - 1):
+        ref = orc.q4k_forward_prepared(wb, x[t], k, n, 0, 1, orc.SEM_AVX2)
+        assert np.array_equal(bits(got[t]), bits(ref)), t
+    part = np.zeros((m, n), np.float32)
+    run(part, 5, n - 3)
+    assert np.array_equal(bits(part[:, 5:n - 3]), bits(got[:, 5:n - 3]))
+    assert not part[:, :5].any() and not part[:, n - 3:].any()
+    w.free()
