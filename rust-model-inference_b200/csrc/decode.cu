@@ -375,44 +375,50 @@ __global__ void __launch_bounds__(256)
   float* red = sc + group * cs;                                     // [group] (padded to 4)
   uint16_t* qs = reinterpret_cast<uint16_t*>(red + ((group + 3) & ~(size_t)3));  // [group][hd]
   uint16_t* p16 = qs + group * hd;                                  // [group][cs]
-  uint8_t* tiles = reinterpret_cast<uint8_t*>(p16 + group * cs);    // 2 x SEQ_TILE x hd f16 (16-byte aligned: cs % 4 == 0, hd % 8 == 0)
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(p16 + group * cs);    // 2 x SEQ_TILE rows (16-byte aligned: cs % 4 == 0, hd % 8 == 0)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-  const size_t row_bytes = hd * 2, tile_bytes = SEQ_TILE * row_bytes, row16 = hd / 8;
+  // K rows are padded by 16 bytes: the threads of a warp read the same words of different rows, and rows of exactly
+  // hd * 2 = 256 bytes would all start in the same bank
+  const size_t row_bytes = hd * 2, k_stride = row_bytes + 16, tile_bytes = SEQ_TILE * k_stride, row16 = hd / 8;
   const int n_tiles = (T + SEQ_TILE - 1) / SEQ_TILE;
   const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
   const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
   const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
-  auto stage = [&](const uint16_t* base, int tile, int buf) {
+  auto stage = [&](const uint16_t* base, int tile, int buf, size_t stride) {
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
     uint8_t* dst = tiles + (size_t)buf * tile_bytes;
     for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
-      cp_async16(dst + (i / row16) * row_bytes + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
+      cp_async16(dst + (i / row16) * stride + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
     cp_async_commit();
   };
   for (size_t i = tid; i < group * hd; i += blockDim.x) qs[i] = q16[b * nq + kvh * group * hd + i];
-  stage(kbase, 0, 0);
+  stage(kbase, 0, 0, k_stride);
   // scores[g][t] = f32(sum_f64 q*k) * kq_scale (dot.rs:115-118)
   for (int tile = 0; tile < n_tiles; tile++) {
-    if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1, k_stride);
     if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
     for (size_t item = tid; item < (size_t)nt * group; item += blockDim.x) {
       const size_t tl = item / group, g = item % group;
-      const uint32_t* kr = reinterpret_cast<const uint32_t*>(kt + tl * row_bytes);
-      const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + g * hd);
+      const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride);
+      const uint4* qr = reinterpret_cast<const uint4*>(qs + g * hd);
       double s = 0.0;
-      for (size_t i = 0; i < hd / 2; i++) {
-        const uint32_t kk = kr[i], qq = qr[i];
-        s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq & 0xffff)), f16_bits_to_f32((uint16_t)(kk & 0xffff)));
-        s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qq >> 16)), f16_bits_to_f32((uint16_t)(kk >> 16)));
+      for (size_t i = 0; i < hd / 8; i++) {
+        const uint4 kv = kr[i], qv = qr[i];
+        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qw[e] & 0xffff)), f16_bits_to_f32((uint16_t)(kw[e] & 0xffff)));
+          s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qw[e] >> 16)), f16_bits_to_f32((uint16_t)(kw[e] >> 16)));
+        }
       }
       sc[g * cs + t0 + tl] = __fmul_rn((float)s, kq_scale);
     }
     __syncthreads();
   }
-  stage(vbase, 0, 0);  // the first V tile travels while the soft-max is evaluated
+  stage(vbase, 0, 0, row_bytes);  // the first V tile travels while the soft-max is evaluated
   // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
   for (size_t g = warp; g < group; g += nwarp) {
     float mx = -INFINITY;
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(256)
   // out[g][d] = f32(sum_f64 over t of v[t][d] * p[g][t]), one output element per thread and pass
   double accv[2] = {0.0, 0.0};
   for (int tile = 0; tile < n_tiles; tile++) {
-    if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1);
+    if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1, row_bytes);
     if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     const uint16_t* vt = reinterpret_cast<const uint16_t*>(tiles + (size_t)(tile & 1) * tile_bytes);
@@ -1010,7 +1016,7 @@ int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t*
                              float* scales) {
   const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
   const size_t smem = group * cs * 4 + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 2 + group * cs * 2 +
-                      2 * (size_t)SEQ_TILE * d.hd * 2;
+                      2 * (size_t)SEQ_TILE * (d.hd * 2 + 16);
   auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2>
                                        : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON>
                                                                    : attention_seq_kernel<RMI_SEM_SCALAR>);
