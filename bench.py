@@ -306,7 +306,7 @@ def q4k_bench(pkg, ctx, torch, stream, hbm_peak, iters=10, cpu_threads=0):
 FORWARDS = {"session": 0, "text": 1, "text_f32kv": 2, "logits": 3, "logits_f32kv": 4}
 
 
-def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="session"):
+def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="session", lean=False):
     ctx.set_semantics(sem)
     model = pkg.Qwen3Model.from_file(path)
     s = pkg.Qwen3Session(model, n_prompt + n_gen, batch=batch, forward=FORWARDS[forward])
@@ -316,7 +316,7 @@ def decode_bench(pkg, ctx, cfg, path, batch, n_prompt, n_gen, sem, forward="sess
            "gen_ms": s.gen_ms, "prefill_ms": s.prefill_ms, "first_tokens": [int(t) for t in toks[0, :4]],
            "prefill": "prompt positions as rows through every operator; cache rows bit-identical to the reference's "
                       "token loop (AVX2: eight-lane order on CUDA cores)"}
-    if forward == "session":
+    if forward == "session" and not lean:
         s.set_prefill(pkg.PREFILL_TOKEN_LOOP)
         s.generate(prompts, 1)
         res["prefill_ms_token_loop"] = s.prefill_ms
@@ -519,6 +519,8 @@ def main():
     ap.add_argument("--decode-forward", default="session", choices=sorted(FORWARDS),
                     help="which of the reference's copies of the forward the session reproduces "
                          "(text_f32kv holds at most 512 positions)")
+    ap.add_argument("--decode-lean", action="store_true",
+                    help="decode workload: skip the token-loop and tensor-core prefill comparisons (short runs under a profiler)")
     ap.add_argument("--workload", default="ffn", choices=["ffn", "sharded", "gemv", "decode", "q4k"],
                     help="ffn: the headline line; sharded: BASELINE config 5 (separate JSON line)")
     args = ap.parse_args()
@@ -572,7 +574,7 @@ def main():
             if not os.path.exists(path):
                 pkg.synth.write_qwen3_gguf(path, cfg, pkg.synth.qwen3_tensors(cfg, 0))
             res, _ = decode_bench(pkg, ctx, cfg, path, args.decode_batch, args.decode_prompt, args.decode_gen, sem,
-                                  args.decode_forward)
+                                  args.decode_forward, lean=args.decode_lean)
             kv = 28 * (args.decode_prompt + args.decode_gen // 2) * 1024 * 2 * 2
             roof = hbm_peak * 1e9 / (633233408 + args.decode_batch * kv) * args.decode_batch
             print(json.dumps({"metric": "Qwen3-0.6B-architecture greedy decode throughput", "value": res["tok_s"],
@@ -621,7 +623,23 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The step's kernels (quantizer, gate|up GEMM, down GEMM) run as programmatic dependents
+    # (rmi_set_dependent_launch): each sets up its barriers and tensor memory while its predecessor drains.  The same
+    # steps without it are timed beside (value_plain_launch).
+    ctx.set_dependent_launch(False)
     for i in range(max(args.warmup, R)):   # also builds the tcgen05 weight layout of every set
+        step(i)
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_plain = max(3, min(args.steps, 4 * R))
+    p0.record(stream)
+    for i in range(n_plain):
+        step(i)
+    p1.record(stream)
+    barrier()
+    ms_plain = p0.elapsed_time(p1) / n_plain
+    ctx.set_dependent_launch(True)
+    for i in range(max(3, args.warmup)):
         step(i)
     barrier()
     launches0 = ctx.launch_count()
@@ -730,13 +748,17 @@ def main():
            "api": "rmi_ffn_swiglu_q8_0_pipelined (host pointers, pinned; copies of neighbouring steps overlap the "
                   "arithmetic); serial_value = one rmi_ffn_swiglu_q8_0 call per step"}
 
+    ctx.set_dependent_launch(False)
     line = {"metric": METRIC, "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "configs[1]: Q8_0 prefill GEMM + fused FFN, M=512 K=1024 n_ff=3072",
                        "semantics": args.semantics, "l2_hygiene": f"{R} distinct weight/input/output sets "
                        f"({R * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB) rotated every step",
-                       "int8_ops_per_step": OPS_STEP, "parallelism": f"replicas x{world}, no collective"},
+                       "int8_ops_per_step": OPS_STEP, "parallelism": f"replicas x{world}, no collective",
+                       "launch": "programmatic dependent launch (rmi_set_dependent_launch(1)); value_plain_launch = "
+                                 "the same steps launched plainly, this rank"},
+            "value_plain_launch": OPS_STEP / (ms_plain / 1e3) / 1e12,
             "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary()}
     if exact is not None:
         line["avx2_bit_exact_cuda_cores"] = exact

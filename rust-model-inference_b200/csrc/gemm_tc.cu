@@ -348,6 +348,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_kernel(const gemm_params p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = hdr->tmem_base;
+  // Dependent launch: barriers and tensor memory are set up while the preceding kernel drains; everything below
+  // reads what it wrote (activation images and scales) or writes what it may still read.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -610,8 +614,12 @@ int32_t launch_nt(rmi_ctx* ctx, const gemm_params& p, size_t m_tiles) {
   pp.n_tiles = m_tiles * p.n_tiles_n;
   size_t grid = pp.n_tiles < (size_t)ctx->sm_count ? pp.n_tiles : (size_t)ctx->sm_count;
   const int pr = rmi_prof_begin(ctx, EPI == GEMM_EPI_SWIGLU_Q8 ? "gemm_tc_swiglu" : "gemm_tc");
-  kern<<<(unsigned)grid, THREADS, smem, ctx->stream>>>(pp);
+  const cudaError_t le = rmi_launch(ctx, kern, dim3((unsigned)grid), dim3(THREADS), smem, pp);
   rmi_prof_end(ctx, pr);
+  if (le != cudaSuccess) {
+    rmi_set_error("launch of gemm_tc failed: %s", cudaGetErrorString(le));
+    return RMI_ERR_CUDA;
+  }
   return rmi_post_launch(ctx, "gemm_tc");
 }
 

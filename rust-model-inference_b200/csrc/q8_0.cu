@@ -82,6 +82,8 @@ template <int SEM>
 __global__ void q8_quantize_kernel(const float* __restrict__ x, size_t m, size_t n,
                                    uint8_t* __restrict__ q8, float* __restrict__ scales,
                                    int out_mode) {
+  pdl_wait();               // x may come from the preceding kernel of a dependent launch
+  pdl_launch_dependents();
   size_t blocks = n / 32;
   size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
   int lane = threadIdx.x & 31;
@@ -862,10 +864,12 @@ int32_t launch_q8_quantize(rmi_ctx* ctx, const float* x, size_t m, size_t n, uin
   size_t warps = m * (n / 32);
   if (warps == 0) return RMI_OK;
   unsigned grid = (unsigned)((warps + 7) / 8);
-  switch (ctx->sem) {
-    case RMI_SEM_AVX2: q8_quantize_kernel<RMI_SEM_AVX2><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
-    case RMI_SEM_NEON: q8_quantize_kernel<RMI_SEM_NEON><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
-    default: q8_quantize_kernel<RMI_SEM_SCALAR><<<grid, 256, 0, ctx->stream>>>(x, m, n, q8, scales, out_mode); break;
+  auto kern = ctx->sem == RMI_SEM_AVX2 ? q8_quantize_kernel<RMI_SEM_AVX2>
+                                       : (ctx->sem == RMI_SEM_NEON ? q8_quantize_kernel<RMI_SEM_NEON> : q8_quantize_kernel<RMI_SEM_SCALAR>);
+  const cudaError_t le = rmi_launch(ctx, kern, dim3(grid), dim3(256), 0, x, m, n, q8, scales, out_mode);
+  if (le != cudaSuccess) {
+    rmi_set_error("launch of q8_quantize failed: %s", cudaGetErrorString(le));
+    return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "q8_quantize");
 }
