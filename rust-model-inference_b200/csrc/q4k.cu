@@ -840,25 +840,34 @@ __global__ void q4k_dequant_matmul_kernel(const uint8_t* __restrict__ w, size_t 
 // group: the low or the high nibbles of 32 quant bytes, one 6-bit scale/min pair), 256 threads with 8 x 4
 // accumulators each, two shared-memory stages.
 constexpr int Q4G_BN = 128, Q4G_BM = 64, Q4G_BK = 32, Q4G_PAD = 4;
+// Two groups of 256 threads share a tile and take alternate K chunks (each with its own pair of shared-memory
+// stages and its own named barrier), so that a CTA brings 16 warps to an SM: a 4096 x 4096 weight with 256
+// activation rows is only 128 tiles, and 8 warps per SM leave the FMA pipe idle most of the time.  The two
+// partial tiles are added at the end (group 0 + group 1); forward_dequant carries a tolerance, not an order.
+constexpr int Q4G_KGROUPS = 2;
+constexpr size_t Q4G_GROUP_SMEM = 2 * Q4G_BK * (Q4G_BN + Q4G_PAD + Q4G_BM + Q4G_PAD) * 4;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256 * Q4G_KGROUPS)
     q4k_dequant_gemm_kernel(const uint8_t* __restrict__ w, size_t nb, size_t n_rows, const float* __restrict__ x,
                             size_t m_rows, float* __restrict__ out) {
   extern __shared__ __align__(16) uint8_t q4g_smem[];
-  float (*Ws)[Q4G_BK][Q4G_BN + Q4G_PAD] = reinterpret_cast<float (*)[Q4G_BK][Q4G_BN + Q4G_PAD]>(q4g_smem);
+  const int kg = threadIdx.x >> 8, tid = threadIdx.x & 255;
+  uint8_t* gsm = q4g_smem + (size_t)kg * Q4G_GROUP_SMEM;
+  float (*Ws)[Q4G_BK][Q4G_BN + Q4G_PAD] = reinterpret_cast<float (*)[Q4G_BK][Q4G_BN + Q4G_PAD]>(gsm);
   float (*Xs)[Q4G_BK][Q4G_BM + Q4G_PAD] =
-      reinterpret_cast<float (*)[Q4G_BK][Q4G_BM + Q4G_PAD]>(q4g_smem + 2 * Q4G_BK * (Q4G_BN + Q4G_PAD) * 4);
-  const int tid = threadIdx.x;
+      reinterpret_cast<float (*)[Q4G_BK][Q4G_BM + Q4G_PAD]>(gsm + 2 * Q4G_BK * (Q4G_BN + Q4G_PAD) * 4);
   const size_t n0 = (size_t)blockIdx.x * Q4G_BN, m0 = (size_t)blockIdx.y * Q4G_BM;
   const size_t K = nb * 256;
-  const int n_chunks = (int)(nb * 8);
+  const int n_chunks = (int)(nb * 8);   // a multiple of 8: both groups walk the same number of chunks
+  auto group_sync = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(1 + kg) : "memory"); };
   // loader roles: weights - thread (row tid/2, 16 of the chunk's 32 values); activations - thread (row tid/4, 8 values)
   const int wr = tid >> 1, wh = tid & 1;
   const int xr = tid >> 2, xq = tid & 3;
   const bool w_ok = n0 + wr < n_rows, x_ok = m0 + xr < m_rows;
   const uint8_t* wrow = w + (n0 + wr) * nb * 144;
   const float* xrow = x + (m0 + xr) * K;
-  // compute roles: tx = 8 consecutive weight rows, ty = 4 consecutive activation rows
+  // compute roles: tx = weight rows 4tx..4tx+3 and 64+4tx..64+4tx+3 (the sixteen tx of a warp read 256 contiguous
+  // bytes per load: no bank conflict), ty = 4 consecutive activation rows
   const int tx = tid & 15, ty = tid >> 4;
   float acc[4][8];
 #pragma unroll
@@ -887,28 +896,30 @@ __global__ void __launch_bounds__(256)
     scale_min_w(hv.y, hv.z, hv.w, cc, &sc, &mn);
     const float d1 = __fmul_rn(f16_bits_to_f32((uint16_t)(hv.x & 0xffffu)), (float)sc);
     const float m1 = __fmul_rn(f16_bits_to_f32((uint16_t)(hv.x >> 16)), (float)mn);
+    const float c1 = -__fmul_rn(d1, 8388608.0f);
     const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-    for (int v = 0; v < 16; v++) {
-      const uint32_t byte = (q[v >> 2] >> (8 * (v & 3))) & 0xffu;
-      const float qf = (float)(hi ? (byte >> 4) : (byte & 0xFu));
-      Ws[st][wh * 16 + v][wr] = w_ok ? __fsub_rn(__fmul_rn(d1, qf), m1) : 0.0f;
+    for (int v4 = 0; v4 < 4; v4++) {
+      const uint32_t nib = hi ? (q[v4] >> 4) & 0x0F0F0F0Fu : q[v4] & 0x0F0F0F0Fu;
+#pragma unroll
+      for (int v = 0; v < 4; v++)   // (d*sc)*q as fma(d*sc, 2^23 + q, -(d*sc)*2^23): exact product, one rounding
+        Ws[st][wh * 16 + 4 * v4 + v][wr] = w_ok ? __fsub_rn(__fmaf_rn(d1, byte_plus_2p23(nib, v), c1), m1) : 0.0f;
     }
     const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
     for (int v = 0; v < 8; v++) Xs[st][xq * 8 + v][xr] = x_ok ? xv[v] : 0.0f;
   };
 
-  fetch(0);
-  stash(0, 0);
-  __syncthreads();
-  for (int c = 0; c < n_chunks; c++) {
-    const int st = c & 1;
-    if (c + 1 < n_chunks) fetch(c + 1);
+  fetch(kg);
+  stash(kg, 0);
+  group_sync();
+  for (int c = kg, it = 0; c < n_chunks; c += Q4G_KGROUPS, it++) {
+    const int st = it & 1;
+    if (c + Q4G_KGROUPS < n_chunks) fetch(c + Q4G_KGROUPS);
 #pragma unroll
     for (int k = 0; k < Q4G_BK; k++) {
-      const float4 a0 = *reinterpret_cast<const float4*>(&Ws[st][k][tx * 8]);
-      const float4 a1 = *reinterpret_cast<const float4*>(&Ws[st][k][tx * 8 + 4]);
+      const float4 a0 = *reinterpret_cast<const float4*>(&Ws[st][k][tx * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&Ws[st][k][64 + tx * 4]);
       const float4 b0 = *reinterpret_cast<const float4*>(&Xs[st][k][ty * 4]);
       const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float bv[4] = {b0.x, b0.y, b0.z, b0.w};
@@ -917,21 +928,37 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int b = 0; b < 8; b++) acc[a][b] = __fmaf_rn(av[b], bv[a], acc[a][b]);
     }
-    if (c + 1 < n_chunks) stash(c + 1, st ^ 1);
-    __syncthreads();
+    if (c + Q4G_KGROUPS < n_chunks) stash(c + Q4G_KGROUPS, st ^ 1);
+    group_sync();
   }
+  // group 1 hands its partial tile over through its own (now idle) stages: [32 values][256 threads]
+  float* hand = reinterpret_cast<float*>(q4g_smem + Q4G_GROUP_SMEM);
+  if (kg == 1) {
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+      for (int b = 0; b < 8; b++) hand[(a * 8 + b) * 256 + tid] = acc[a][b];
+  }
+  __syncthreads();
+  if (kg != 0) return;
+#pragma unroll
+  for (int a = 0; a < 4; a++)
+#pragma unroll
+    for (int b = 0; b < 8; b++) acc[a][b] = __fadd_rn(acc[a][b], hand[(a * 8 + b) * 256 + tid]);
 #pragma unroll
   for (int a = 0; a < 4; a++) {
     const size_t mrow = m0 + ty * 4 + a;
     if (mrow >= m_rows) continue;
-    float* o = out + mrow * n_rows + n0 + tx * 8;
-    if (n0 + tx * 8 + 8 <= n_rows && (n_rows & 3) == 0) {
+    float* o = out + mrow * n_rows + n0 + tx * 4;   // columns 4tx..4tx+3, then 64 further on
+    if (n0 + 64 + tx * 4 + 4 <= n_rows && (n_rows & 3) == 0) {
       *reinterpret_cast<float4*>(o) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
-      *reinterpret_cast<float4*>(o + 4) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+      *reinterpret_cast<float4*>(o + 64) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
     } else {
 #pragma unroll
-      for (int b = 0; b < 8; b++)
-        if (n0 + tx * 8 + b < n_rows) o[b] = acc[a][b];
+      for (int b = 0; b < 8; b++) {
+        const size_t col = n0 + tx * 4 + (b < 4 ? b : 60 + b);
+        if (col < n_rows) out[mrow * n_rows + col] = acc[a][b];
+      }
     }
   }
 }
@@ -1073,12 +1100,12 @@ int32_t launch_q4k_dequant_matmul(rmi_ctx* ctx, const rmi_weight* w, const float
   const size_t nb = w->n_in / 256;
   if (m >= 32) {  // compute-bound: tiled f32 GEMM with on-the-fly decode
     dim3 g2((unsigned)((w->n_rows + Q4G_BN - 1) / Q4G_BN), (unsigned)((m + Q4G_BM - 1) / Q4G_BM));
-    constexpr size_t smem = 2 * Q4G_BK * (Q4G_BN + Q4G_PAD + Q4G_BM + Q4G_PAD) * 4;
+    constexpr size_t smem = Q4G_KGROUPS * Q4G_GROUP_SMEM;
     if (cudaFuncSetAttribute(q4k_dequant_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       rmi_set_error("cudaFuncSetAttribute(%zu B shared) failed", smem);
       return RMI_ERR_CUDA;
     }
-    q4k_dequant_gemm_kernel<<<g2, 256, smem, ctx->stream>>>(w->d_raw, nb, w->n_rows, x, m, out);
+    q4k_dequant_gemm_kernel<<<g2, 256 * Q4G_KGROUPS, smem, ctx->stream>>>(w->d_raw, nb, w->n_rows, x, m, out);
     return rmi_post_launch(ctx, "q4k_dequant_gemm");
   }
   size_t t = 0;
