@@ -188,3 +188,31 @@ def test_q4k_q8k_many_rows_tiled_kernel_bit_exact(rmi, ctx, m, n, k):
     assert np.array_equal(bits(part[:, 5:n - 3]), bits(got[:, 5:n - 3]))
     assert not part[:, :5].any() and not part[:, n - 3:].any()
     w.free()
+
+
+@pytest.mark.parametrize("m", [2, 5, 8, 13, 31])
+def test_q4k_q8k_few_rows_stream_and_split_k_kernels_bit_exact(rmi, ctx, m):
+    """m < 32 under AVX2 semantics: groups of 8 / 4 rows through the streaming kernel, the last 2 / 1 rows through
+    the split-K kernel.  Six super-blocks per row (one full chunk of four and a short one), a weight row count that
+    is no multiple of the 16- and 4-row tiles, and a row range that starts and ends inside a tile."""
+    ctx.set_semantics(rmi.SEM_AVX2)
+    n, k = 100, 1536
+    wb = rmi.synth.q4_k_weight(n, k, seed=20 + m)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q4_K, k, n)
+    x = rmi.synth.normal((m, k), seed=8)
+    import ctypes as C
+
+    def run(out, row_begin, row_end):
+        st = rmi.lib().rmi_matmul_q4_k_q8k(ctx.handle, w._h, C.c_void_p(x.ctypes.data), C.c_size_t(m),
+                                           C.c_void_p(out.ctypes.data), C.c_size_t(row_begin), C.c_size_t(row_end))
+        assert st == 0, rmi.lib().rmi_last_error()
+
+    got = np.zeros((m, n), np.float32)
+    run(got, 0, n)
+    ref = np.stack([orc.q4k_forward_prepared(wb, x[t], k, n, 0, 1, orc.SEM_AVX2) for t in range(m)])
+    assert np.array_equal(bits(got), bits(ref))
+    part = np.zeros((m, n), np.float32)
+    run(part, 5, n - 3)
+    assert np.array_equal(bits(part[:, 5:n - 3]), bits(ref[:, 5:n - 3]))
+    assert not part[:, :5].any() and not part[:, n - 3:].any()
+    w.free()
