@@ -275,7 +275,10 @@ int32_t rmi_qwen3_free(rmi_ctx* ctx, rmi_qwen3* model);
 int32_t rmi_qwen3_config(const rmi_qwen3* model, size_t* n_embd, size_t* n_layer, size_t* n_head,
                          size_t* n_head_kv, size_t* head_dim, size_t* n_ff, size_t* vocab);
 /* Qwen3Session::new (src/models/qwen3.rs:440-550) for `batch` independent sequences:
- * F16 KV cache [batch][n_layer][capacity][n_head_kv*head_dim] x2 in HBM plus all scratch. */
+ * F16 KV cache [batch][n_layer][capacity][n_head_kv*head_dim] x2 in HBM plus all scratch.  Any
+ * capacity in 1..=n_ctx is accepted, as in the reference (:442-447): up to a few thousand positions the
+ * attention kernels keep their score rows in shared memory, beyond that the same arithmetic runs with
+ * the rows in a global scratch area (6 bytes per head and position). */
 int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size_t batch, size_t capacity,
                            rmi_session** out);
 int32_t rmi_session_free(rmi_ctx* ctx, rmi_session* s);

@@ -358,12 +358,16 @@ __global__ void __launch_bounds__(256)
 // sequential f64 P.V); K and V stream through two shared-memory tiles of SEQ_TILE positions.
 constexpr int SEQ_TILE = 128;
 
-template <int SEM>
+// GS: the score and probability rows ([group][capacity] f32 and f16) live in a global scratch area instead of shared
+// memory (g_sc / g_p16, one slice per CTA), for capacities whose rows do not fit: only this CTA touches its slice and
+// the phases are separated by CTA barriers, so the arithmetic and its order are unchanged.
+template <int SEM, bool GS>
 __global__ void __launch_bounds__(256)
     attention_seq_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
                          const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
                          size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
-                         float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales) {
+                         float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales,
+                         float* __restrict__ g_sc, uint16_t* __restrict__ g_p16) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -371,11 +375,12 @@ __global__ void __launch_bounds__(256)
   const size_t group = n_head / n_head_kv, nq = n_head * hd, nk = n_head_kv * hd;
   const int T = *d_step + 1;
   const size_t cs = (capacity + 7) & ~(size_t)7;  // keeps every array 16-byte aligned
-  float* sc = reinterpret_cast<float*>(smem);                       // [group][cs]
-  float* red = sc + group * cs;                                     // [group] (padded to 4)
+  const size_t slice = (b * n_head_kv + kvh) * group * cs;         // GS: this CTA's rows in the scratch area
+  float* sc = GS ? g_sc + slice : reinterpret_cast<float*>(smem);   // [group][cs]
+  float* red = GS ? reinterpret_cast<float*>(smem) : sc + group * cs;  // [group] (padded to 4)
   uint16_t* qs = reinterpret_cast<uint16_t*>(red + ((group + 3) & ~(size_t)3));  // [group][hd]
-  uint16_t* p16 = qs + group * hd;                                  // [group][cs]
-  uint8_t* tiles = reinterpret_cast<uint8_t*>(p16 + group * cs);    // 2 x SEQ_TILE rows (16-byte aligned: cs % 4 == 0, hd % 8 == 0)
+  uint16_t* p16 = GS ? g_p16 + slice : qs + group * hd;             // [group][cs]
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(GS ? qs + group * hd : p16 + group * cs);  // 2 x SEQ_TILE rows (16-byte aligned)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
   // K rows are padded by 16 bytes: the threads of a warp read the same words of different rows, and rows of exactly
   // hd * 2 = 256 bytes would all start in the same bank
@@ -1006,27 +1011,48 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
 }
 
 // One CTA per (kv head, sequence); needs group * head_dim <= 512 (two outputs per thread).
-bool attention_seq_eligible(const decode_dims& d) {
+bool attention_seq_shape_ok(const decode_dims& d) {
   const size_t group = d.n_head / d.n_head_kv;
-  return group * d.hd <= 512 && (group * d.hd) % 32 == 0 && d.hd % 8 == 0 && d.batch * d.n_head_kv >= 128;
+  return group * d.hd <= 512 && (group * d.hd) % 32 == 0 && d.hd % 8 == 0;
+}
+
+// ... and preferred over the cluster kernel when there are enough (sequence, kv head) pairs to fill the GPU
+bool attention_seq_eligible(const decode_dims& d) { return attention_seq_shape_ok(d) && d.batch * d.n_head_kv >= 128; }
+
+// Shared memory of attention_seq_kernel; global_scores: without the [group][capacity] score and probability rows.
+size_t attention_seq_smem_bytes(const decode_dims& d, bool global_scores) {
+  const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
+  return (global_scores ? 0 : group * cs * 4 + group * cs * 2) + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 2 +
+         2 * (size_t)SEQ_TILE * (d.hd * 2 + 16);
+}
+
+// Bytes of global scratch for the score rows (f32) and the probability rows (f16) of all CTAs.
+size_t attention_seq_scratch_bytes(const decode_dims& d) {
+  const size_t cs = (d.capacity + 7) & ~(size_t)7;
+  return d.batch * d.n_head * cs * 6;
 }
 
 int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
                              const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
-                             float* scales) {
-  const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
-  const size_t smem = group * cs * 4 + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 2 + group * cs * 2 +
-                      2 * (size_t)SEQ_TILE * (d.hd * 2 + 16);
-  auto kern = ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2>
-                                       : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON>
-                                                                   : attention_seq_kernel<RMI_SEM_SCALAR>);
+                             float* scales, void* score_scratch) {
+  const size_t cs = (d.capacity + 7) & ~(size_t)7;
+  const bool gs = score_scratch != nullptr;
+  const size_t smem = attention_seq_smem_bytes(d, gs);
+  float* g_sc = reinterpret_cast<float*>(score_scratch);
+  uint16_t* g_p16 = gs ? reinterpret_cast<uint16_t*>(g_sc + d.batch * d.n_head * cs) : nullptr;
+  auto kern = gs ? (ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2, true>
+                                             : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON, true>
+                                                                         : attention_seq_kernel<RMI_SEM_SCALAR, true>))
+                 : (ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2, false>
+                                             : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON, false>
+                                                                         : attention_seq_kernel<RMI_SEM_SCALAR, false>));
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     rmi_set_error("attention needs %zu B of shared memory", smem);
     return RMI_ERR_UNSUPPORTED;
   }
   if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head_kv, (unsigned)d.batch), dim3(256), smem, q16, k_cache, v_cache, d_step,
-                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales) != cudaSuccess) {
+                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales, g_sc, g_p16) != cudaSuccess) {
     rmi_set_error("launch of attention_seq failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }
@@ -1091,6 +1117,13 @@ int32_t launch_attention_scores_f16kv(rmi_ctx* ctx, const decode_dims& d, const 
                                       const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out,
                                       uint8_t* q8, float* scales) {
   return launch_attention_softmax_t<true, true>(ctx, d, q32, k_cache, v_cache, d_step, layer, attn_out, q8, scales);
+}
+
+size_t cli_attention_smem_bytes(const decode_dims& d, int forward) {
+  const size_t cap4 = (d.capacity + 3) & ~(size_t)3;
+  if (forward == RMI_FORWARD_APP_TEXT) return (2 * cap4 + d.hd + 256) * 4 + 2 * ATT_TILE * d.hd * 2;
+  const size_t elem = (forward == RMI_FORWARD_APP_LOGITS) ? 2 : 4;   // F16 cache, else one of the F32-cache variants
+  return (cap4 + d.hd + 16 * d.hd + 32) * 4 + 2 * SM_TILE * (d.hd * elem + 16);
 }
 
 size_t argmax_scratch_floats(size_t batch) { return batch * ARGMAX_SLICES; }

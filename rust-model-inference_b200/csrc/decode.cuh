@@ -21,10 +21,16 @@ int32_t launch_attention(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16
                          uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                          float* scales, const float* qkv = nullptr, const float* q_norm = nullptr,
                          const float* k_norm = nullptr, const float* rope = nullptr);
+bool attention_seq_shape_ok(const decode_dims& d);
 bool attention_seq_eligible(const decode_dims& d);
+size_t attention_seq_smem_bytes(const decode_dims& d, bool global_scores);
+size_t attention_seq_scratch_bytes(const decode_dims& d);
+// score_scratch: null = score rows in shared memory; else attention_seq_scratch_bytes(d) bytes of device memory
 int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
                              const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
-                             float* scales);
+                             float* scales, void* score_scratch);
+// shared memory per CTA of the attention kernel a CLI forward variant (RMI_FORWARD_APP_*) uses
+size_t cli_attention_smem_bytes(const decode_dims& d, int forward);
 int32_t launch_attention_online(rmi_ctx* ctx, const decode_dims& d, const float* q32, const uint16_t* k_cache,
                                 const uint16_t* v_cache, const int* d_step, size_t layer, float* attn_out, uint8_t* q8,
                                 float* scales);

@@ -45,6 +45,7 @@ struct rmi_session {
   uint16_t *k_cache, *v_cache;
   float *x, *x2, *qkv, *proj, *gu, *logits, *rope, *attn_dbg;  // x2: second residual buffer of the fused-norm path
   bool fused_norm;
+  void* attn_scratch;  // score / probability rows of attention_seq_kernel when they do not fit in shared memory
   int forward;    // RMI_FORWARD_*: which of the reference's copies of the forward this session reproduces
   float* q32;     // f32 query after norm + rotation (CLI forward)
   float *k32_cache, *v32_cache;  // F32 caches of the CLI forward with `--kv-cache f32`; allocated on first use
@@ -279,7 +280,7 @@ static void free_session(rmi_session* s) {
   if (!s) return;
   drop_graphs(s);
   cudaFree(s->k_cache); cudaFree(s->v_cache); cudaFree(s->x); cudaFree(s->x2); cudaFree(s->qkv); cudaFree(s->proj);
-  cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8);
+  cudaFree(s->gu); cudaFree(s->logits); cudaFree(s->rope); cudaFree(s->q16); cudaFree(s->q8); cudaFree(s->attn_scratch);
   cudaFree(s->xs); cudaFree(s->prompts); cudaFree(s->gen); cudaFree(s->d_step); cudaFree(s->d_flag);
   cudaFree(s->attn_dbg);
   cudaFree(s->q32);
@@ -316,6 +317,10 @@ extern "C" int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t
   // the text loop gathers a column of V into a 512-entry array (src/app/text.rs:478) and panics beyond it
   RMI_REQUIRE(forward != RMI_FORWARD_APP_TEXT_F32KV || (s->d.capacity + 255) / 256 * 256 <= 512, RMI_ERR_BAD_SHAPE,
               "the text loop's F32 cache holds at most 512 positions, session capacity is %zu", s->d.capacity);
+  // the CLI variants keep a score row per head in shared memory: refuse a capacity that cannot run before anything is captured
+  RMI_REQUIRE(!is_cli_forward(forward) || cli_attention_smem_bytes(s->d, forward) <= ctx->smem_optin, RMI_ERR_UNSUPPORTED,
+              "forward variant %d needs %zu B of shared memory per attention CTA at capacity %zu (limit %zu)", forward,
+              cli_attention_smem_bytes(s->d, forward), s->d.capacity, ctx->smem_optin);
   if (uses_f32_cache(forward) && !s->k32_cache) {
     const size_t kv = s->d.batch * s->d.n_layer * s->d.capacity * s->d.n_head_kv * s->d.hd * 4;
     float *k32 = nullptr, *v32 = nullptr;
@@ -365,11 +370,19 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   s->d.batch = batch;
   s->d.capacity = capacity;
   const decode_dims& d = s->d;
-  if (attention_smem_bytes(d) > ctx->smem_optin) {
-    rmi_set_error("capacity %zu needs %zu B of shared memory per attention CTA (limit %zu)", capacity,
-                  attention_smem_bytes(d), ctx->smem_optin);
-    free_session(s);
-    return RMI_ERR_UNSUPPORTED;
+  // Attention kernel of the session forward: the cluster kernel (score rows and this CTA's K/V chunk in shared
+  // memory) for few sequences, the single-CTA kernel for many; when the capacity's score rows do not fit in shared
+  // memory (beyond a few thousand positions) the single-CTA kernel keeps them in a global scratch area instead, so
+  // any capacity up to the model's context length is accepted (src/models/qwen3.rs:442-447).
+  bool seq_attention = attention_seq_eligible(d), long_attention = false;
+  if (seq_attention ? attention_seq_smem_bytes(d, false) > ctx->smem_optin : attention_smem_bytes(d) > ctx->smem_optin) {
+    if (!attention_seq_shape_ok(d) || attention_seq_smem_bytes(d, true) > ctx->smem_optin) {
+      rmi_set_error("capacity %zu needs %zu B of shared memory per attention CTA (limit %zu) and the head shape has no "
+                    "long-context kernel", capacity, attention_smem_bytes(d), ctx->smem_optin);
+      free_session(s);
+      return RMI_ERR_UNSUPPORTED;
+    }
+    seq_attention = long_attention = true;
   }
   const size_t nq = d.n_head * d.hd, nk = d.n_head_kv * d.hd;
   const size_t max_n_in = nq > d.n_ff ? (nq > d.n_embd ? nq : d.n_embd) : (d.n_ff > d.n_embd ? d.n_ff : d.n_embd);
@@ -393,10 +406,11 @@ extern "C" int32_t rmi_session_create(rmi_ctx* ctx, const rmi_qwen3* model, size
   SESSION_ALLOC(s->argmax_i, argmax_scratch_floats(batch) * 4);
   s->forward = RMI_FORWARD_QWEN3_SESSION;
   s->k32_cache = s->v32_cache = nullptr;
-  s->seq_attention = attention_seq_eligible(s->d);
+  s->seq_attention = seq_attention;
+  if (long_attention) SESSION_ALLOC(s->attn_scratch, attention_seq_scratch_bytes(d));
   SESSION_ALLOC(s->q32, batch * nq * 4);
   s->fused_norm = true;
-  s->fused_qk = batch <= 4;  // measured: a loss at batch 32
+  s->fused_qk = batch <= 4 && !seq_attention;  // measured: a loss at batch 32; the single-CTA kernel has no fused form
   for (const auto& l : model->layers) {
     s->fused_norm = s->fused_norm && q8_gemv_fused_norm_eligible(ctx, l.wqkv, batch) && q8_gemv_fused_norm_eligible(ctx, l.wgu, batch);
   }
@@ -470,7 +484,7 @@ static int32_t enqueue_step(rmi_ctx* ctx, rmi_session* s, size_t n_prompt, size_
       RMI_TRY(launch_qk_norm_rope_kv(ctx, d, s->qkv, w.q_norm, w.k_norm, s->rope, s->d_step, s->q16, s->k_cache,
                                      s->v_cache, l));
       if (s->seq_attention)
-        RMI_TRY(launch_attention_seq(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
+        RMI_TRY(launch_attention_seq(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs, s->attn_scratch));
       else
         RMI_TRY(launch_attention(ctx, d, s->q16, s->k_cache, s->v_cache, s->d_step, l, s->attn_dbg, s->q8, s->xs));
     }

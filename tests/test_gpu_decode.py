@@ -234,6 +234,30 @@ def test_qwen3_head_shape_and_long_context(rmi, ctx, tmp_path_factory):
     model.free()
 
 
+@pytest.mark.parametrize("batch", [1, 3])
+def test_capacity_beyond_the_shared_memory_score_rows(rmi, ctx, tmp_path_factory, batch):
+    """A session may be as long as the model's context (src/models/qwen3.rs:442-447).  At 40960 positions the score
+    rows of the attention kernels no longer fit in shared memory and the single-CTA kernel keeps them in a global
+    scratch area: same tokens and the same hidden-state bits as the oracle, and as a short session of the same model."""
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg = tiny_cfg(n_head=4, n_head_kv=2, head_dim=128, n_embd=256, n_ctx=40960)
+    path, tensors = _model(rmi, tmp_path_factory, cfg, seed=3)
+    model = rmi.Qwen3Model.from_file(path)
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], 40, seed=5 + b) for b in range(batch)])
+    long_s = rmi.Qwen3Session(model, 40960, batch=batch)
+    got = long_s.generate(prompts, 12)
+    hid = long_s.hidden().copy()
+    long_s.free()
+    short_s = rmi.Qwen3Session(model, 64, batch=batch)
+    assert np.array_equal(short_s.generate(prompts, 12), got)
+    assert np.array_equal(bits(short_s.hidden()), bits(hid))
+    short_s.free()
+    ref, trace = orc.Qwen3(cfg, tensors).generate(prompts[0], 12, sem=orc.SEM_AVX2, threads=8, want_trace=True)
+    assert np.array_equal(got[0], ref)
+    assert np.array_equal(bits(hid[0]), bits(trace[-1]))
+    model.free()
+
+
 def test_session_errors(rmi, ctx, tmp_path_factory):
     cfg = tiny_cfg()
     path, _ = _model(rmi, tmp_path_factory, cfg, seed=0)
