@@ -158,6 +158,13 @@ int32_t rmi_matmul_q8_0_prequantized_dev(rmi_ctx* ctx, const rmi_weight* w, cons
  * then the matmul.  m <= 32 runs the memory-bound GEMV kernels (NEON / SCALAR: swapped-operand GEMM
  * from 9 rows), m > 32 the tcgen05 GEMM. */
 int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
+/* ops::matmul_q8_0, the legacy f32-input matmul (src/ops/kernel/q8_0/parallel.rs:317-341): the dequantized
+ * weight times the f32 activation, no activation quantization.  RMI_SEM_AVX2 reproduces matmul_q8_0_avx2_range
+ * (avx2.rs:180-217: two 8-lane accumulators, fma(d * f32(q), x, acc), hsum_ps); the other semantics reproduce
+ * matmul_q8_0_fallback_range (scalar.rs:3-29), which is what the reference runs off x86.  output[t*n_rows + r],
+ * m <= 65535 rows of x per call; _dev takes device pointers and returns before the kernel finishes. */
+int32_t rmi_matmul_q8_0_f32(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
+int32_t rmi_matmul_q8_0_f32_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output);
 int32_t rmi_matmul_q8_0_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m,
                             float* output);
 /* No counterpart in the reference.  Same result as rmi_matmul_q8_0_dev for m <= 32, but the call

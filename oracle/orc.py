@@ -151,6 +151,15 @@ def matmul_q8_0_fallback_range(weight, x, n_in, row_start, row_end):
     return out
 
 
+def matmul_q8_0_f32(weight, x, n_in, n_out, sem=SEM_AVX2):
+    """ops::matmul_q8_0 (f32 input, src/ops/kernel/q8_0/parallel.rs:317-341) for every row of x."""
+    weight, x = _u8(weight), _f32(x).reshape(-1, n_in)
+    out = np.zeros((x.shape[0], n_out), np.float32)
+    for t in range(x.shape[0]):
+        lib().orc_matmul_q8_0_f32(_p(weight), _p(x[t]), _p(out[t]), C.c_size_t(n_in), C.c_size_t(n_out), C.c_int(sem))
+    return out
+
+
 def q8_forward_batched(weight, x, n_in, n_out, sem=SEM_AVX2, threads=1):
     weight, x = _u8(weight), _f32(x).reshape(-1, n_in)
     out = np.zeros((x.shape[0], n_out), np.float32)

@@ -375,6 +375,37 @@ void orc_matmul_q8_0_fallback_range(const uint8_t* weight, const float* input, f
   }
 }
 
+/* src/ops/kernel/q8_0/avx2.rs:180-217: two 8-lane accumulators; per block acc0 takes the products of elements
+ * 0..7 and 16..23, acc1 those of 8..15 and 24..31, each as fma(d * f32(q), x, acc); lanes added, then hsum_ps. */
+void orc_matmul_q8_0_avx2_range(const uint8_t* weight, const float* input, float* output,
+                                size_t n_in, size_t row_start, size_t row_end) {
+  size_t blocks = n_in / 32, stride = blocks * 34;
+  for (size_t row = row_start; row < row_end; row++) {
+    float acc0[8] = {0}, acc1[8] = {0};
+    for (size_t b = 0; b < blocks; b++) {
+      const uint8_t* blk = weight + row * stride + b * 34;
+      const int8_t* q = (const int8_t*)(blk + 2);
+      const float* x = input + b * 32;
+      float d = wd_of(blk);
+      for (int l = 0; l < 8; l++) acc0[l] = fmaf(d * (float)q[l], x[l], acc0[l]);
+      for (int l = 0; l < 8; l++) acc1[l] = fmaf(d * (float)q[8 + l], x[8 + l], acc1[l]);
+      for (int l = 0; l < 8; l++) acc0[l] = fmaf(d * (float)q[16 + l], x[16 + l], acc0[l]);
+      for (int l = 0; l < 8; l++) acc1[l] = fmaf(d * (float)q[24 + l], x[24 + l], acc1[l]);
+    }
+    float s[8];
+    for (int l = 0; l < 8; l++) s[l] = acc0[l] + acc1[l];
+    output[row - row_start] = hsum8(s);
+  }
+}
+
+/* src/ops/kernel/q8_0/parallel.rs:317-341 (ops::matmul_q8_0, f32 input): the AVX2 kernel on x86, the scalar
+ * kernel everywhere else (there is no NEON variant of this function). */
+void orc_matmul_q8_0_f32(const uint8_t* weight, const float* input, float* output, size_t n_in, size_t n_out,
+                         int sem) {
+  if (sem == ORC_SEM_AVX2) orc_matmul_q8_0_avx2_range(weight, input, output, n_in, 0, n_out);
+  else orc_matmul_q8_0_fallback_range(weight, input, output, n_in, 0, n_out);
+}
+
 /* ------------------------------------------------------------------ thread pool */
 /* Fork-join over nth workers with the reference's (ith, nth) convention
  * (src/core/thread_pool.rs:119-161: every worker runs f(ith, nth), caller is ith 0). */

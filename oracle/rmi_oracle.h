@@ -10,9 +10,11 @@
  * the reference's own tests hold for this path (tests/test_oracle_golden.py lists each
  * vector with the reference test it comes from).  The reference itself (Rust, crates
  * not vendored) cannot be compiled where this was written, so no reference binary is
- * used.  Two spots stay unpinned at bit level because the reference has no x86
- * fixture for them: exp() inside softmax/SiLU (platform libm) and the plain-loop
- * dot_f16 used by attention.
+ * used.  Three spots stay unpinned at bit level because the reference has no x86
+ * fixture for them: exp() inside softmax/SiLU (platform libm), the plain-loop
+ * dot_f16 used by attention, and the legacy f32-input matmul_q8_0 (no test of the
+ * reference calls it; its two restatements are pinned on data where both orders
+ * must give the exact integer result).
  *
  * Each function cites the reference file:line (paths relative to the reference
  * project root) it restates.
@@ -87,6 +89,12 @@ void orc_q8_0_block_sums(const uint8_t* weight, const uint8_t* input_q8, int32_t
 /* src/ops/kernel/q8_0/scalar.rs:3-29 (f32 input, no activation quantization) */
 void orc_matmul_q8_0_fallback_range(const uint8_t* weight, const float* input, float* output,
                                     size_t n_in, size_t row_start, size_t row_end);
+/* src/ops/kernel/q8_0/avx2.rs:180-217 (f32 input, two 8-lane accumulators) */
+void orc_matmul_q8_0_avx2_range(const uint8_t* weight, const float* input, float* output,
+                                size_t n_in, size_t row_start, size_t row_end);
+/* src/ops/kernel/q8_0/parallel.rs:317-341: ops::matmul_q8_0 = AVX2 kernel on x86 (ORC_SEM_AVX2), scalar elsewhere */
+void orc_matmul_q8_0_f32(const uint8_t* weight, const float* input, float* output, size_t n_in, size_t n_out,
+                         int sem);
 /* src/ops/kernel/trait_.rs:57-109: Kernel::forward / forward_batched for Q8Kernel:
  * per token: quantize the row, then the GEMV. n_tokens rows. */
 void orc_q8_forward_batched(const uint8_t* weight, const float* input, float* output,

@@ -491,6 +491,19 @@ def matmul_q8_0(weight: QuantizedTensor, x) -> np.ndarray:
     return out
 
 
+def matmul_q8_0_f32(weight: QuantizedTensor, x) -> np.ndarray:
+    """ops::matmul_q8_0 (src/ops/kernel/q8_0/parallel.rs:317-341): dequantized weight x f32 activations [m, n_in],
+    no activation quantization; AVX2 or scalar accumulation order by the context's semantics."""
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, weight.n_in)
+    out = np.zeros((x.shape[0], weight.n_out), np.float32)
+    _check(lib().rmi_matmul_q8_0_f32(weight._ctx.handle, weight._h, _p(x), _sz(x.shape[0]), _p(out)))
+    return out
+
+
+def matmul_q8_0_f32_dev(weight: QuantizedTensor, x_ptr: int, m: int, out_ptr: int):
+    _check(lib().rmi_matmul_q8_0_f32_dev(weight._ctx.handle, weight._h, C.c_void_p(x_ptr), _sz(m), C.c_void_p(out_ptr)))
+
+
 def q8_0_block_sums(weight: QuantizedTensor, q8, m: int, use_tensor_cores: bool = False) -> np.ndarray:
     q8 = np.ascontiguousarray(q8, np.uint8)
     out = np.zeros((m, weight.n_out, weight.n_in // 32), np.int32)

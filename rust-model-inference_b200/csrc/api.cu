@@ -727,6 +727,33 @@ extern "C" int32_t rmi_matmul_q8_0(rmi_ctx* ctx, const rmi_weight* w, const floa
   return RMI_OK;
 }
 
+extern "C" int32_t rmi_matmul_q8_0_f32_dev(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q8_0));
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  RMI_REQUIRE(x && output, RMI_ERR_BAD_HANDLE, "rmi_matmul_q8_0_f32_dev: null buffer");
+  RMI_REQUIRE(m <= 65535, RMI_ERR_BAD_SHAPE, "rmi_matmul_q8_0_f32_dev: at most 65535 rows per call, got %zu", m);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return launch_q8_matmul_f32(ctx, w, x, m, output);
+}
+
+extern "C" int32_t rmi_matmul_q8_0_f32(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* output) {
+  RMI_TRY(rmi_check_ctx(ctx));
+  RMI_TRY(rmi_check_weight(w, RMI_GGML_Q8_0));
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  RMI_REQUIRE(x && output, RMI_ERR_BAD_HANDLE, "rmi_matmul_q8_0_f32: null buffer");
+  RMI_REQUIRE(m <= 65535, RMI_ERR_BAD_SHAPE, "rmi_matmul_q8_0_f32: at most 65535 rows per call, got %zu", m);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  float *dx, *dout;
+  RMI_TRY(rmi_scratch(ctx, 5, m * w->n_in * 4, (void**)&dx));
+  RMI_TRY(rmi_scratch(ctx, 6, m * w->n_rows * 4, (void**)&dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(dx, x, m * w->n_in * 4, cudaMemcpyHostToDevice, ctx->stream));
+  RMI_TRY(launch_q8_matmul_f32(ctx, w, dx, m, dout));
+  RMI_CUDA_CHECK(cudaMemcpyAsync(output, dout, m * w->n_rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  RMI_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+  return RMI_OK;
+}
+
 extern "C" int32_t rmi_q8_0_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* q8, size_t m,
                                        int32_t* sums, int32_t use_tc) {
   RMI_TRY(rmi_check_ctx(ctx));

@@ -11,6 +11,7 @@ int32_t launch_q8_gemv(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, con
                        float* out, size_t out_stride, size_t row_begin, size_t row_end);
 bool q8_gemv_fused_norm_eligible(const rmi_ctx* ctx, const rmi_weight* w, size_t m);
 // x = x_in (+ add); rms_norm(x, norm_w, eps); quantize; out = W x.  x is also written to x_out (!= x_in).
+int32_t launch_q8_matmul_f32(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* out);
 int32_t launch_q8_gemv_fused_norm(rmi_ctx* ctx, const rmi_weight* w, const float* x_in, const float* add,
                                   const float* norm_w, float eps, float* x_out, size_t m, float* out, size_t out_stride);
 int32_t launch_q8_block_sums(rmi_ctx* ctx, const rmi_weight* w, const uint8_t* xq, size_t m, int32_t* sums);

@@ -831,6 +831,52 @@ __global__ void silu_mul_quantize_kernel(const float* __restrict__ gate, const f
   }
 }
 
+// ---------------------------------------------------------------- f32-input matmul (ops::matmul_q8_0)
+
+// Dequantized weight x f32 activation without activation quantization (src/ops/kernel/q8_0/parallel.rs:317-341).
+// AVX2 (avx2.rs:180-217): two 8-lane accumulators per row; per block acc0 takes elements 0..7 and 16..23, acc1
+// 8..15 and 24..31, each term fma(d * f32(q), x, acc); acc0 + acc1 lane by lane, then hsum_ps.  Thread (row r of
+// the 16-row tile, chain c of 16) owns elements c and 16 + c of every block, which is lane c % 8 of acc c / 8.
+// Every other instruction set runs scalar.rs:3-29: per block local += f32(q) * x over the 32 elements in order
+// (separate multiply and add), sum += d * local; one thread per row.
+template <int SEM>
+__global__ void __launch_bounds__(256)
+    q8_matmul_f32_kernel(const uint8_t* __restrict__ w, size_t blocks, size_t n_rows, const float* __restrict__ x,
+                         float* __restrict__ out) {
+  const int rit = threadIdx.x >> 4, c = threadIdx.x & 15;
+  const size_t tile = blockIdx.x, row = tile * 16 + rit, K = blocks * 32;
+  const float* xr = x + (size_t)blockIdx.y * K;
+  const uint8_t* rec = w + tile * blocks * Q8_REC_BYTES;
+  if (SEM == RMI_SEM_AVX2) {
+    float acc = 0.0f;
+    for (size_t b = 0; b < blocks; b++) {
+      const uint8_t* r = rec + b * Q8_REC_BYTES;
+      const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(r + 2 * rit));
+      const int8_t* q = reinterpret_cast<const int8_t*>(r + 32 + rit * 32);
+      acc = __fmaf_rn(__fmul_rn(d, (float)q[c]), __ldg(xr + b * 32 + c), acc);
+      acc = __fmaf_rn(__fmul_rn(d, (float)q[16 + c]), __ldg(xr + b * 32 + 16 + c), acc);
+    }
+    // acc0[L] + acc1[L], then dot.rs:447-456: s_i = a[i+4] + a[i]; (s0 + s1) + (s2 + s3)
+    const float a = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+    const float s = __fadd_rn(__shfl_xor_sync(0xffffffffu, a, 4), a);
+    const float t = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+    const float res = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
+    if (c == 0 && row < n_rows) out[(size_t)blockIdx.y * n_rows + row] = res;
+  } else {
+    if (c != 0 || row >= n_rows) return;
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; b++) {
+      const uint8_t* r = rec + b * Q8_REC_BYTES;
+      const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(r + 2 * rit));
+      const int8_t* q = reinterpret_cast<const int8_t*>(r + 32 + rit * 32);
+      float local = 0.0f;
+      for (int k = 0; k < 32; k++) local = __fadd_rn(local, __fmul_rn((float)q[k], __ldg(xr + b * 32 + k)));
+      sum = __fadd_rn(sum, __fmul_rn(d, local));
+    }
+    out[(size_t)blockIdx.y * n_rows + row] = sum;
+  }
+}
+
 // ---------------------------------------------------------------- host launchers
 
 int32_t launch_q8_repack_tile16(rmi_ctx* ctx, const uint8_t* raw, uint8_t* dst, size_t n_rows,
@@ -1104,4 +1150,14 @@ int32_t launch_silu_mul_quantize(rmi_ctx* ctx, const float* gate, const float* u
     return RMI_ERR_CUDA;
   }
   return rmi_post_launch(ctx, "silu_mul_quantize");
+}
+
+int32_t launch_q8_matmul_f32(rmi_ctx* ctx, const rmi_weight* w, const float* x, size_t m, float* out) {
+  if (m == 0 || w->n_rows == 0) return RMI_OK;
+  const dim3 grid((unsigned)w->n_tiles16, (unsigned)m);
+  if (ctx->sem == RMI_SEM_AVX2)
+    q8_matmul_f32_kernel<RMI_SEM_AVX2><<<grid, 256, 0, ctx->stream>>>(w->d_tile16, w->n_in / 32, w->n_rows, x, out);
+  else
+    q8_matmul_f32_kernel<RMI_SEM_SCALAR><<<grid, 256, 0, ctx->stream>>>(w->d_tile16, w->n_in / 32, w->n_rows, x, out);
+  return rmi_post_launch(ctx, "q8_matmul_f32");
 }

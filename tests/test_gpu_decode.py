@@ -320,6 +320,27 @@ def test_config4_full_size_greedy_tokens_identical_over_128_steps(rmi, ctx):
     model.free()
 
 
+def test_config4_full_size_batch_32_token_identity_on_sampled_sequences(rmi, ctx):
+    # BASELINE config 4 at batch 32 (the single-CTA attention kernel, eight activation rows per GEMV pass, batched
+    # prompt processing): three of the 32 sequences against the oracle, tokens and final hidden-state bits
+    ctx.set_semantics(rmi.SEM_AVX2)
+    cfg, path, tensors = _full_model(rmi)
+    model = rmi.Qwen3Model.from_file(path)
+    B, P, G = 32, 40, 8
+    prompts = np.stack([rmi.synth.prompt_tokens(cfg["vocab"], P, seed=2000 + b) for b in range(B)])
+    s = rmi.Qwen3Session(model, P + G, batch=B)
+    got = s.generate(prompts, G)
+    hid = s.hidden()
+    oracle = orc.Qwen3(cfg, tensors)
+    threads = min(os.cpu_count() or 1, 16)
+    for b in (0, 13, 31):
+        ref, trace = oracle.generate(prompts[b], G, sem=orc.SEM_AVX2, threads=threads, want_trace=True)
+        assert np.array_equal(got[b], ref), b
+        assert np.array_equal(bits(hid[b]), bits(trace[-1])), b
+    s.free()
+    model.free()
+
+
 @pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON, orc.SEM_SCALAR])
 @pytest.mark.parametrize("batch,n_prompt", [(1, 70), (3, 33), (40, 300)])
 def test_batched_prefill_equals_the_token_loop(rmi, ctx, tmp_path_factory, sem, batch, n_prompt):

@@ -287,3 +287,30 @@ def test_streaming_gemv_many_long_rows_bit_exact(rmi, ctx, sem, n, k, m):
     part = rmi.matmul_q8_0_prequantized_rows(w, q8, sc, m, row_begin=17, row_end=n - 33)
     assert np.array_equal(bits(part[:, 17:n - 33]), bits(ref[:, 17:n - 33]))
     w.free()
+
+
+# ------------------------------------------------------------------ f32-input matmul (ops::matmul_q8_0)
+
+@pytest.mark.parametrize("sem", SEMS)
+@pytest.mark.parametrize("n,k,m", [(40, 96, 1), (1024, 1024, 3), (300, 2048, 2)])
+def test_f32_input_matmul_q8_0_bit_exact(rmi, ctx, sem, n, k, m):
+    """rmi_matmul_q8_0_f32 = ops::matmul_q8_0 (src/ops/kernel/q8_0/parallel.rs:317-341): the AVX2 order under AVX2
+    semantics, the scalar order otherwise; ragged last tile, several activation rows, host and device entry points."""
+    torch = pytest.importorskip("torch")
+    ctx.set_semantics(sem)
+    wb = make_q8_0_weight(n, k, 2)
+    w = rmi.QuantizedTensor.from_bytes(wb, rmi.GGML_Q8_0, k, n)
+    x = np.random.default_rng(n + m).standard_normal((m, k)).astype(np.float32)
+    ref = orc.matmul_q8_0_f32(wb, x, k, n, sem)
+    got = rmi.matmul_q8_0_f32(w, x)
+    assert np.array_equal(bits(got), bits(ref))
+    xd = torch.from_numpy(x).cuda()
+    od = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    rmi.matmul_q8_0_f32_dev(w, xd.data_ptr(), m, od.data_ptr())
+    ctx.sync()
+    assert np.array_equal(bits(od.cpu().numpy()), bits(ref))
+    # the quantize-then-GEMV path of the same weight agrees within the quantization error of the activation
+    q = rmi.matmul_q8_0(w, x)
+    assert rel_err(q, ref) < 2e-2
+    w.free()

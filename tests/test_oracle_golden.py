@@ -652,3 +652,36 @@ def test_cli_f32_cache_oracle_runs_and_tracks_the_f16_cache_variant():
         tl, trl = oracle.generate(prompt, 6, want_trace=True, logits_tool=True, kv_f32=kv_f32)
         assert tl.shape == (6,) and np.isfinite(trl).all()
         assert np.abs(trl - (tr32 if kv_f32 else tr16)).max() <= 1e-2 * max(1.0, np.abs(tr16).max())
+
+
+def test_f32_input_matmul_q8_0_exact_on_integer_data_in_both_orders():
+    """ops::matmul_q8_0 (src/ops/kernel/q8_0/parallel.rs:317-341) has no vector in the reference's own tests, so its
+    restatements (AVX2: avx2.rs:180-217, scalar: scalar.rs:3-29) are pinned on data where every product and every
+    partial sum is an exactly representable integer multiple of the scale: both accumulation orders must then give the
+    exact value, which is computed in int64."""
+    rng = np.random.default_rng(5)
+    n_out, n_in = 19, 160
+    blocks = n_in // 32
+    q = rng.integers(-127, 128, size=(n_out, blocks, 32), dtype=np.int64)
+    e = rng.integers(-3, 4, size=(n_out, blocks))                # scales 2^-3 .. 2^3
+    x = rng.integers(-8, 9, size=n_in).astype(np.float32)
+    weight = bytearray()
+    for r in range(n_out):
+        for b in range(blocks):
+            weight += np.float16(2.0 ** float(e[r, b])).tobytes() + q[r, b].astype(np.int8).tobytes()
+    weight = np.frombuffer(bytes(weight), np.uint8)
+    exact = np.array([sum(float(2.0 ** float(e[r, b])) * float((q[r, b] * x[b * 32:(b + 1) * 32].astype(np.int64)).sum())
+                          for b in range(blocks)) for r in range(n_out)], np.float64)
+    for sem in (orc.SEM_AVX2, orc.SEM_SCALAR, orc.SEM_NEON):
+        got = orc.matmul_q8_0_f32(weight, x, n_in, n_out, sem)[0]
+        assert np.array_equal(got.astype(np.float64), exact), sem
+
+
+def test_f32_input_matmul_q8_0_orders_agree_within_tolerance_and_differ_in_bits():
+    weight = make_q8_0_weight(64, 1024, 3)
+    x = np.random.default_rng(4).standard_normal(1024).astype(np.float32)
+    a = orc.matmul_q8_0_f32(weight, x, 1024, 64, orc.SEM_AVX2)[0]
+    s = orc.matmul_q8_0_f32(weight, x, 1024, 64, orc.SEM_SCALAR)[0]
+    assert np.max(np.abs(a - s)) / np.max(np.abs(s)) < 1e-5
+    assert not np.array_equal(bits(a), bits(s))      # sixteen fused chains vs one chain with separate mul and add
+    assert np.array_equal(bits(s), bits(orc.matmul_q8_0_fallback_range(weight, x, 1024, 0, 64)))
