@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256, RMI_GEMV_SHORT_MINB)
   constexpr int NL = LB / 4;        // AVX2 lanes (dp4a groups) per thread
   constexpr int WPT = 16 / LB;      // warps per 16-row tile
   constexpr int U = LB == 16 ? 4 : 8;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   const size_t K = blocks * 32;
   int8_t* xq_s = reinterpret_cast<int8_t*>(smem);
   float* xs_s = reinterpret_cast<float*>(smem + MP * K);
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(256)
   constexpr int NL = LB / 4;        // AVX2 lanes (dp4a groups) per thread
   constexpr int WPT = 16 / LB;      // warps per 16-row tile
   constexpr int U = gemv_batch<LB>::U;
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   const size_t K = blocks * 32;
   int8_t* xq_s = reinterpret_cast<int8_t*>(smem);
   float* xs_s = reinterpret_cast<float*>(smem + MP * K);

@@ -342,10 +342,11 @@ extern "C" int32_t rmi_session_set_forward(rmi_ctx* ctx, rmi_session* s, int32_t
 
 #define SESSION_ALLOC(ptr, bytes)                                                             \
   do {                                                                                        \
-    cudaError_t _e = cudaMalloc((void**)&(ptr), (bytes) ? (bytes) : 16);                      \
+    const size_t _n = (size_t)(bytes);                                                        \
+    cudaError_t _e = cudaMalloc((void**)&(ptr), _n != 0 ? _n : 16);                           \
     if (_e != cudaSuccess) {                                                                  \
       (void)cudaGetLastError();                                                               \
-      rmi_set_error("session allocation of %zu bytes failed: %s", (size_t)(bytes), cudaGetErrorString(_e)); \
+      rmi_set_error("session allocation of %zu bytes failed: %s", _n, cudaGetErrorString(_e)); \
       free_session(s);                                                                        \
       return RMI_ERR_OOM;                                                                     \
     }                                                                                         \
