@@ -964,10 +964,13 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
   // Enough warps to keep every SM streaming: a pass over MP activation rows does MP times the
   // arithmetic per weight byte, so fewer (fatter) warps are needed as MP grows.
   {
-    // small problem: one CTA per tile with the tile staged by a single bulk copy
+    // small problem (up to six CTAs per SM): one CTA per tile and group of MP rows with the tile staged by a single
+    // bulk copy, so a row's weights cost one memory round trip instead of one per register batch.  Measured on the
+    // 0.6B decode step: batch 4 / 8 / 16 / 32 go from 2.08 / 3.37 / 5.73 / 9.42 to 3.03 / 3.92 / 6.19 / 9.93 k tok/s
+    // with the passes of 4 and 8 rows included; twelve CTAs per SM is slower again (9.28 k at batch 32).
     const size_t t1 = (row_end + 15) / 16 - row_begin / 16, blocks = w->n_in / 32;
     const size_t smem = 128 + blocks * Q8_REC_BYTES + (size_t)MP * (w->n_in + blocks * 4);
-    if (MP <= 2 && t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024) {
+    if (t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024) {
       auto kern = q8_gemv_staged_kernel<SEM, MP, false>;
       if (smem > 48 * 1024 &&
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
