@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(256)
                          const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
                          size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
                          float* __restrict__ attn_out, uint8_t* __restrict__ q8, float* __restrict__ scales,
-                         float* __restrict__ g_sc, uint16_t* __restrict__ g_p16) {
+                         float* __restrict__ g_sc, double* __restrict__ g_pd) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -376,11 +376,13 @@ __global__ void __launch_bounds__(256)
   const int T = *d_step + 1;
   const size_t cs = (capacity + 7) & ~(size_t)7;  // keeps every array 16-byte aligned
   const size_t slice = (b * n_head_kv + kvh) * group * cs;         // GS: this CTA's rows in the scratch area
-  float* sc = GS ? g_sc + slice : reinterpret_cast<float*>(smem);   // [group][cs]
-  float* red = GS ? reinterpret_cast<float*>(smem) : sc + group * cs;  // [group] (padded to 4)
-  uint16_t* qs = reinterpret_cast<uint16_t*>(red + ((group + 3) & ~(size_t)3));  // [group][hd]
-  uint16_t* p16 = GS ? g_p16 + slice : qs + group * hd;             // [group][cs]
-  uint8_t* tiles = reinterpret_cast<uint8_t*>(GS ? qs + group * hd : p16 + group * cs);  // 2 x SEQ_TILE rows (16-byte aligned)
+  // f64 copies of the query rows and of the f16 probabilities: a product of two f16 values is exact in f32 and in
+  // f64, so s + f64(f32(q) * f32(k)) (dot.rs:115-118) equals fma(f64(q), f64(k), s) bit for bit
+  double* qd = reinterpret_cast<double*>(smem);                     // [group][hd]
+  double* pd = GS ? g_pd + slice : qd + group * hd;                 // [group][cs]
+  float* sc = GS ? g_sc + slice : reinterpret_cast<float*>(pd + group * cs);   // [group][cs]
+  float* red = GS ? reinterpret_cast<float*>(qd + group * hd) : sc + group * cs;  // [group] (padded to 4)
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(red + ((group + 3) & ~(size_t)3));  // 2 x SEQ_TILE rows (16-byte aligned)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
   // K rows are padded by 16 bytes: the threads of a warp read the same words of different rows, and rows of exactly
   // hd * 2 = 256 bytes would all start in the same bank
@@ -396,7 +398,8 @@ __global__ void __launch_bounds__(256)
       cp_async16(dst + (i / row16) * stride + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
     cp_async_commit();
   };
-  for (size_t i = tid; i < group * hd; i += blockDim.x) qs[i] = q16[b * nq + kvh * group * hd + i];
+  for (size_t i = tid; i < group * hd; i += blockDim.x)
+    qd[i] = (double)f16_bits_to_f32(q16[b * nq + kvh * group * hd + i]);
   stage(kbase, 0, 0, k_stride);
   // scores[g][t] = f32(sum_f64 q*k) * kq_scale (dot.rs:115-118)
   for (int tile = 0; tile < n_tiles; tile++) {
@@ -408,15 +411,16 @@ __global__ void __launch_bounds__(256)
     for (size_t item = tid; item < (size_t)nt * group; item += blockDim.x) {
       const size_t tl = item / group, g = item % group;
       const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride);
-      const uint4* qr = reinterpret_cast<const uint4*>(qs + g * hd);
+      const double2* qr = reinterpret_cast<const double2*>(qd + g * hd);
       double s = 0.0;
       for (size_t i = 0; i < hd / 8; i++) {
-        const uint4 kv = kr[i], qv = qr[i];
-        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w}, qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        const uint4 kv = kr[i];
+        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-          s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qw[e] & 0xffff)), f16_bits_to_f32((uint16_t)(kw[e] & 0xffff)));
-          s += (double)__fmul_rn(f16_bits_to_f32((uint16_t)(qw[e] >> 16)), f16_bits_to_f32((uint16_t)(kw[e] >> 16)));
+          const double2 q2 = qr[i * 4 + e];
+          s = fma(q2.x, (double)f16_bits_to_f32((uint16_t)(kw[e] & 0xffff)), s);
+          s = fma(q2.y, (double)f16_bits_to_f32((uint16_t)(kw[e] >> 16)), s);
         }
       }
       sc[g * cs + t0 + tl] = __fmul_rn((float)s, kq_scale);
@@ -451,7 +455,7 @@ __global__ void __launch_bounds__(256)
     const size_t g = i / T, t = i % T;
     float pv = sc[g * cs + t];
     if (red[g] > 0.0f) pv = __fdiv_rn(pv, red[g]);
-    p16[g * cs + t] = f32_to_f16_bits(pv);
+    pd[g * cs + t] = (double)f16_round_trip(pv);
   }
   // out[g][d] = f32(sum_f64 over t of v[t][d] * p[g][t]), one output element per thread and pass
   double accv[2] = {0.0, 0.0};
@@ -464,10 +468,9 @@ __global__ void __launch_bounds__(256)
     int pass = 0;
     for (size_t o = tid; o < group * hd && pass < 2; o += blockDim.x, pass++) {
       const size_t g = o / hd, dd = o % hd;
-      const uint16_t* pr = p16 + g * cs + t0;
+      const double* pr = pd + g * cs + t0;
       double s = accv[pass];
-      for (int tl = 0; tl < nt; tl++)
-        s += (double)__fmul_rn(f16_bits_to_f32(vt[(size_t)tl * hd + dd]), f16_bits_to_f32(pr[tl]));
+      for (int tl = 0; tl < nt; tl++) s = fma((double)f16_bits_to_f32(vt[(size_t)tl * hd + dd]), pr[tl], s);
       accv[pass] = s;
     }
     __syncthreads();
@@ -1022,14 +1025,14 @@ bool attention_seq_eligible(const decode_dims& d) { return attention_seq_shape_o
 // Shared memory of attention_seq_kernel; global_scores: without the [group][capacity] score and probability rows.
 size_t attention_seq_smem_bytes(const decode_dims& d, bool global_scores) {
   const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
-  return (global_scores ? 0 : group * cs * 4 + group * cs * 2) + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 2 +
+  return (global_scores ? 0 : group * cs * 4 + group * cs * 8) + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 8 +
          2 * (size_t)SEQ_TILE * (d.hd * 2 + 16);
 }
 
-// Bytes of global scratch for the score rows (f32) and the probability rows (f16) of all CTAs.
+// Bytes of global scratch for the score rows (f32) and the probability rows (f64 copies of the f16 values) of all CTAs.
 size_t attention_seq_scratch_bytes(const decode_dims& d) {
   const size_t cs = (d.capacity + 7) & ~(size_t)7;
-  return d.batch * d.n_head * cs * 6;
+  return d.batch * d.n_head * cs * 12;
 }
 
 int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
@@ -1038,8 +1041,8 @@ int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t*
   const size_t cs = (d.capacity + 7) & ~(size_t)7;
   const bool gs = score_scratch != nullptr;
   const size_t smem = attention_seq_smem_bytes(d, gs);
-  float* g_sc = reinterpret_cast<float*>(score_scratch);
-  uint16_t* g_p16 = gs ? reinterpret_cast<uint16_t*>(g_sc + d.batch * d.n_head * cs) : nullptr;
+  double* g_pd = reinterpret_cast<double*>(score_scratch);   // doubles first: 8-byte alignment
+  float* g_sc = gs ? reinterpret_cast<float*>(g_pd + d.batch * d.n_head * cs) : nullptr;
   auto kern = gs ? (ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2, true>
                                              : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON, true>
                                                                          : attention_seq_kernel<RMI_SEM_SCALAR, true>))
@@ -1052,7 +1055,7 @@ int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t*
     return RMI_ERR_UNSUPPORTED;
   }
   if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head_kv, (unsigned)d.batch), dim3(256), smem, q16, k_cache, v_cache, d_step,
-                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales, g_sc, g_p16) != cudaSuccess) {
+                 d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales, g_sc, g_pd) != cudaSuccess) {
     rmi_set_error("launch of attention_seq failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
   }
