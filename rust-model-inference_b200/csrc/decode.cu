@@ -178,7 +178,12 @@ __global__ void __launch_bounds__(256)
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned CL = cluster.num_blocks(), rank = cluster.block_rank();
   extern __shared__ __align__(16) uint8_t smem[];
-  pdl_wait();
+  // Dependent launch.  Without the fused q/k part everything below reads what the preceding kernel wrote (the
+  // query heads and the newest cache rows).  With it (FQ) the step counter and the cache rows of earlier positions
+  // were written at least two kernels ago (the counter at the end of the previous step, the rows in earlier steps;
+  // the predecessor of this kernel has passed its own wait, so all of that is complete and visible): the K/V staging
+  // below is issued first and the wait comes just before the q|k|v projection is read.
+  if (!FQ) pdl_wait();
   pdl_launch_dependents();
   // Distributed shared memory of another CTA may only be touched once that CTA is known to run: every CTA
   // arrives here and waits just before its first remote store (the staging below overlaps the barrier).
@@ -220,6 +225,7 @@ __global__ void __launch_bounds__(256)
     cp_async16(vbuf + i * 16, vbase + (i / row16) * nk + (i % row16) * 8);
   cp_async_commit();
   if (fused) {
+    pdl_wait();
     const float* proj = fq.qkv + b * (nq + 2 * nk);
     const float* tab = fq.rope + (size_t)(T - 1) * hd;
     for (size_t unit = warp; unit < group + 2; unit += nwarp) {

@@ -480,6 +480,17 @@ __global__ void __launch_bounds__(128)
                    : "memory");
     }
   }
+  // the norm weight is a model weight like the tile: the first batch of it (the only one up to 1024 columns) is
+  // requested before the wait as well, instead of after the two barriers of the norm below
+  constexpr int NB = 8;
+  float nw_pre[FUSED ? NB : 1];
+  if (FUSED) {
+#pragma unroll
+    for (int u = 0; u < NB; u++) {
+      const size_t blk = (threadIdx.x >> 5) + 4 * u;
+      nw_pre[FUSED ? u : 0] = blk < blocks ? __ldg(na.norm_w + blk * 32 + (threadIdx.x & 31)) : 0.0f;
+    }
+  }
   pdl_wait();  // the weight copy above is in flight; everything below depends on the previous kernel
   pdl_launch_dependents();
   if (!FUSED) {  // activations, in parallel with the weight copy
@@ -494,7 +505,6 @@ __global__ void __launch_bounds__(128)
     const size_t seq0 = (size_t)blockIdx.y * MP;
     // Warp w owns the 32-blocks w, w+4, ...; they are handled NB at a time with every global load of a batch
     // (input, residual, norm weight) issued before the first use: loads inside a rolled loop would be serialised.
-    constexpr int NB = 8;
 #pragma unroll
     for (int m = 0; m < MP; m++) {
       const float* xi = na.x_in + (seq0 + m) * K;
@@ -533,7 +543,9 @@ __global__ void __launch_bounds__(128)
     for (size_t b0 = warp; b0 < blocks; b0 += 4 * NB) {
       float nw[NB];
 #pragma unroll
-      for (int u = 0; u < NB; u++) nw[u] = b0 + 4 * u < blocks ? __ldg(na.norm_w + (b0 + 4 * u) * 32 + lane) : 0.0f;
+      for (int u = 0; u < NB; u++)
+        nw[u] = b0 == (size_t)warp ? nw_pre[FUSED ? u : 0]
+                                   : (b0 + 4 * u < blocks ? __ldg(na.norm_w + (b0 + 4 * u) * 32 + lane) : 0.0f);
 #pragma unroll
       for (int m = 0; m < MP; m++) {
         const float sc = s_scale[m];
