@@ -418,14 +418,15 @@ def sharded_sweep(args, pkg, ctx, torch, dist, rank, world, stream, hbm_peak, bf
             r["ms_local_shard"] = timed(lambda: lin.forward_dev(x, out_local), iters)
             r["ms_nccl_allgather"] = timed(lambda: lin.forward_dev(x, out_local, gathered, out_full), iters)
             same = {"nccl_allgather": bool(torch.equal(out_full.view(torch.int32), ref_full.view(torch.int32)))}
-            for name, mode in (("fused_peer_stores", pkg.EXCHANGE_FUSED_STORES), ("peer_copy_overlapped", pkg.EXCHANGE_PEER_COPY)):
+            for name, mode in (("fused_peer_stores", pkg.EXCHANGE_FUSED_STORES), ("peer_copy_overlapped", pkg.EXCHANGE_PEER_COPY),
+                               ("peer_push_overlapped", pkg.EXCHANGE_PEER_PUSH)):
                 r["ms_" + name] = timed(lambda: peer.forward_dev(x.data_ptr(), m, mode), iters)
                 got = np.empty((m, n), np.float32)
                 ctx.d2h(got, peer.out_ptr)
                 same[name] = bool(np.array_equal(got.view(np.uint32), ref_full.cpu().numpy().view(np.uint32)))
                 if world > 1:
                     dist.barrier()
-            best = min(("nccl_allgather", "fused_peer_stores", "peer_copy_overlapped"), key=lambda nm: r["ms_" + nm])
+            best = min(("nccl_allgather", "fused_peer_stores", "peer_copy_overlapped", "peer_push_overlapped"), key=lambda nm: r["ms_" + nm])
             r["best_exchange"] = best
             r["ms_best"] = r["ms_" + best]
             r["speedup_vs_1gpu"] = r["ms_1gpu"] / r["ms_best"]

@@ -410,6 +410,8 @@ int32_t rmi_set_wait_limit_ms(rmi_ctx* ctx, uint32_t ms);
  *                            columns into every rank's buffer over NVLink (best for small m);
  *                            RMI_EXCHANGE_PEER_COPY: m is cut into slabs of rows and the copy engines
  *                            push slab i to the peers while slab i+1 is computed (best for large m).
+ *                            RMI_EXCHANGE_PEER_PUSH: the same slabs, pushed by a small kernel with plain
+ *                            peer stores (a third of the SMs, all peers at once) instead of the copy engines.
  *                            All ranks must make the same sequence of calls.  Reads of round k's
  *                            result must be enqueued on the context's stream before round k+1 is
  *                            called; the buffer is then safe until round k+2 is called.  A rank that
@@ -417,7 +419,7 @@ int32_t rmi_set_wait_limit_ms(rmi_ctx* ctx, uint32_t ms);
  *                            rmi_check_status reports RMI_ERR_TIMEOUT.
  *   rmi_shard_group_free     after a host-side barrier (no peer may still be writing). */
 typedef struct rmi_shard_group rmi_shard_group;
-enum { RMI_EXCHANGE_FUSED_STORES = 0, RMI_EXCHANGE_PEER_COPY = 1 };
+enum { RMI_EXCHANGE_FUSED_STORES = 0, RMI_EXCHANGE_PEER_COPY = 1, RMI_EXCHANGE_PEER_PUSH = 2 };
 int32_t rmi_shard_group_create(rmi_ctx* ctx, int32_t world, int32_t rank, size_t n_out, size_t m_max,
                                rmi_shard_group** out);
 int32_t rmi_shard_group_export(rmi_ctx* ctx, const rmi_shard_group* g, uint8_t* handles192);

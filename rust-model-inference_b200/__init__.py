@@ -601,7 +601,7 @@ def peer_signal_wait_dev(ctx: Context, flag_ptrs, rank: int, epoch: int):
                                           C.c_uint32(epoch & 0xffffffff)))
 
 
-EXCHANGE_FUSED_STORES, EXCHANGE_PEER_COPY = 0, 1
+EXCHANGE_FUSED_STORES, EXCHANGE_PEER_COPY, EXCHANGE_PEER_PUSH = 0, 1, 2
 
 
 class ShardGroup:

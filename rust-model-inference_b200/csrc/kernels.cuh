@@ -49,6 +49,8 @@ int32_t ffn_device(rmi_ctx* ctx, const rmi_weight* wgu, const rmi_weight* wd, co
 
 // peer.cu: writes `epoch` into slot `rank` of every flag array, then waits (at most ctx->wait_limit_ns) until
 // all `world` slots of flags[rank] reached it; on `stream`
+int32_t launch_peer_push(rmi_ctx* ctx, cudaStream_t stream, const float* src, float* const* dsts, int n_peers, size_t n_rows,
+                         size_t n_cols, size_t stride);
 int32_t launch_peer_signal_wait(rmi_ctx* ctx, cudaStream_t stream, uint32_t* const* flags, int world, int rank,
                                 uint32_t epoch);
 

@@ -16,6 +16,25 @@ struct peer_flags {
   uint32_t* p[RMI_MAX_FANOUT];
 };
 
+struct peer_dsts {
+  float* p[RMI_MAX_FANOUT];
+};
+
+// Pushes rows [0, n_rows) x columns [0, n_cols) of `src` (row stride `stride` floats; the caller has offset the
+// pointers to the slab and to this rank's columns) into the same place of every peer's buffer with plain 16-byte
+// stores over NVLink.  A few dozen CTAs next to the matmul of the next slab: the copy is bound by the links, not by
+// the SMs.  blockIdx.y selects the peer, so the peers are written concurrently.
+__global__ void __launch_bounds__(256)
+    peer_push_kernel(const float* __restrict__ src, peer_dsts dst, size_t n_rows, size_t n_cols, size_t stride) {
+  float* out = dst.p[blockIdx.y];
+  const size_t c4 = n_cols / 4, total = n_rows * c4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / c4, c = (i % c4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(src + r * stride + c);
+    *reinterpret_cast<float4*>(out + r * stride + c) = v;
+  }
+}
+
 __global__ void peer_signal_wait_kernel(peer_flags flags, int world, int rank, uint32_t epoch, uint64_t limit_ns,
                                         rmi_dev_status* status) {
   const int p = threadIdx.x;
@@ -98,4 +117,17 @@ extern "C" int32_t rmi_check_status(rmi_ctx* ctx) {
   RMI_TRY(rmi_check_ctx(ctx));
   std::lock_guard<std::mutex> lock(ctx->mu);
   return rmi_check_dev_status(ctx, "rmi_check_status");
+}
+
+// dsts: the peers' pointers to the same element as src (n_peers <= RMI_MAX_FANOUT - 1).  n_cols % 4 == 0, 16-byte aligned.
+int32_t launch_peer_push(rmi_ctx* ctx, cudaStream_t stream, const float* src, float* const* dsts, int n_peers, size_t n_rows,
+                         size_t n_cols, size_t stride) {
+  if (n_peers <= 0 || n_rows == 0 || n_cols == 0) return RMI_OK;
+  peer_dsts d = {};
+  for (int i = 0; i < n_peers; i++) d.p[i] = dsts[i];
+  // about a third of the SMs in total: enough loads in flight for the links, few enough to leave the matmul its issue slots
+  unsigned per_peer = (unsigned)(ctx->sm_count / 3 / n_peers);
+  if (per_peer < 4) per_peer = 4;
+  peer_push_kernel<<<dim3(per_peer, (unsigned)n_peers), 256, 0, stream>>>(src, d, n_rows, n_cols, stride);
+  return rmi_post_launch(ctx, "peer_push");
 }

@@ -220,8 +220,8 @@ extern "C" int32_t rmi_matmul_q8_0_sharded_dev(rmi_ctx* ctx, rmi_shard_group* g,
   RMI_TRY(check_group(g));
   RMI_TRY(rmi_check_weight(w, RMI_GGML_Q8_0));
   RMI_REQUIRE(g->connected, RMI_ERR_BAD_HANDLE, "shard group is not connected (rmi_shard_group_connect)");
-  RMI_REQUIRE(exchange == RMI_EXCHANGE_FUSED_STORES || exchange == RMI_EXCHANGE_PEER_COPY, RMI_ERR_UNSUPPORTED,
-              "unknown exchange %d", exchange);
+  RMI_REQUIRE(exchange == RMI_EXCHANGE_FUSED_STORES || exchange == RMI_EXCHANGE_PEER_COPY || exchange == RMI_EXCHANGE_PEER_PUSH,
+              RMI_ERR_UNSUPPORTED, "unknown exchange %d", exchange);
   const size_t npr = g->n_out / (size_t)g->world;
   RMI_REQUIRE(w->n_rows == npr, RMI_ERR_BAD_SHAPE, "weight shard has %zu rows, the group expects %zu", w->n_rows, npr);
   RMI_REQUIRE(m >= 1 && m <= g->m_max, RMI_ERR_BAD_SHAPE, "m=%zu outside 1..%zu", m, g->m_max);
@@ -252,11 +252,18 @@ extern "C" int32_t rmi_matmul_q8_0_sharded_dev(rmi_ctx* ctx, rmi_shard_group* g,
       RMI_TRY(matmul_q8_0_device(ctx, w, x + r0 * w->n_in, nr, own + r0 * g->n_out + col_off, g->n_out));
       RMI_CUDA_CHECK(cudaEventRecord(g->ev_slab[s], ctx->stream));
       RMI_CUDA_CHECK(cudaStreamWaitEvent(g->copy_stream, g->ev_slab[s], 0));
-      for (int i = 1; i < g->world; i++) {
-        float* peer = g->peer_out[par][(g->rank + i) % g->world];
-        RMI_CUDA_CHECK(cudaMemcpy2DAsync(peer + r0 * g->n_out + col_off, g->n_out * sizeof(float),
-                                         own + r0 * g->n_out + col_off, g->n_out * sizeof(float), npr * sizeof(float), nr,
-                                         cudaMemcpyDeviceToDevice, g->copy_stream));
+      if (exchange == RMI_EXCHANGE_PEER_PUSH && npr % 4 == 0 && g->n_out % 4 == 0) {
+        // one kernel stores the slab into all peers at once (peers in rank order starting after this rank)
+        float* dsts[RMI_MAX_FANOUT];
+        for (int i = 1; i < g->world; i++) dsts[i - 1] = g->peer_out[par][(g->rank + i) % g->world] + r0 * g->n_out + col_off;
+        RMI_TRY(launch_peer_push(ctx, g->copy_stream, own + r0 * g->n_out + col_off, dsts, g->world - 1, nr, npr, g->n_out));
+      } else {
+        for (int i = 1; i < g->world; i++) {
+          float* peer = g->peer_out[par][(g->rank + i) % g->world];
+          RMI_CUDA_CHECK(cudaMemcpy2DAsync(peer + r0 * g->n_out + col_off, g->n_out * sizeof(float),
+                                           own + r0 * g->n_out + col_off, g->n_out * sizeof(float), npr * sizeof(float), nr,
+                                           cudaMemcpyDeviceToDevice, g->copy_stream));
+        }
       }
       r0 += nr;
     }

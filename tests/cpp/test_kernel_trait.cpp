@@ -89,7 +89,7 @@ static void sharded_checks() {
   uint8_t handles[192];
   rmi::check(rmi_shard_group_export(ctx, g, handles));
   rmi::check(rmi_shard_group_connect(ctx, g, handles));
-  for (int exchange : {RMI_EXCHANGE_FUSED_STORES, RMI_EXCHANGE_PEER_COPY}) {
+  for (int exchange : {RMI_EXCHANGE_FUSED_STORES, RMI_EXCHANGE_PEER_COPY, RMI_EXCHANGE_PEER_PUSH}) {
     float* result = nullptr;
     rmi::check(rmi_matmul_q8_0_sharded_dev(ctx, g, wt, (const float*)dx, m, exchange, &result));
     rmi::check(rmi_check_status(ctx));
@@ -98,7 +98,7 @@ static void sharded_checks() {
   }
   uint32_t epoch = 0;
   rmi::check(rmi_shard_group_epoch(g, &epoch));
-  EXPECT(epoch == 2);
+  EXPECT(epoch == 3);
   rmi::check(rmi_shard_group_free(ctx, g));
   // NCCL entry point with a one-rank communicator created through the library
   uint8_t id[128];

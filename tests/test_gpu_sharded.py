@@ -113,7 +113,7 @@ def test_peer_sharded_linear_single_rank_and_flag_round(rmi, m):
         x = torch.from_numpy(rmi.synth.normal((m, k), seed=9 + rnd)).cuda()
         ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
         rmi.matmul_q8_0_dev(lin.weight, x.data_ptr(), m, ref.data_ptr())
-        ptr = lin.forward_dev(x.data_ptr(), m, rmi.EXCHANGE_PEER_COPY if rnd % 2 else rmi.EXCHANGE_FUSED_STORES)
+        ptr = lin.forward_dev(x.data_ptr(), m, (rmi.EXCHANGE_FUSED_STORES, rmi.EXCHANGE_PEER_COPY, rmi.EXCHANGE_PEER_PUSH)[rnd % 3])
         ctx.check_status()
         got = np.empty((m, n), np.float32)
         ctx.d2h(got, ptr)
@@ -211,7 +211,7 @@ for m in (1, 16, 160, 1200):
         pkg.matmul_q8_0_dev(full, x.data_ptr(), m, ref.data_ptr())
         refs.append(ref)
     ctx.sync()
-    for exchange in (pkg.EXCHANGE_FUSED_STORES, pkg.EXCHANGE_PEER_COPY):
+    for exchange in (pkg.EXCHANGE_FUSED_STORES, pkg.EXCHANGE_PEER_COPY, pkg.EXCHANGE_PEER_PUSH):
         for x, ref in zip(xs, refs):
             ptr = lin.forward_dev(x.data_ptr(), m, exchange)
             got = np.empty((m, n), np.float32)
