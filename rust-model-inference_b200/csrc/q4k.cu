@@ -497,11 +497,18 @@ __global__ void __launch_bounds__(32 * Q4S_WARPS)
   // the MB activation rows of this pass, once per CTA.  Word 16 jg + 8 h + l of a super-block (group jg, low / high
   // half h, lane l) goes to word 32 (jg / 2) + 4 l + 2 (jg % 2) + h: lane l then reads words 4l..4l+3 of two pieces.
   {
+    // asynchronous 4-byte copies straight to the permuted place: all of a thread's copies are in flight at once (a
+    // load-store loop through registers would pay one memory round trip per batch of loads)
+    const int* src = reinterpret_cast<const int*>(q8 + t0 * nb * 256);
     for (size_t idx = tid; idx < (size_t)MB * nb * 64; idx += 32 * Q4S_WARPS) {
       const size_t rb = idx >> 6;   // (activation row, super-block)
       const int ws = (int)(idx & 63), jg = ws >> 4, h = (ws >> 3) & 1, l = ws & 7;
-      xq_s[rb * 64 + 32 * (jg >> 1) + 4 * l + 2 * (jg & 1) + h] = __ldg(reinterpret_cast<const int*>(q8 + t0 * nb * 256) + idx);
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(
+                       xq_s + rb * 64 + 32 * (jg >> 1) + 4 * l + 2 * (jg & 1) + h)),
+                   "l"(src + idx)
+                   : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     for (size_t idx = tid; idx < (size_t)MB * nb * 4; idx += 32 * Q4S_WARPS) {
       // mod.rs:749-756: hadd_epi16 (wrapping i16) of neighbouring bsums, the two pairs of lane idx % 4
       const int2 b4 = __ldg(reinterpret_cast<const int2*>(bs + t0 * nb * 16) + idx);
@@ -509,6 +516,7 @@ __global__ void __launch_bounds__(32 * Q4S_WARPS)
                             (int)(int16_t)((int16_t)(b4.y & 0xffff) + (int16_t)(b4.y >> 16)));
     }
     for (size_t idx = tid; idx < (size_t)MB * nb; idx += 32 * Q4S_WARPS) xd_s[idx] = __ldg(d8 + t0 * nb + idx);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
 
