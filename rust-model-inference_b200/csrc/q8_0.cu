@@ -982,7 +982,9 @@ static int32_t gemv_dispatch_lb(rmi_ctx* ctx, const rmi_weight* w, const uint8_t
     // with the passes of 4 and 8 rows included; twelve CTAs per SM is slower again (9.28 k at batch 32).
     const size_t t1 = (row_end + 15) / 16 - row_begin / 16, blocks = w->n_in / 32;
     const size_t smem = 128 + blocks * Q8_REC_BYTES + (size_t)MP * (w->n_in + blocks * 4);
-    if (t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024) {
+    // wider passes only while two CTAs fit on an SM (an 8192-column tile with eight activation rows takes a whole SM
+    // and ran slower than the register-staged kernel: 92 against 55 us for 4096 x 8192 at M = 16)
+    if (t1 * n_groups <= (size_t)ctx->sm_count * 6 && smem <= ctx->smem_optin - 1024 && (MP <= 2 || smem <= 100 * 1024)) {
       auto kern = q8_gemv_staged_kernel<SEM, MP, false>;
       if (smem > 48 * 1024 &&
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
