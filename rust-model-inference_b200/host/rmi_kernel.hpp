@@ -8,6 +8,7 @@
 //   QuantizedLinear                       src/core/model.rs:12-104
 //   quantize_q8_0_into                    src/ops/quant/q8_0.rs:3-24
 //   matmul_q8_0_quantized_parallel_rows   src/ops/kernel/q8_0/parallel.rs:102-139
+//   matmul_q8_0 (legacy f32 input)        src/ops/kernel/q8_0/parallel.rs:317-341
 // Error convention: the trait methods return nothing; a failing device call throws
 // rmi::Error (the Rust shim panics, like `.expect("GPU matmul failed")` in dispatch.rs:47-48).
 #pragma once
@@ -73,6 +74,12 @@ inline void matmul_q8_0_quantized_parallel_rows(const Weight& weight, const uint
     if (s >= e) return;
   }
   check(rmi_matmul_q8_0_prequantized(context(), weight.handle(), input_q8, input_scales, 1, output, s, e));
+}
+
+// matmul_q8_0(weight, input, output, n_in, n_out): the legacy f32-input matmul, one activation row, no activation
+// quantization; accumulation order by the context's semantics (AVX2 or the scalar fallback).
+inline void matmul_q8_0(const Weight& weight, const float* input, float* output, size_t /*n_in*/, size_t /*n_out*/) {
+  check(rmi_matmul_q8_0_f32(context(), weight.handle(), input, 1, output));
 }
 
 // trait Kernel

@@ -143,6 +143,19 @@ int main(int argc, char** argv) {
       k.forward(ones.data(), out, 32, 1);
       EXPECT(std::fabs(out[0] - 32.0f) < 5e-3f);
     }
+    {  // legacy f32-input matmul: uniform weight 1 * 0.5 against an exactly representable activation row
+      auto w = q8_0_uniform_row(1, 0.5f);
+      rmi::Weight wt(RMI_GGML_Q8_0, w.data(), w.size(), 32, 1);
+      std::vector<float> x(32);
+      float expect = 0.0f;
+      for (int i = 0; i < 32; i++) {
+        x[i] = 0.25f * (float)(i - 7);
+        expect += 0.5f * x[i];
+      }
+      float out[1] = {0};
+      rmi::matmul_q8_0(wt, x.data(), out, 32, 1);
+      EXPECT(out[0] == expect);  // every partial sum is a small multiple of 1/8: exact in any order
+    }
     {  // q8_kernel_thread_partition
       std::vector<uint8_t> w;
       for (int i = 0; i < 4; i++) {
