@@ -218,11 +218,10 @@ __global__ void __launch_bounds__(256)
   if (!fused)
     for (size_t i = tid; i < group * row16; i += blockDim.x)
       cp_async16(qs + i * 8, q16 + b * nq + kvh * group * hd + i * 8);
-  for (size_t i = tid; i < (size_t)n_ld * row16; i += blockDim.x)
-    cp_async16(kbuf + (i / row16) * kstride + (i % row16) * 16, kbase + (i / row16) * nk + (i % row16) * 8);
+  const row_copy_plan plan = make_row_copy_plan((unsigned)row16);
+  cp_async_rows(plan, kbuf, kstride, kbase, nk * 2, (unsigned)n_ld);
   cp_async_commit();
-  for (size_t i = tid; i < (size_t)n_ld * row16; i += blockDim.x)
-    cp_async16(vbuf + i * 16, vbase + (i / row16) * nk + (i % row16) * 8);
+  cp_async_rows(plan, vbuf, hd * 2, vbase, nk * 2, (unsigned)n_ld);
   cp_async_commit();
   if (fused) {
     pdl_wait();
@@ -267,8 +266,9 @@ __global__ void __launch_bounds__(256)
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // all CTAs of the cluster have started
 
   // scores[g][t] = f32(sum_f64 q*k) * kq_scale, sequential over the head dimension (dot.rs:115-118)
-  for (size_t item = tid; item < (size_t)n_t * group; item += blockDim.x) {
-    const size_t tl = item / group, g = item % group;
+  const unsigned grp = (unsigned)group, hdu = (unsigned)hd;
+  for (unsigned item = tid; item < (unsigned)n_t * grp; item += blockDim.x) {
+    const unsigned tl = item / grp, g = item - tl * grp;
     const uint32_t* kr = reinterpret_cast<const uint32_t*>(kbuf + tl * kstride);
     const uint32_t* qr = reinterpret_cast<const uint32_t*>(qs + g * hd);
     double s = 0.0;
@@ -292,8 +292,8 @@ __global__ void __launch_bounds__(256)
       if (lane == 0) red[g] = mx;
     }
     __syncthreads();
-    for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
-      const size_t g = i / T, t = i % T;
+    for (unsigned i = tid; i < grp * (unsigned)T; i += blockDim.x) {
+      const unsigned g = i / (unsigned)T, t = i - g * (unsigned)T;
       sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
     }
     __syncthreads();
@@ -306,8 +306,8 @@ __global__ void __launch_bounds__(256)
       }
     }
     __syncthreads();
-    for (size_t i = tid; i < group * (size_t)n_t; i += blockDim.x) {
-      const size_t g = i / n_t, tl = i % n_t;
+    for (unsigned i = tid; i < grp * (unsigned)n_t; i += blockDim.x) {
+      const unsigned g = i / (unsigned)n_t, tl = i - g * (unsigned)n_t;
       float pv = sc[g * cs + t0 + tl];
       if (red[g] > 0.0f) pv = __fdiv_rn(pv, red[g]);
       p16[g * chunk + tl] = f32_to_f16_bits(pv);
@@ -318,8 +318,8 @@ __global__ void __launch_bounds__(256)
 
   // partial[g][d] = sum_f64 over this CTA's steps of v[t][d] * p[g][t]  -> rank 0
   double* part0 = cluster.map_shared_rank(part, 0);
-  for (size_t o = tid; o < group * hd; o += blockDim.x) {
-    const size_t g = o / hd, d = o % hd;
+  for (unsigned o = tid; o < grp * hdu; o += blockDim.x) {
+    const unsigned g = o / hdu, d = o - g * hdu;
     const uint16_t* vc = reinterpret_cast<const uint16_t*>(vbuf) + d;
     const uint16_t* pr = p16 + g * chunk;
     double s = 0.0;
@@ -390,6 +390,7 @@ __global__ void __launch_bounds__(256)
   float* red = GS ? reinterpret_cast<float*>(qd + group * hd) : sc + group * cs;  // [group] (padded to 4)
   uint8_t* tiles = reinterpret_cast<uint8_t*>(red + ((group + 3) & ~(size_t)3));  // 2 x SEQ_TILE rows (16-byte aligned)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+  const unsigned grp = (unsigned)group;
   // K rows are padded by 16 bytes: the threads of a warp read the same words of different rows, and rows of exactly
   // hd * 2 = 256 bytes would all start in the same bank
   const size_t row_bytes = hd * 2, k_stride = row_bytes + 16, tile_bytes = SEQ_TILE * k_stride, row16 = hd / 8;
@@ -397,11 +398,10 @@ __global__ void __launch_bounds__(256)
   const float kq_scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
   const uint16_t* kbase = k_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
   const uint16_t* vbase = v_cache + ((b * n_layer + layer) * capacity) * nk + kvh * hd;
+  const row_copy_plan plan = make_row_copy_plan((unsigned)row16);
   auto stage = [&](const uint16_t* base, int tile, int buf, size_t stride) {
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
-    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
-    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
-      cp_async16(dst + (i / row16) * stride + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
+    cp_async_rows(plan, tiles + (size_t)buf * tile_bytes, stride, base + (size_t)t0 * nk, nk * 2, (unsigned)nt);
     cp_async_commit();
   };
   for (size_t i = tid; i < group * hd; i += blockDim.x)
@@ -414,8 +414,8 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
-    for (size_t item = tid; item < (size_t)nt * group; item += blockDim.x) {
-      const size_t tl = item / group, g = item % group;
+    for (unsigned item = tid; item < (unsigned)nt * grp; item += blockDim.x) {
+      const unsigned tl = item / grp, g = item - tl * grp;
       const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride);
       const double2* qr = reinterpret_cast<const double2*>(qd + g * hd);
       double s = 0.0;
@@ -443,8 +443,8 @@ __global__ void __launch_bounds__(256)
     if (lane == 0) red[g] = mx;
   }
   __syncthreads();
-  for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
-    const size_t g = i / T, t = i % T;
+  for (unsigned i = tid; i < grp * (unsigned)T; i += blockDim.x) {
+    const unsigned g = i / (unsigned)T, t = i - g * (unsigned)T;
     sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
   }
   __syncthreads();
@@ -457,26 +457,34 @@ __global__ void __launch_bounds__(256)
     }
   }
   __syncthreads();
-  for (size_t i = tid; i < group * (size_t)T; i += blockDim.x) {
-    const size_t g = i / T, t = i % T;
+  for (unsigned i = tid; i < grp * (unsigned)T; i += blockDim.x) {
+    const unsigned g = i / (unsigned)T, t = i - g * (unsigned)T;
     float pv = sc[g * cs + t];
     if (red[g] > 0.0f) pv = __fdiv_rn(pv, red[g]);
     pd[g * cs + t] = (double)f16_round_trip(pv);
   }
   // out[g][d] = f32(sum_f64 over t of v[t][d] * p[g][t]), one output element per thread and pass
   double accv[2] = {0.0, 0.0};
+  size_t pv_row[2], pv_col[2];  // probability row start and V column of this thread's two outputs
+#pragma unroll
+  for (int pass = 0; pass < 2; pass++) {
+    const unsigned o = tid + pass * blockDim.x, g = o / (unsigned)hd;
+    pv_row[pass] = g * cs;
+    pv_col[pass] = o - g * (unsigned)hd;
+  }
   for (int tile = 0; tile < n_tiles; tile++) {
     if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1, row_bytes);
     if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     const uint16_t* vt = reinterpret_cast<const uint16_t*>(tiles + (size_t)(tile & 1) * tile_bytes);
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
-    int pass = 0;
-    for (size_t o = tid; o < group * hd && pass < 2; o += blockDim.x, pass++) {
-      const size_t g = o / hd, dd = o % hd;
-      const double* pr = pd + g * cs + t0;
+#pragma unroll
+    for (int pass = 0; pass < 2; pass++) {
+      if (tid + pass * blockDim.x >= group * hd) break;
+      const double* pr = pd + pv_row[pass] + t0;
+      const uint16_t* vc = vt + pv_col[pass];
       double s = accv[pass];
-      for (int tl = 0; tl < nt; tl++) s = fma((double)f16_bits_to_f32(vt[(size_t)tl * hd + dd]), pr[tl], s);
+      for (int tl = 0; tl < nt; tl++) s = fma((double)f16_bits_to_f32(vc[(size_t)tl * hd]), pr[tl], s);
       accv[pass] = s;
     }
     __syncthreads();
@@ -529,11 +537,10 @@ __global__ void __launch_bounds__(256)
   uint8_t* tiles = reinterpret_cast<uint8_t*>(seg + 256);
   const size_t row_bytes = hd * 2, tile_bytes = ATT_TILE * row_bytes, row16 = hd / 8;
   const int n_tiles = (T + ATT_TILE - 1) / ATT_TILE;
+  const row_copy_plan plan = make_row_copy_plan((unsigned)row16);
   auto stage = [&](const uint16_t* base, int tile, int buf) {
     const int t0 = tile * ATT_TILE, nt = min(ATT_TILE, T - t0);
-    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
-    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
-      cp_async16(dst + (i / row16) * row_bytes + (i % row16) * 16, base + (size_t)(t0 + i / row16) * nk + (i % row16) * 8);
+    cp_async_rows(plan, tiles + (size_t)buf * tile_bytes, row_bytes, base + (size_t)t0 * nk, nk * 2, (unsigned)nt);
     cp_async_commit();
   };
 
@@ -681,12 +688,11 @@ __global__ void __launch_bounds__(256)
   const size_t row_bytes = hd * sizeof(kv_t), row_stride = row_bytes + 16, tile_bytes = SM_TILE * row_stride;
   const size_t row16 = row_bytes / 16;
   const int n_tiles = (T + SM_TILE - 1) / SM_TILE;
+  const row_copy_plan plan = make_row_copy_plan((unsigned)row16);
   auto stage = [&](const kv_t* base, int tile, int buf) {
     const int t0 = tile * SM_TILE, nt = min(SM_TILE, T - t0);
-    uint8_t* dst = tiles + (size_t)buf * tile_bytes;
-    for (size_t i = tid; i < (size_t)nt * row16; i += blockDim.x)
-      cp_async16(dst + (i / row16) * row_stride + (i % row16) * 16,
-                 reinterpret_cast<const uint8_t*>(base + (size_t)(t0 + i / row16) * nk) + (i % row16) * 16);
+    cp_async_rows(plan, tiles + (size_t)buf * tile_bytes, row_stride, base + (size_t)t0 * nk, nk * sizeof(kv_t),
+                  (unsigned)nt);
     cp_async_commit();
   };
 

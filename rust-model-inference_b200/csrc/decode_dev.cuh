@@ -14,6 +14,36 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Copying `rows` rows of `row16` 16-byte pieces (global rows src_stride bytes apart, shared rows dst_stride bytes
+// apart) with cp.async, the pieces dealt to the CTA's threads in order.  The (row, piece) of a thread advances by a
+// fixed step, so the plan costs two 32-bit divisions per kernel and the copy loops none.
+struct row_copy_plan {
+  unsigned r0, c0, dr, dc, row16;
+};
+__device__ __forceinline__ row_copy_plan make_row_copy_plan(unsigned row16) {
+  row_copy_plan p;
+  p.row16 = row16;
+  p.r0 = threadIdx.x / row16;
+  p.c0 = threadIdx.x - p.r0 * row16;
+  p.dr = blockDim.x / row16;
+  p.dc = blockDim.x - p.dr * row16;
+  return p;
+}
+__device__ __forceinline__ void cp_async_rows(const row_copy_plan& p, uint8_t* dst, size_t dst_stride, const void* src,
+                                              size_t src_stride, unsigned rows) {
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  unsigned r = p.r0, c = p.c0;
+  while (r < rows) {
+    cp_async16(dst + r * dst_stride + c * 16, s + r * src_stride + c * 16);
+    r += p.dr;
+    c += p.dc;
+    if (c >= p.row16) {
+      c -= p.row16;
+      r++;
+    }
+  }
+}
+
 __device__ __forceinline__ double warp_sum_f64(double v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
