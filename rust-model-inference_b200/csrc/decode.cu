@@ -367,8 +367,15 @@ constexpr int SEQ_TILE = 128;
 // GS: the score and probability rows ([group][capacity] f32 and f16) live in a global scratch area instead of shared
 // memory (g_sc / g_p16, one slice per CTA), for capacities whose rows do not fit: only this CTA touches its slice and
 // the phases are separated by CTA barriers, so the arithmetic and its order are unchanged.
-template <int SEM, bool GS>
-__global__ void __launch_bounds__(256)
+// G > 0: the group has exactly G query heads of 128 elements.  Every cached value is then converted once for all
+// heads of the group, by SEQ_THREADS_G threads: a thread of the score pass takes one position and one of QS slices of
+// the head dimension for the G heads (G independent chains), a thread of the P.V pass takes two adjacent output
+// columns and one of PS slices of each tile's positions for the G heads (2 G chains).  The f64 partial sums are added
+// in ascending slice order: like the tree sums of the other f64 accumulations, exact whenever no f64 rounding occurs,
+// which the products of two f16 values make the overwhelmingly common case.  G == 0: any group and head size.
+constexpr int SEQ_THREADS_G = 512;
+template <int SEM, bool GS, int G>
+__global__ void __launch_bounds__(G > 0 ? SEQ_THREADS_G : 256)
     attention_seq_kernel(const uint16_t* __restrict__ q16, const uint16_t* __restrict__ k_cache,
                          const uint16_t* __restrict__ v_cache, const int* __restrict__ d_step, size_t n_head,
                          size_t n_head_kv, size_t hd, size_t layer, size_t n_layer, size_t capacity,
@@ -391,6 +398,9 @@ __global__ void __launch_bounds__(256)
   uint8_t* tiles = reinterpret_cast<uint8_t*>(red + ((group + 3) & ~(size_t)3));  // 2 x SEQ_TILE rows (16-byte aligned)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
   const unsigned grp = (unsigned)group;
+  constexpr int HD = 128;  // head size of the G > 0 variants
+  constexpr int QS = SEQ_THREADS_G / SEQ_TILE, PS = SEQ_THREADS_G / (HD / 2);  // slices of the two passes
+  constexpr int GA = G > 0 ? G : 1;
   // K rows are padded by 16 bytes: the threads of a warp read the same words of different rows, and rows of exactly
   // hd * 2 = 256 bytes would all start in the same bank
   const size_t row_bytes = hd * 2, k_stride = row_bytes + 16, tile_bytes = SEQ_TILE * k_stride, row16 = hd / 8;
@@ -408,44 +418,110 @@ __global__ void __launch_bounds__(256)
     qd[i] = (double)f16_bits_to_f32(q16[b * nq + kvh * group * hd + i]);
   stage(kbase, 0, 0, k_stride);
   // scores[g][t] = f32(sum_f64 q*k) * kq_scale (dot.rs:115-118)
+  // One barrier per tile: after it the tile's rows are visible and every thread is done with the previous tile, so
+  // the other tile buffer may be refilled and (G > 0) the previous tile's partial sums may be folded.
+  double* qk_parts = reinterpret_cast<double*>(tiles + 2 * tile_bytes);  // G > 0: [2][QS][G][SEQ_TILE]
+  auto fold_scores = [&](int tile) {
+    const double* part = qk_parts + (size_t)(tile & 1) * (QS * GA * SEQ_TILE);
+    const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
+    for (int item = tid; item < GA * SEQ_TILE; item += blockDim.x) {
+      const int g = item >> 7, t = item & (SEQ_TILE - 1);
+      if (t < nt) {
+        double s = part[g * SEQ_TILE + t];
+#pragma unroll
+        for (int h = 1; h < QS; h++) s += part[(h * GA + g) * SEQ_TILE + t];
+        sc[g * cs + t0 + t] = __fmul_rn((float)s, kq_scale);
+      }
+    }
+  };
   for (int tile = 0; tile < n_tiles; tile++) {
-    if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1, k_stride);
-    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+    cp_async_wait<0>();
     __syncthreads();
+    if (tile + 1 < n_tiles) stage(kbase, tile + 1, (tile + 1) & 1, k_stride);
     const uint8_t* kt = tiles + (size_t)(tile & 1) * tile_bytes;
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
-    for (unsigned item = tid; item < (unsigned)nt * grp; item += blockDim.x) {
-      const unsigned tl = item / grp, g = item - tl * grp;
-      const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride);
-      const double2* qr = reinterpret_cast<const double2*>(qd + g * hd);
-      double s = 0.0;
-      for (size_t i = 0; i < hd / 8; i++) {
-        const uint4 kv = kr[i];
-        const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+    if constexpr (G > 0) {
+      if (tile > 0) fold_scores(tile - 1);
+      double* qk_part = qk_parts + (size_t)(tile & 1) * (QS * G * SEQ_TILE);
+      const int tl = tid & (SEQ_TILE - 1), h = tid >> 7;                    // four warps per slice
+      if (tl < nt) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride) + h * (HD / QS / 8);
+        const double2* qr = reinterpret_cast<const double2*>(qd + h * (HD / QS));
+        double s[G];
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const double2 q2 = qr[i * 4 + e];
-          s = fma(q2.x, (double)f16_bits_to_f32((uint16_t)(kw[e] & 0xffff)), s);
-          s = fma(q2.y, (double)f16_bits_to_f32((uint16_t)(kw[e] >> 16)), s);
+        for (int g = 0; g < G; g++) s[g] = 0.0;
+#pragma unroll 2
+        for (int i = 0; i < HD / QS / 8; i++) {
+          const uint4 kv = kr[i];
+          const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const double k0 = (double)f16_bits_to_f32((uint16_t)(kw[e] & 0xffff));
+            const double k1 = (double)f16_bits_to_f32((uint16_t)(kw[e] >> 16));
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+              const double2 q2 = qr[g * (HD / 2) + i * 4 + e];
+              s[g] = fma(q2.x, k0, s[g]);
+              s[g] = fma(q2.y, k1, s[g]);
+            }
+          }
         }
-      }
-      sc[g * cs + t0 + tl] = __fmul_rn((float)s, kq_scale);
-    }
-    __syncthreads();
-  }
-  stage(vbase, 0, 0, row_bytes);  // the first V tile travels while the soft-max is evaluated
-  // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
-  for (size_t g = warp; g < group; g += nwarp) {
-    float mx = -INFINITY;
-    for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * cs + t]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) red[g] = mx;
+        for (int g = 0; g < G; g++) qk_part[(h * G + g) * SEQ_TILE + tl] = s[g];
+      }
+    } else {
+      for (unsigned item = tid; item < (unsigned)nt * grp; item += blockDim.x) {
+        const unsigned tl = item / grp, g = item - tl * grp;
+        const uint4* kr = reinterpret_cast<const uint4*>(kt + tl * k_stride);
+        const double2* qr = reinterpret_cast<const double2*>(qd + g * hd);
+        double s = 0.0;
+        for (size_t i = 0; i < hd / 8; i++) {
+          const uint4 kv = kr[i];
+          const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const double2 q2 = qr[i * 4 + e];
+            s = fma(q2.x, (double)f16_bits_to_f32((uint16_t)(kw[e] & 0xffff)), s);
+            s = fma(q2.y, (double)f16_bits_to_f32((uint16_t)(kw[e] >> 16)), s);
+          }
+        }
+        sc[g * cs + t0 + tl] = __fmul_rn((float)s, kq_scale);
+      }
+    }
   }
   __syncthreads();
-  for (unsigned i = tid; i < grp * (unsigned)T; i += blockDim.x) {
-    const unsigned g = i / (unsigned)T, t = i - g * (unsigned)T;
-    sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
+  stage(vbase, 0, 0, row_bytes);  // the first V tile travels while the soft-max is evaluated
+  // max, exp, sequential f32 sum (attention.rs:28-38), divide, f16
+  if constexpr (G > 0) {
+    fold_scores(n_tiles - 1);
+    __syncthreads();
+    // every warp finds the G maxima itself (a maximum does not depend on the order): no hand-over through shared memory
+    float mx[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      float m = -INFINITY;
+      for (int t = lane; t < T; t += 32) m = fmaxf(m, sc[g * cs + t]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      mx[g] = m;
+    }
+    __syncthreads();  // all maxima taken before any score is overwritten
+#pragma unroll
+    for (int g = 0; g < G; g++)
+      for (int t = tid; t < T; t += blockDim.x) sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], mx[g]));
+  } else {
+    for (size_t g = warp; g < group; g += nwarp) {
+      float mx = -INFINITY;
+      for (int t = lane; t < T; t += 32) mx = fmaxf(mx, sc[g * cs + t]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) red[g] = mx;
+    }
+    __syncthreads();
+    for (unsigned i = tid; i < grp * (unsigned)T; i += blockDim.x) {
+      const unsigned g = i / (unsigned)T, t = i - g * (unsigned)T;
+      sc[g * cs + t] = exp_cr(__fsub_rn(sc[g * cs + t], red[g]));
+    }
   }
   __syncthreads();
   for (size_t g = warp; g < group; g += nwarp) {
@@ -472,22 +548,59 @@ __global__ void __launch_bounds__(256)
     pv_row[pass] = g * cs;
     pv_col[pass] = o - g * (unsigned)hd;
   }
+  double acc2[GA][2];  // G > 0: columns 2 * pair and 2 * pair + 1 of the G heads over this thread's slice of the positions
+#pragma unroll
+  for (int g = 0; g < GA; g++) acc2[g][0] = acc2[g][1] = 0.0;
   for (int tile = 0; tile < n_tiles; tile++) {
+    cp_async_wait<0>();
+    __syncthreads();  // the tile (and, first time, the probabilities) visible; everyone is done with the previous tile
     if (tile + 1 < n_tiles) stage(vbase, tile + 1, (tile + 1) & 1, row_bytes);
-    if (tile + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
-    __syncthreads();
     const uint16_t* vt = reinterpret_cast<const uint16_t*>(tiles + (size_t)(tile & 1) * tile_bytes);
     const int t0 = tile * SEQ_TILE, nt = min(SEQ_TILE, T - t0);
+    if constexpr (G > 0) {
+      const int pair = tid & 63, slice = tid >> 6;
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(vt) + pair;
+      const double* pr = pd + t0;
+      const int t_end = min(nt, slice * (SEQ_TILE / PS) + SEQ_TILE / PS);
+#pragma unroll 4
+      for (int tl = slice * (SEQ_TILE / PS); tl < t_end; tl++) {
+        const uint32_t w = vw[tl * (HD / 2)];
+        const double v0 = (double)f16_bits_to_f32((uint16_t)(w & 0xffff)), v1 = (double)f16_bits_to_f32((uint16_t)(w >> 16));
 #pragma unroll
-    for (int pass = 0; pass < 2; pass++) {
-      if (tid + pass * blockDim.x >= group * hd) break;
-      const double* pr = pd + pv_row[pass] + t0;
-      const uint16_t* vc = vt + pv_col[pass];
-      double s = accv[pass];
-      for (int tl = 0; tl < nt; tl++) s = fma((double)f16_bits_to_f32(vc[(size_t)tl * hd]), pr[tl], s);
-      accv[pass] = s;
+        for (int g = 0; g < G; g++) {
+          const double pg = pr[g * cs + tl];
+          acc2[g][0] = fma(v0, pg, acc2[g][0]);
+          acc2[g][1] = fma(v1, pg, acc2[g][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int pass = 0; pass < 2; pass++) {
+        if (tid + pass * blockDim.x >= group * hd) break;
+        const double* pr = pd + pv_row[pass] + t0;
+        const uint16_t* vc = vt + pv_col[pass];
+        double s = accv[pass];
+        for (int tl = 0; tl < nt; tl++) s = fma((double)f16_bits_to_f32(vc[(size_t)tl * hd]), pr[tl], s);
+        accv[pass] = s;
+      }
+    }
+  }
+  if constexpr (G > 0) {  // the PS slices of every output, added in order (the tiles are free by now)
+    double* pv_part = reinterpret_cast<double*>(tiles);  // [PS][G * HD]
+    const int pair = tid & 63, slice = tid >> 6;
+    __syncthreads();  // every thread is done with the last tile
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      pv_part[slice * (G * HD) + g * HD + 2 * pair] = acc2[g][0];
+      pv_part[slice * (G * HD) + g * HD + 2 * pair + 1] = acc2[g][1];
     }
     __syncthreads();
+    if (tid < G * HD) {  // G * HD <= SEQ_THREADS_G: one output per thread
+      double s = pv_part[tid];
+#pragma unroll
+      for (int q = 1; q < PS; q++) s += pv_part[q * (G * HD) + tid];
+      accv[0] = s;
+    }
   }
   // f32 (debug) and Q8_0 blocks of this kv head's group*hd outputs: 32 consecutive outputs per warp and pass
   const size_t out0 = kvh * group * hd;
@@ -1038,13 +1151,29 @@ bool attention_seq_eligible(const decode_dims& d) { return attention_seq_shape_o
 size_t attention_seq_smem_bytes(const decode_dims& d, bool global_scores) {
   const size_t group = d.n_head / d.n_head_kv, cs = (d.capacity + 7) & ~(size_t)7;
   return (global_scores ? 0 : group * cs * 4 + group * cs * 8) + ((group + 3) & ~(size_t)3) * 4 + group * d.hd * 8 +
-         2 * (size_t)SEQ_TILE * (d.hd * 2 + 16);
+         2 * (size_t)SEQ_TILE * (d.hd * 2 + 16) + 2 * (SEQ_THREADS_G / SEQ_TILE) * group * SEQ_TILE * 8;  // last: slices of the score dots, two tiles
 }
 
 // Bytes of global scratch for the score rows (f32) and the probability rows (f64 copies of the f16 values) of all CTAs.
 size_t attention_seq_scratch_bytes(const decode_dims& d) {
   const size_t cs = (d.capacity + 7) & ~(size_t)7;
   return d.batch * d.n_head * cs * 12;
+}
+
+using attention_seq_fn = void (*)(const uint16_t*, const uint16_t*, const uint16_t*, const int*, size_t, size_t, size_t,
+                                 size_t, size_t, size_t, float*, uint8_t*, float*, float*, double*);
+template <int SEM, bool GS>
+static attention_seq_fn attention_seq_pick_g(int g) {
+  return g == 2 ? attention_seq_kernel<SEM, GS, 2> : (g == 4 ? attention_seq_kernel<SEM, GS, 4> : attention_seq_kernel<SEM, GS, 0>);
+}
+template <int SEM>
+static attention_seq_fn attention_seq_pick_gs(bool gs, int g) {
+  return gs ? attention_seq_pick_g<SEM, true>(g) : attention_seq_pick_g<SEM, false>(g);
+}
+static attention_seq_fn attention_seq_pick(int sem, bool gs, int g) {
+  return sem == RMI_SEM_AVX2 ? attention_seq_pick_gs<RMI_SEM_AVX2>(gs, g)
+                             : (sem == RMI_SEM_NEON ? attention_seq_pick_gs<RMI_SEM_NEON>(gs, g)
+                                                    : attention_seq_pick_gs<RMI_SEM_SCALAR>(gs, g));
 }
 
 int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t* q16, const uint16_t* k_cache,
@@ -1055,18 +1184,15 @@ int32_t launch_attention_seq(rmi_ctx* ctx, const decode_dims& d, const uint16_t*
   const size_t smem = attention_seq_smem_bytes(d, gs);
   double* g_pd = reinterpret_cast<double*>(score_scratch);   // doubles first: 8-byte alignment
   float* g_sc = gs ? reinterpret_cast<float*>(g_pd + d.batch * d.n_head * cs) : nullptr;
-  auto kern = gs ? (ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2, true>
-                                             : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON, true>
-                                                                         : attention_seq_kernel<RMI_SEM_SCALAR, true>))
-                 : (ctx->sem == RMI_SEM_AVX2 ? attention_seq_kernel<RMI_SEM_AVX2, false>
-                                             : (ctx->sem == RMI_SEM_NEON ? attention_seq_kernel<RMI_SEM_NEON, false>
-                                                                         : attention_seq_kernel<RMI_SEM_SCALAR, false>));
+  const size_t group = d.n_head / d.n_head_kv;
+  const int gv = d.hd == 128 && (group == 2 || group == 4) ? (int)group : 0;  // conversions shared by the group's heads
+  auto kern = attention_seq_pick(ctx->sem, gs, gv);
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     (void)cudaGetLastError();
     rmi_set_error("attention needs %zu B of shared memory", smem);
     return RMI_ERR_UNSUPPORTED;
   }
-  if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head_kv, (unsigned)d.batch), dim3(256), smem, q16, k_cache, v_cache, d_step,
+  if (rmi_launch(ctx, kern, dim3((unsigned)d.n_head_kv, (unsigned)d.batch), dim3(gv ? SEQ_THREADS_G : 256), smem, q16, k_cache, v_cache, d_step,
                  d.n_head, d.n_head_kv, d.hd, layer, d.n_layer, d.capacity, attn_out, q8, scales, g_sc, g_pd) != cudaSuccess) {
     rmi_set_error("launch of attention_seq failed: %s", cudaGetErrorString(cudaGetLastError()));
     return RMI_ERR_CUDA;
