@@ -1145,7 +1145,7 @@ bool attention_seq_shape_ok(const decode_dims& d) {
 }
 
 // ... and preferred over the cluster kernel when there are enough (sequence, kv head) pairs to fill the GPU
-bool attention_seq_eligible(const decode_dims& d) { return attention_seq_shape_ok(d) && d.batch * d.n_head_kv >= 128; }
+bool attention_seq_eligible(const decode_dims& d) { return attention_seq_shape_ok(d) && d.batch * d.n_head_kv >= 64; }
 
 // Shared memory of attention_seq_kernel; global_scores: without the [group][capacity] score and probability rows.
 size_t attention_seq_smem_bytes(const decode_dims& d, bool global_scores) {

@@ -183,7 +183,7 @@ def test_cli_forward_qwen3_head_shape_long_context_and_batch(rmi, ctx, tmp_path_
 
 @pytest.mark.parametrize("sem", [orc.SEM_AVX2, orc.SEM_NEON])
 def test_large_batch_uses_the_single_cta_attention_and_stays_bit_exact(rmi, ctx, tmp_path_factory, sem):
-    """batch * n_head_kv >= 128 switches to attention_seq_kernel (one CTA per sequence and kv head, K/V streamed
+    """batch * n_head_kv >= 64 switches to attention_seq_kernel (one CTA per sequence and kv head, K/V streamed
     through shared-memory tiles); head_dim 128, 300 positions cross the tile and the 256-padding boundaries."""
     ctx.set_semantics(sem)
     cfg = tiny_cfg(n_embd=512, n_layer=2, n_head=8, n_head_kv=4, head_dim=128, n_ff=1024, vocab=512)
