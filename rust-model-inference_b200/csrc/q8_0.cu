@@ -366,20 +366,18 @@ __global__ void __launch_bounds__(256)
   pdl_wait();
   pdl_launch_dependents();
   {
-    // four 16-byte loads in flight per thread: a rolled loop would wait for each one in turn
-    const int4* src = reinterpret_cast<const int4*>(xq);
-    int4* dst = reinterpret_cast<int4*>(xq_s);
-    const size_t n16 = MP * K / 16;
-    for (size_t i0 = threadIdx.x; i0 < n16; i0 += 4 * blockDim.x) {
-      int4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; u++)
-        if (i0 + u * blockDim.x < n16) v[u] = __ldg(src + i0 + u * blockDim.x);
-#pragma unroll
-      for (int u = 0; u < 4; u++)
-        if (i0 + u * blockDim.x < n16) dst[i0 + u * blockDim.x] = v[u];
-    }
-    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+    // asynchronous copies straight into shared memory, all of a thread's pieces in flight at once: a load / store
+    // loop through registers waits for each batch in turn
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(xq_s + i * 16)),
+                   "l"(xq + i * 16)
+                   : "memory");
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(xs_s + i)),
+                   "l"(xs + i)
+                   : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
   if (!active) return;
@@ -493,11 +491,19 @@ __global__ void __launch_bounds__(128)
   }
   pdl_wait();  // the weight copy above is in flight; everything below depends on the previous kernel
   pdl_launch_dependents();
-  if (!FUSED) {  // activations, in parallel with the weight copy
-    const int4* src = reinterpret_cast<const int4*>(xq);
-    int4* dst = reinterpret_cast<int4*>(xq_s);
-    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x) dst[i] = __ldg(src + i);
-    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x) xs_s[i] = __ldg(xs + i);
+  if (!FUSED) {
+    // activations, in parallel with the weight copy: asynchronous copies straight into shared memory, all of a
+    // thread's pieces in flight at once (a load / store loop through registers waits for each batch in turn)
+    for (size_t i = threadIdx.x; i < MP * K / 16; i += blockDim.x)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(xq_s + i * 16)),
+                   "l"(xq + i * 16)
+                   : "memory");
+    for (size_t i = threadIdx.x; i < MP * blocks; i += blockDim.x)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(xs_s + i)),
+                   "l"(xs + i)
+                   : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else {
     __shared__ double s_part[MP][4];
     __shared__ float s_scale[MP];
